@@ -1,0 +1,115 @@
+"""ctypes binding of libmla_fp4_b200.so (declarations: include/mla_fp4_b200.h).
+
+The library is required: there is no Python or CPU fallback.  If it is missing
+or fails to load, importing this module raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libmla_fp4_b200.so"
+ABI_VERSION = 1
+
+OK = 0
+ERR_BAD_ARG = 1
+ERR_UNSUPPORTED = 2
+ERR_WORKSPACE_TOO_SMALL = 3
+ERR_CUDA = 4
+ERR_DEVICE_TIMEOUT = 5
+ERR_NOT_BUILT = 6
+
+KERNEL_TCGEN05 = 0
+KERNEL_FP32_CHECK = 1
+OUT_BF16 = 0
+OUT_F32 = 1
+
+TILE_TOKENS = 128
+GROUP_HEADS = 64
+
+
+class DecodeArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p),
+        ("q_stride_batch", C.c_int64), ("q_stride_qpos", C.c_int64), ("q_stride_head", C.c_int64),
+        ("kv_cache", C.c_void_p),
+        ("kv_cache_sf", C.c_void_p),
+        ("block_tables", C.c_void_p),
+        ("block_table_stride", C.c_int64),
+        ("seq_lens", C.c_void_p),
+        ("out", C.c_void_p),
+        ("lse", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+        ("status", C.c_void_p),
+        ("batch", C.c_int32), ("q_len", C.c_int32), ("num_heads", C.c_int32), ("page_size", C.c_int32),
+        ("num_pages", C.c_int64),
+        ("softmax_scale", C.c_float), ("output_scale", C.c_float),
+        ("out_dtype", C.c_int32),
+        ("kernel", C.c_int32),
+        ("num_ctas", C.c_int32),
+        ("enable_pdl", C.c_int32),
+        ("stream", C.c_void_p),
+    ]
+
+
+EXPORTS = (
+    "mla_fp4_abi_version",
+    "mla_fp4_last_error",
+    "mla_fp4_workspace_bytes",
+    "mla_fp4_plan_partition",
+    "mla_fp4_decode",
+    "mla_fp4_merge_partials",
+    "mla_fp4_dequant_e2m1_to_e4m3",
+)
+
+
+def _load() -> C.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m flashinfer_mla_fp4_b200.build` "
+            "(nvcc, sm_100a). There is no fallback path."
+        )
+    lib = C.CDLL(str(LIB_PATH))
+    lib.mla_fp4_abi_version.restype = C.c_int
+    lib.mla_fp4_last_error.restype = C.c_char_p
+    lib.mla_fp4_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_size_t)]
+    lib.mla_fp4_workspace_bytes.restype = C.c_int
+    i32p = C.POINTER(C.c_int32)
+    lib.mla_fp4_plan_partition.argtypes = [i32p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                           i32p, i32p, i32p, i32p, i32p, i32p, i32p]
+    lib.mla_fp4_plan_partition.restype = C.c_int
+    lib.mla_fp4_decode.argtypes = [C.POINTER(DecodeArgs)]
+    lib.mla_fp4_decode.restype = C.c_int
+    lib.mla_fp4_merge_partials.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_int32,
+                                           C.c_void_p, C.c_void_p]
+    lib.mla_fp4_merge_partials.restype = C.c_int
+    lib.mla_fp4_dequant_e2m1_to_e4m3.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
+    lib.mla_fp4_dequant_e2m1_to_e4m3.restype = C.c_int
+    v = lib.mla_fp4_abi_version()
+    if v != ABI_VERSION:
+        raise ImportError(f"{LIB_PATH} has ABI version {v}, expected {ABI_VERSION}: rebuild it")
+    return lib
+
+
+lib = _load()
+
+
+def last_error() -> str:
+    return (lib.mla_fp4_last_error() or b"").decode("utf-8", "replace")
+
+
+def check(rc: int) -> None:
+    """Map a non-zero status to the exception type the reference wrapper raises for it."""
+    if rc == OK:
+        return
+    msg = last_error()
+    if rc in (ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE_TOO_SMALL):
+        raise ValueError(msg)
+    raise RuntimeError(f"mla_fp4 error {rc}: {msg}")
+
+
+def workspace_bytes(batch: int, q_len: int, num_heads: int, num_ctas: int) -> int:
+    out = C.c_size_t(0)
+    check(lib.mla_fp4_workspace_bytes(batch, q_len, num_heads, num_ctas, C.byref(out)))
+    return int(out.value)

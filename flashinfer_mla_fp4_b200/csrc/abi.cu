@@ -1,0 +1,184 @@
+// extern "C" boundary of libmla_fp4_b200.so: argument validation, host planner, launches.
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "common.cuh"
+#include "launch.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+
+int sm_count(int* out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
+  int n = 0;
+  e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("cudaDeviceGetAttribute: ") + cudaGetErrorString(e));
+  *out = n;
+  return MLA_FP4_OK;
+}
+
+bool page_size_ok(int ps) { return ps >= 8 && ps <= 128 && (128 % ps) == 0; }
+
+}  // namespace
+
+extern "C" {
+
+int mla_fp4_abi_version(void) { return MLA_FP4_ABI_VERSION; }
+
+const char* mla_fp4_last_error(void) { return g_last_error.c_str(); }
+
+int mla_fp4_workspace_bytes(int32_t batch, int32_t q_len, int32_t num_heads, int32_t num_ctas, size_t* bytes_out) {
+  if (!bytes_out) return fail(MLA_FP4_ERR_BAD_ARG, "bytes_out is null");
+  if (batch < 0 || q_len <= 0 || num_heads <= 0) return fail(MLA_FP4_ERR_BAD_ARG, "batch/q_len/num_heads out of range");
+  if (num_ctas <= 0) {
+    int rc = sm_count(&num_ctas);
+    if (rc) return rc;
+  }
+  // two partial slots per CTA (its first and its last segment), whatever the batch is
+  *bytes_out = size_t(2) * size_t(num_ctas) * mla::kSlotBytes;
+  return MLA_FP4_OK;
+}
+
+int mla_fp4_plan_partition(const int32_t* seq_lens_host, int32_t batch, int32_t q_len, int32_t num_heads,
+                           int32_t num_ctas, int32_t max_segments, int32_t* seg_cta, int32_t* seg_request,
+                           int32_t* seg_group, int32_t* seg_tile_begin, int32_t* seg_tile_end, int32_t* seg_slot,
+                           int32_t* num_segments) {
+  if (!num_segments || (batch > 0 && !seq_lens_host)) return fail(MLA_FP4_ERR_BAD_ARG, "null pointer");
+  if (batch < 0 || q_len <= 0 || num_heads <= 0 || num_ctas <= 0)
+    return fail(MLA_FP4_ERR_BAD_ARG, "batch/q_len/num_heads/num_ctas out of range");
+  const int groups = mla::num_groups(q_len, num_heads);
+  int64_t T = 0;
+  for (int b = 0; b < batch; ++b) T += mla::tiles_of(seq_lens_host[b]);
+  const int64_t Tt = T * groups;
+  int count = 0;
+  for (int i = 0; i < num_ctas; ++i) {
+    mla::Walker w;
+    w.seq_lens = seq_lens_host; w.batch = batch; w.groups = groups; w.cta = i; w.first = true;
+    w.f = mla::cta_lo(Tt, num_ctas, i);
+    w.hi = mla::cta_lo(Tt, num_ctas, i + 1);
+    w.b = 0; w.g = groups; w.t = 0;
+    if (T > 0 && w.f < w.hi) {
+      w.g = int(w.f / T);
+      int64_t r = w.f % T, run = 0;
+      for (int b = 0; b < batch; ++b) {
+        int tb = mla::tiles_of(seq_lens_host[b]);
+        if (r < run + tb) { w.b = b; w.t = int(r - run); break; }
+        run += tb;
+      }
+    }
+    mla::Segment s;
+    while (w.next(s)) {
+      if (count < max_segments) {
+        if (seg_cta) seg_cta[count] = i;
+        if (seg_request) seg_request[count] = s.b;
+        if (seg_group) seg_group[count] = s.g;
+        if (seg_tile_begin) seg_tile_begin[count] = s.tile_begin;
+        if (seg_tile_end) seg_tile_end[count] = s.tile_end;
+        if (seg_slot) seg_slot[count] = s.slot;
+      }
+      ++count;
+    }
+  }
+  *num_segments = count;
+  return MLA_FP4_OK;
+}
+
+int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
+  if (!a) return fail(MLA_FP4_ERR_BAD_ARG, "args is null");
+  if (a->batch < 0 || a->q_len <= 0 || a->num_heads <= 0) return fail(MLA_FP4_ERR_BAD_ARG, "batch/q_len/num_heads out of range");
+  if (a->batch == 0) return MLA_FP4_OK;
+  if (!a->q || !a->kv_cache || !a->kv_cache_sf || !a->block_tables || !a->seq_lens || !a->out)
+    return fail(MLA_FP4_ERR_BAD_ARG, "a required device pointer is null");
+  if (!page_size_ok(a->page_size))
+    return fail(MLA_FP4_ERR_UNSUPPORTED, "page_size must be one of 8, 16, 32, 64, 128");
+  if (a->num_heads > 128) return fail(MLA_FP4_ERR_UNSUPPORTED, "num_heads must be <= 128");
+  if (a->out_dtype != MLA_FP4_OUT_BF16 && a->out_dtype != MLA_FP4_OUT_F32)
+    return fail(MLA_FP4_ERR_UNSUPPORTED, "out_dtype must be MLA_FP4_OUT_BF16 or MLA_FP4_OUT_F32");
+  if (reinterpret_cast<uintptr_t>(a->kv_cache) % 32) return fail(MLA_FP4_ERR_BAD_ARG, "kv_cache must be 32-byte aligned");
+  if (reinterpret_cast<uintptr_t>(a->kv_cache_sf) % 16) return fail(MLA_FP4_ERR_BAD_ARG, "kv_cache_sf must be 16-byte aligned");
+  if (reinterpret_cast<uintptr_t>(a->q) % 16 || a->q_stride_head % 16 || a->q_stride_qpos % 16 || a->q_stride_batch % 16)
+    return fail(MLA_FP4_ERR_BAD_ARG, "q must be 16-byte aligned with strides that are multiples of 16");
+  if (reinterpret_cast<uintptr_t>(a->out) % 16) return fail(MLA_FP4_ERR_BAD_ARG, "out must be 16-byte aligned");
+  if (a->num_pages <= 0) return fail(MLA_FP4_ERR_BAD_ARG, "num_pages must be positive");
+
+  int num_ctas = a->num_ctas;
+  if (num_ctas <= 0) {
+    int rc = sm_count(&num_ctas);
+    if (rc) return rc;
+  }
+  size_t need = size_t(2) * size_t(num_ctas) * mla::kSlotBytes;
+  if (!a->workspace || a->workspace_bytes < need) {
+    char buf[160];
+    snprintf(buf, sizeof buf, "workspace has %zu bytes, but %zu are required", a->workspace ? a->workspace_bytes : size_t(0), need);
+    return fail(MLA_FP4_ERR_WORKSPACE_TOO_SMALL, buf);
+  }
+  if (reinterpret_cast<uintptr_t>(a->workspace) % 16) return fail(MLA_FP4_ERR_BAD_ARG, "workspace must be 16-byte aligned");
+
+  mla::DecodeParams p;
+  p.q = a->q; p.q_stride_batch = a->q_stride_batch; p.q_stride_qpos = a->q_stride_qpos; p.q_stride_head = a->q_stride_head;
+  p.kv_cache = a->kv_cache; p.kv_cache_sf = a->kv_cache_sf;
+  p.block_tables = a->block_tables; p.block_table_stride = a->block_table_stride;
+  p.seq_lens = a->seq_lens; p.out = a->out; p.lse = a->lse; p.workspace = a->workspace; p.status = a->status;
+  p.batch = a->batch; p.q_len = a->q_len; p.num_heads = a->num_heads; p.page_size = a->page_size;
+  p.groups = mla::num_groups(a->q_len, a->num_heads);
+  p.num_pages = a->num_pages;
+  p.softmax_scale = a->softmax_scale; p.output_scale = a->output_scale;
+  p.out_dtype = a->out_dtype; p.pdl = a->enable_pdl ? 1 : 0;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
+
+  cudaError_t e;
+  if (a->kernel == MLA_FP4_KERNEL_FP32_CHECK) {
+    p.pdl = 0;
+    e = mla::launch_fp32_check(p, num_ctas, stream);
+  } else if (a->kernel == MLA_FP4_KERNEL_TCGEN05) {
+    const char* why = nullptr;
+    e = mla::launch_decode_sm100(p, num_ctas, stream, &why);
+    if (e != cudaSuccess && why) return fail(MLA_FP4_ERR_UNSUPPORTED, why);
+  } else {
+    return fail(MLA_FP4_ERR_BAD_ARG, "unknown kernel id");
+  }
+  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("decode launch: ") + cudaGetErrorString(e));
+
+  mla::CombineParams c;
+  c.seq_lens = a->seq_lens; c.workspace = a->workspace; c.out = a->out; c.lse = a->lse;
+  c.batch = a->batch; c.q_len = a->q_len; c.num_heads = a->num_heads; c.groups = p.groups;
+  c.num_ctas = num_ctas; c.out_dtype = a->out_dtype; c.pdl = p.pdl;
+  e = mla::launch_combine(c, stream);
+  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("combine launch: ") + cudaGetErrorString(e));
+  return MLA_FP4_OK;
+}
+
+int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, int32_t parts, int64_t rows, void* out,
+                           int32_t out_dtype, float* lse, void* stream) {
+  if (parts <= 0 || rows < 0) return fail(MLA_FP4_ERR_BAD_ARG, "parts/rows out of range");
+  if (rows == 0) return MLA_FP4_OK;
+  if (!partial_out || !partial_lse || !out) return fail(MLA_FP4_ERR_BAD_ARG, "null pointer");
+  if (out_dtype != MLA_FP4_OUT_BF16 && out_dtype != MLA_FP4_OUT_F32) return fail(MLA_FP4_ERR_UNSUPPORTED, "bad out_dtype");
+  if (reinterpret_cast<uintptr_t>(partial_out) % 16) return fail(MLA_FP4_ERR_BAD_ARG, "partial_out must be 16-byte aligned");
+  cudaError_t e = mla::launch_merge_partials(partial_out, partial_lse, parts, rows, out, out_dtype, lse,
+                                             reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("merge launch: ") + cudaGetErrorString(e));
+  return MLA_FP4_OK;
+}
+
+int mla_fp4_dequant_e2m1_to_e4m3(const void* packed, void* out, int64_t n_bytes, void* stream) {
+  if (n_bytes < 0 || (n_bytes % 4)) return fail(MLA_FP4_ERR_BAD_ARG, "n_bytes must be a non-negative multiple of 4");
+  if (n_bytes == 0) return MLA_FP4_OK;
+  if (!packed || !out) return fail(MLA_FP4_ERR_BAD_ARG, "null pointer");
+  if (reinterpret_cast<uintptr_t>(packed) % 4 || reinterpret_cast<uintptr_t>(out) % 8)
+    return fail(MLA_FP4_ERR_BAD_ARG, "packed must be 4-byte and out 8-byte aligned");
+  cudaError_t e = mla::launch_dequant(packed, out, n_bytes, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("dequant launch: ") + cudaGetErrorString(e));
+  return MLA_FP4_OK;
+}
+
+}  // extern "C"

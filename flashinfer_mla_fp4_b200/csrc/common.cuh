@@ -1,0 +1,175 @@
+// Shared definitions of the FP4 MLA decode engine: constants, the work partition
+// (used identically by the host planner, the decode kernels and the combine kernel)
+// and small device helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/mla_fp4_b200.h"
+
+#define MLA_HD __host__ __device__ __forceinline__
+
+namespace mla {
+
+constexpr int kLatent = MLA_FP4_LATENT_DIM;        // 512
+constexpr int kRope = MLA_FP4_ROPE_DIM;            // 64
+constexpr int kQDim = kLatent + kRope;             // 576
+constexpr int kRowBytes = MLA_FP4_ROW_BYTES;       // 320
+constexpr int kTile = MLA_FP4_TILE_TOKENS;         // 128 KV tokens per tile
+constexpr int kGroupHeads = MLA_FP4_GROUP_HEADS;   // 64 query heads per CTA
+constexpr float kLog2e = 1.4426950408889634f;
+
+// Split-KV partial slot in the workspace: normalised O as f32 [512 dims][64 heads] followed by
+// the base-2 LSE of the 64 heads.
+constexpr size_t kSlotOFloats = size_t(kLatent) * kGroupHeads;
+constexpr size_t kSlotFloats = kSlotOFloats + kGroupHeads;
+constexpr size_t kSlotBytes = kSlotFloats * sizeof(float);
+
+// ----------------------------------------------------------------------------------------------
+// Work partition.
+//
+// A "virtual request" v = g * batch + b is request b seen by head group g (a group is 64 query
+// heads of one query position).  Request b has tiles_b = ceil(seq_len_b / 128) tiles.  All tiles
+// of all virtual requests, in v order, form a flat space of Tt = groups * sum_b tiles_b tiles.
+// CTA i of n owns the contiguous flat range [Tt*i/n, Tt*(i+1)/n).  A CTA therefore walks a list
+// of segments (v, tile_begin, tile_end); only its first and its last segment can cover a request
+// partially.  A partial segment writes a split-KV partial into workspace slot 2*i (first
+// segment of the CTA) or 2*i+1 (any later one); a segment that covers its request completely
+// writes the final output itself.  The combine kernel merges the slots of every split request.
+// ----------------------------------------------------------------------------------------------
+
+MLA_HD int tiles_of(int seq_len) { return seq_len > 0 ? (seq_len + kTile - 1) / kTile : 0; }
+
+MLA_HD int num_groups(int q_len, int num_heads) {
+  return q_len * ((num_heads + kGroupHeads - 1) / kGroupHeads);
+}
+
+MLA_HD int64_t cta_lo(int64_t Tt, int n, int i) { return (Tt * int64_t(i)) / n; }
+
+// CTA that owns flat tile f: the largest i with cta_lo(i) <= f.
+MLA_HD int cta_of_tile(int64_t Tt, int n, int64_t f) {
+  return int(((f + 1) * n + Tt - 1) / Tt) - 1;
+}
+
+MLA_HD int slot_of(int cta, bool first_segment_of_cta) { return 2 * cta + (first_segment_of_cta ? 0 : 1); }
+
+// Where request (virtual) v with flat start `start` and `tiles` tiles lands: the CTAs that touch it.
+struct Span {
+  int cta_first, cta_last;  // inclusive
+  bool split;               // more than one CTA
+};
+MLA_HD Span span_of(int64_t Tt, int n, int64_t start, int tiles) {
+  Span s;
+  s.cta_first = cta_of_tile(Tt, n, start);
+  s.cta_last = cta_of_tile(Tt, n, start + tiles - 1);
+  s.split = s.cta_last != s.cta_first;
+  return s;
+}
+// Slot written by CTA i for a split request whose flat start is `start`.
+MLA_HD int slot_in_span(int64_t Tt, int n, int i, int64_t start) {
+  return slot_of(i, cta_lo(Tt, n, i) >= start);
+}
+
+// One segment of a CTA's walk.
+struct Segment {
+  int b, g;                 // request, head group
+  int tile_begin, tile_end; // tiles of the request, [begin, end)
+  int seq_len;
+  int slot;                 // -1: covers the whole request (writes the final output)
+};
+
+// Sequential walker over the segments of one CTA.  `start_*` describe the position of the CTA's
+// first flat tile and are found once per CTA (find_start on the device, a plain loop on the host).
+struct Walker {
+  const int32_t* seq_lens;
+  int batch, groups;
+  int64_t f, hi;   // current flat tile, end of the CTA's range
+  int b, g, t;     // current request, group, tile inside the request
+  bool first;      // next segment is the first of this CTA
+  int cta;
+
+  MLA_HD bool next(Segment& s) {
+    while (f < hi) {
+      if (g >= groups) return false;
+      int sl = seq_lens[b];
+      int tb = tiles_of(sl);
+      if (t >= tb) {
+        t = 0;
+        if (++b == batch) { b = 0; ++g; }
+        continue;
+      }
+      int64_t room = hi - f;
+      int end = (tb - t) <= room ? tb : t + int(room);
+      s.b = b; s.g = g; s.tile_begin = t; s.tile_end = end; s.seq_len = sl;
+      s.slot = (t == 0 && end == tb) ? -1 : slot_of(cta, first);
+      f += end - t;
+      t = end;
+      first = false;
+      return true;
+    }
+    return false;
+  }
+};
+
+// Decoded head group: which query position and which first head it covers.
+MLA_HD void group_coords(int g, int num_heads, int& qpos, int& head0) {
+  int per = (num_heads + kGroupHeads - 1) / kGroupHeads;
+  qpos = g / per;
+  head0 = (g % per) * kGroupHeads;
+}
+
+#ifdef __CUDACC__
+// Warp-cooperative: total tile count of the batch. All 32 lanes must call; all get the result.
+__device__ __forceinline__ int64_t warp_total_tiles(const int32_t* seq_lens, int batch) {
+  int lane = threadIdx.x & 31;
+  int64_t acc = 0;
+  for (int i = lane; i < batch; i += 32) acc += tiles_of(seq_lens[i]);
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  return acc;
+}
+
+// Warp-cooperative: locate flat tile r (0 <= r < T, within one group) -> request b and tile t.
+__device__ __forceinline__ void warp_locate(const int32_t* seq_lens, int batch, int64_t r, int& b_out, int& t_out) {
+  int lane = threadIdx.x & 31;
+  int64_t run = 0;
+  b_out = batch; t_out = 0;
+  for (int base = 0; base < batch; base += 32) {
+    int i = base + lane;
+    int64_t v = i < batch ? tiles_of(seq_lens[i]) : 0;
+    int64_t inc = v;
+    for (int o = 1; o < 32; o <<= 1) {
+      int64_t u = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += u;
+    }
+    int64_t tot = __shfl_sync(0xffffffffu, inc, 31);
+    if (r < run + tot) {
+      unsigned m = __ballot_sync(0xffffffffu, run + inc > r);
+      int l = __ffs(m) - 1;
+      int64_t exc = __shfl_sync(0xffffffffu, inc - v, l);
+      b_out = base + l;
+      t_out = int(r - (run + exc));
+      return;
+    }
+    run += tot;
+  }
+}
+
+// Initialise a walker for CTA `cta` of `n`. Warp-cooperative (all 32 lanes call, all get it).
+__device__ __forceinline__ Walker make_walker(const int32_t* seq_lens, int batch, int groups, int cta, int n) {
+  Walker w;
+  w.seq_lens = seq_lens; w.batch = batch; w.groups = groups; w.cta = cta; w.first = true;
+  int64_t T = warp_total_tiles(seq_lens, batch);
+  int64_t Tt = T * groups;
+  w.f = cta_lo(Tt, n, cta);
+  w.hi = cta_lo(Tt, n, cta + 1);
+  w.b = 0; w.g = groups; w.t = 0;
+  if (T > 0 && w.f < w.hi) {
+    w.g = int(w.f / T);
+    warp_locate(seq_lens, batch, w.f % T, w.b, w.t);
+  }
+  return w;
+}
+#endif  // __CUDACC__
+
+}  // namespace mla

@@ -1,0 +1,43 @@
+// Kernel parameter blocks and launcher prototypes shared by the translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mla {
+
+struct DecodeParams {
+  const void* q;
+  int64_t q_stride_batch, q_stride_qpos, q_stride_head;
+  const void* kv_cache;
+  const float* kv_cache_sf;
+  const int32_t* block_tables;
+  int64_t block_table_stride;
+  const int32_t* seq_lens;
+  void* out;
+  float* lse;
+  void* workspace;
+  int32_t* status;
+  int32_t batch, q_len, num_heads, page_size, groups;
+  int64_t num_pages;
+  float softmax_scale, output_scale;
+  int32_t out_dtype;
+  int32_t pdl;
+};
+
+struct CombineParams {
+  const int32_t* seq_lens;
+  const void* workspace;
+  void* out;
+  float* lse;
+  int32_t batch, q_len, num_heads, groups, num_ctas, out_dtype, pdl;
+};
+
+cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);
+cudaError_t launch_merge_partials(const float* po, const float* pl, int parts, int64_t rows, void* out,
+                                  int out_dtype, float* lse, cudaStream_t stream);
+cudaError_t launch_fp32_check(const DecodeParams& p, int num_ctas, cudaStream_t stream);
+cudaError_t launch_dequant(const void* in, void* out, int64_t n_bytes, cudaStream_t stream);
+// tcgen05 decode kernel (decode_sm100.cu). Returns cudaErrorNotSupported-like codes through `err`.
+cudaError_t launch_decode_sm100(const DecodeParams& p, int num_ctas, cudaStream_t stream, const char** err);
+
+}  // namespace mla

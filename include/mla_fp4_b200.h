@@ -1,0 +1,132 @@
+/*
+ * C ABI of the B200 FP4 MLA decode engine (libmla_fp4_b200.so).
+ *
+ * Every entry point is extern "C", takes plain pointers and sizes, returns an
+ * int status (0 = OK), never throws, never takes ownership of a buffer, and
+ * -- unless its comment says otherwise -- neither allocates device memory nor
+ * synchronises the stream.  All device buffers are caller-owned.
+ *
+ * The reference project has no native code; its kernel is a CuTe-DSL callable
+ * produced by JIT compilation.  Each declaration below names the reference
+ * interface it stands in for (path inside the reference project : line).
+ */
+#ifndef MLA_FP4_B200_H_
+#define MLA_FP4_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MLA_FP4_ABI_VERSION 1
+
+/* status codes */
+#define MLA_FP4_OK 0
+#define MLA_FP4_ERR_BAD_ARG 1            /* null pointer, bad shape/stride/alignment          */
+#define MLA_FP4_ERR_UNSUPPORTED 2        /* page size / head count / dtype outside the build  */
+#define MLA_FP4_ERR_WORKSPACE_TOO_SMALL 3
+#define MLA_FP4_ERR_CUDA 4               /* a CUDA runtime/driver call failed                  */
+#define MLA_FP4_ERR_DEVICE_TIMEOUT 5     /* a bounded device-side wait expired (status word)   */
+#define MLA_FP4_ERR_NOT_BUILT 6          /* library built without the sm_100a kernels          */
+
+/* fixed problem constants (reference wrappers/batch_mla_fp4.py:206-221) */
+#define MLA_FP4_LATENT_DIM 512
+#define MLA_FP4_ROPE_DIM 64
+#define MLA_FP4_ROW_BYTES 320
+#define MLA_FP4_TILE_TOKENS 128          /* KV tokens per work tile                            */
+#define MLA_FP4_GROUP_HEADS 64           /* query heads handled by one CTA                     */
+
+/* kernel selection for mla_fp4_decode */
+#define MLA_FP4_KERNEL_TCGEN05 0         /* the product path: TMA + tcgen05/TMEM               */
+#define MLA_FP4_KERNEL_FP32_CHECK 1      /* plain-FP32 CUDA-core kernel, a test cross-check    */
+
+/* output element types (reference: out dtype bf16 default, wrappers/batch_mla_fp4.py:228) */
+#define MLA_FP4_OUT_BF16 0
+#define MLA_FP4_OUT_F32 1
+
+typedef struct MlaFp4DecodeArgs {
+  /* query, E4M3 bytes, logical shape [batch, q_len, num_heads, 576], unit last stride;
+     strides in bytes(=elements).  Replaces q_latent/q_rope of the compiled callable
+     (wrappers/batch_mla_fp4.py:381-383, :441-443). */
+  const void* q;
+  int64_t q_stride_batch, q_stride_qpos, q_stride_head;
+  /* cache rows, uint8 [num_pages, page_size, 320] contiguous, 32-byte aligned
+     (wrappers/batch_mla_fp4.py:384-388). */
+  const void* kv_cache;
+  /* per-token FP32 scale [num_pages, page_size, 1] contiguous (wrappers/batch_mla_fp4.py:388). */
+  const float* kv_cache_sf;
+  /* physical page ids, int32 [batch, block_table_stride] row-major (wrappers/batch_mla_fp4.py:446). */
+  const int32_t* block_tables;
+  int64_t block_table_stride;
+  /* int32 [batch] attended tokens per request (wrappers/batch_mla_fp4.py:438-440, :451). */
+  const int32_t* seq_lens;
+  /* output [batch, q_len, num_heads, 512] contiguous, element type out_dtype (wrappers/...:422-432). */
+  void* out;
+  /* optional base-2 log-sum-exp [batch, q_len, num_heads] f32; may be NULL.  The reference
+     computes it (wrappers/batch_mla_fp4.py:433-437) but does not return it. */
+  float* lse;
+  /* caller-owned scratch for split-KV partials (the reference slices the wrapper's
+     int8 workspace buffer, wrappers/batch_mla_fp4.py:413-420). */
+  void* workspace;
+  size_t workspace_bytes;
+  /* int32[8] device status words, zeroed by the caller before first use; word 0 becomes
+     non-zero when a bounded device-side wait expired.  May be NULL. */
+  int32_t* status;
+  int32_t batch, q_len, num_heads, page_size;
+  int64_t num_pages;
+  float softmax_scale, output_scale;
+  int32_t out_dtype;   /* MLA_FP4_OUT_*    */
+  int32_t kernel;      /* MLA_FP4_KERNEL_* */
+  int32_t num_ctas;    /* CTAs of the persistent decode grid; 0 = one per SM of the current device */
+  int32_t enable_pdl;  /* programmatic dependent launch between decode and combine (0/1) */
+  void* stream;        /* cudaStream_t */
+} MlaFp4DecodeArgs;
+
+/* ABI version of the loaded library (== MLA_FP4_ABI_VERSION of the header it was built from). */
+int mla_fp4_abi_version(void);
+
+/* Message of the last non-zero status returned on the calling thread. */
+const char* mla_fp4_last_error(void);
+
+/* Scratch bytes mla_fp4_decode needs for (batch, q_len, num_heads) on a grid of num_ctas CTAs
+   (0 = SM count of the current device).  Stands in for
+   flashinfer cute_dsl/attention/scheduler/mla_persistent.py:285-291 (mla_get_workspace_size),
+   reached from wrappers/batch_mla_fp4.py:390-396.  Host only. */
+int mla_fp4_workspace_bytes(int32_t batch, int32_t q_len, int32_t num_heads, int32_t num_ctas,
+                            size_t* bytes_out);
+
+/* Host copy of the work partition the decode kernel derives on the device: request b, head
+   group g and tile range of every segment of every CTA.  seq_lens is a HOST array.  Arrays
+   hold up to max_segments entries; *num_segments receives the count (the required count when
+   it exceeds max_segments).  Stands in for the reference's split heuristic + static tile
+   scheduler (flashinfer cute_dsl/attention/scheduler/mla_persistent.py:137-282).  Host only. */
+int mla_fp4_plan_partition(const int32_t* seq_lens_host, int32_t batch, int32_t q_len,
+                           int32_t num_heads, int32_t num_ctas, int32_t max_segments,
+                           int32_t* seg_cta, int32_t* seg_request, int32_t* seg_group,
+                           int32_t* seg_tile_begin, int32_t* seg_tile_end, int32_t* seg_slot,
+                           int32_t* num_segments);
+
+/* One decode step: launches the decode kernel and the split-KV combine kernel on args->stream.
+   Stands in for the compiled callable invoked at wrappers/batch_mla_fp4.py:441-457
+   (mla_decode_fp4.py:60-305: split_kv_kernel + reduction_kernel). */
+int mla_fp4_decode(const MlaFp4DecodeArgs* args);
+
+/* Merge `parts` normalised partial outputs with base-2 LSEs (decode context parallel):
+   partial_out f32 [parts, rows, 512], partial_lse f32 [parts, rows] ->
+   out [rows, 512] (out_dtype) and optional lse [rows].  Same arithmetic as the split-KV
+   reduction (flashinfer cute_dsl/attention/mla_decode.py:614-710); the reference has no
+   multi-GPU path of its own. */
+int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, int32_t parts,
+                           int64_t rows, void* out, int32_t out_dtype, float* lse, void* stream);
+
+/* Bit-exact E2M1 nibble -> E4M3 byte dequantisation of `n_bytes` packed bytes on the device
+   (out holds 2*n_bytes E4M3 bytes, low nibble first), using the same device routine as the
+   decode kernel.  Pins the table of tests/test_cute_dsl_mla_fp4.py:80-84. */
+int mla_fp4_dequant_e2m1_to_e4m3(const void* packed, void* out, int64_t n_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLA_FP4_B200_H_ */

@@ -1,0 +1,199 @@
+"""GPU parity tests: the CUDA path (through the wrapper and the C ABI) against the CPU oracle.
+
+Tolerance (stated by the task): per-head cosine >= 0.9999 and max-abs error <= 2e-2 * RMS(out)
+against the FP32 dequantise-then-attend oracle; the E2M1 -> E4M3 table bit-exact.  The
+reference's own test tolerance (|diff| <= 1.5e-3, tests/test_cute_dsl_mla_fp4.py:227-232) is
+applied on the reference's generator grid.
+"""
+import ctypes
+
+import pytest
+import torch
+
+from oracle import mla_fp4_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+KERNELS = {"tcgen05": 0, "fp32_check": 1}
+
+
+def _dev():
+    if not torch.cuda.is_available():
+        pytest.fail("a CUDA device is required for -m gpu tests")
+    return torch.device("cuda:0")
+
+
+def run_case(case, kernel="tcgen05", out_dtype=torch.bfloat16, return_lse=True, output_scale=1.0, workspace=None,
+             four_d=False, out=None):
+    from flashinfer_mla_fp4_b200 import BatchMLADecodeCuteDSLFP4Wrapper
+
+    ws = workspace if workspace is not None else torch.empty(64 << 20, dtype=torch.int8, device=case.q.device)
+    w = BatchMLADecodeCuteDSLFP4Wrapper(ws)
+    w.plan(num_heads=case.num_heads, page_size=case.page_size, out_dtype=out_dtype, is_var_seq=True)
+    w._kernel = KERNELS[kernel]
+    cache, sf = (case.kv_cache.unsqueeze(1), case.kv_cache_sf.unsqueeze(1)) if four_d else (case.kv_cache, case.kv_cache_sf)
+    res = w.run(case.q, cache, case.block_tables, case.seq_lens, case.max_seq_len, case.softmax_scale,
+                output_scale=output_scale, out=out, kv_cache_sf=sf, return_lse=return_lse)
+    torch.cuda.synchronize()
+    w.check_device_status()
+    return res
+
+
+def check_case(case, kernel, **kw):
+    out, lse = run_case(case, kernel, **kw)
+    ref, ref_lse = O.mla_decode(case.q, case.kv_cache, case.kv_cache_sf, case.block_tables, case.seq_lens,
+                                case.softmax_scale, kw.get("output_scale", 1.0))
+    m = O.assert_parity(out, ref, f"{case.name}/{kernel}")
+    live = torch.isfinite(ref_lse)
+    torch.testing.assert_close(lse.cpu()[live], ref_lse[live], atol=2e-3, rtol=1e-4)
+    assert (lse.cpu()[~live] == float("-inf")).all()
+    return m
+
+
+def test_dequant_table_bit_exact():
+    from flashinfer_mla_fp4_b200 import _cabi
+
+    dev = _dev()
+    # every byte value (all 256 nibble pairs), in every position of a word
+    packed = torch.arange(256, dtype=torch.uint8).repeat(4).reshape(4, 256).t().contiguous().reshape(-1).to(dev)
+    out = torch.empty(packed.numel() * 2, dtype=torch.uint8, device=dev)
+    _cabi.check(_cabi.lib.mla_fp4_dequant_e2m1_to_e4m3(packed.data_ptr(), out.data_ptr(), packed.numel(),
+                                                      ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    tab = torch.from_numpy(O.e2m1_to_e4m3_byte_table())
+    p = packed.cpu().long()
+    expect = torch.stack((tab[p & 0xF], tab[p >> 4]), dim=-1).reshape(-1)
+    assert torch.equal(out.cpu(), expect)
+
+
+@pytest.mark.parametrize("kernel", ["fp32_check", "tcgen05"])
+@pytest.mark.parametrize("config", ["small", "uniform"])
+def test_named_configs(config, kernel):
+    from flashinfer_mla_fp4_b200 import synth
+
+    check_case(synth.config_case(config, device=_dev()), kernel)
+
+
+@pytest.mark.parametrize("kernel", ["fp32_check", "tcgen05"])
+@pytest.mark.parametrize("seq_len", [1, 63, 64, 65, 127, 128, 129, 300, 1000])
+def test_tail_lengths(seq_len, kernel):
+    from flashinfer_mla_fp4_b200 import synth
+
+    check_case(synth.build_case("tail", [seq_len, max(1, seq_len - 1)], 16, 64, seed=seq_len, device=_dev()), kernel)
+
+
+@pytest.mark.parametrize("kernel", ["fp32_check", "tcgen05"])
+@pytest.mark.parametrize("heads,page_size", [(16, 16), (64, 32), (128, 128), (128, 8), (40, 64)])
+def test_heads_and_page_sizes(heads, page_size, kernel):
+    from flashinfer_mla_fp4_b200 import synth
+
+    check_case(synth.build_case("hp", [700, 129, 64, 2500], heads, page_size, seed=heads + page_size, device=_dev()), kernel)
+
+
+@pytest.mark.parametrize("kernel", ["fp32_check", "tcgen05"])
+def test_ragged_batch_with_empty_requests(kernel):
+    from flashinfer_mla_fp4_b200 import synth
+
+    lens = [0, 5, 4096, 0, 130, 77, 9000, 1]
+    case = synth.build_case("ragged", [max(n, 1) for n in lens], 64, 64, seed=11, device=_dev())
+    case.seq_lens = torch.tensor(lens, dtype=torch.int32, device=case.q.device)
+    case.seq_lens_host = lens
+    check_case(case, kernel)
+
+
+@pytest.mark.parametrize("kernel", ["fp32_check", "tcgen05"])
+def test_q_len_two_and_output_scale_and_f32_out(kernel):
+    from flashinfer_mla_fp4_b200 import synth
+
+    case = synth.build_case("spec", [3000, 1500], 128, 64, q_len=2, seed=12, device=_dev())
+    check_case(case, kernel, output_scale=0.37, out_dtype=torch.float32)
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05"])
+def test_heavy_tailed_latents_and_wide_scales(kernel):
+    from flashinfer_mla_fp4_b200 import synth
+
+    case = synth.build_case("t3", [2000, 333, 4100], 64, 64, seed=13, device=_dev(), latent_dist="student_t3")
+    check_case(case, kernel)
+    # scales spread over many binades
+    g = torch.Generator(device=case.q.device).manual_seed(1)
+    case.kv_cache_sf.mul_(torch.exp2(torch.randint(-12, 13, case.kv_cache_sf.shape, generator=g, device=case.q.device).float()))
+    check_case(case, kernel)
+
+
+@pytest.mark.parametrize("batch_size", [1, 4])
+@pytest.mark.parametrize("seq_len", [128, 512, 2048])
+@pytest.mark.parametrize("page_size", [32, 64, 128])
+@pytest.mark.parametrize("is_var_seq", [False, True])
+def test_reference_grid(batch_size, seq_len, page_size, is_var_seq):
+    """The reference's 36-case accuracy grid restated (tests/test_cute_dsl_mla_fp4.py:96-232): seed 42,
+    q = randn*0.1 -> E4M3, source = randn f16, alternating 0.5/1.0 scales, identity block table,
+    H = 128, var-seq lengths max(1, S-1-17i) with 4-D cache/scale, |diff| <= 1.5e-3 (against the
+    oracle here, since the reference compares against a second GPU kernel on the same data)."""
+    from flashinfer_mla_fp4_b200 import synth
+
+    dev = _dev()
+    torch.manual_seed(42)
+    H = 128
+    pages_per_batch = (seq_len + page_size - 1) // page_size
+    total_pages = batch_size * pages_per_batch + 2
+    q = (torch.randn(batch_size, 1, H, 576, dtype=torch.float16, device=dev) * 0.1).to(torch.float8_e4m3fn)
+    source = torch.randn(total_pages, page_size, 576, dtype=torch.float16, device=dev)
+    fp4_cache, token_scale, _ = O.make_reference_style_cache(source)
+    assert fp4_cache.nbytes + token_scale.nbytes == total_pages * page_size * 324
+    block_tables = torch.arange(batch_size * pages_per_batch, dtype=torch.int32, device=dev).view(batch_size, -1)
+    lens = [max(1, seq_len - 1 - i * 17) for i in range(batch_size)] if is_var_seq else [seq_len] * batch_size
+    case = synth.DecodeCase("grid", q, fp4_cache, token_scale, block_tables,
+                            torch.tensor(lens, dtype=torch.int32, device=dev), page_size, H, 1,
+                            1.0 / 512 ** 0.5, 42, lens)
+    out = torch.empty(batch_size, 1, H, 512, dtype=torch.bfloat16, device=dev)
+    res, _ = run_case(case, "tcgen05", four_d=is_var_seq, out=out)
+    assert res.data_ptr() == out.data_ptr() and res.shape == (batch_size, 1, H, 512) and res.dtype == torch.bfloat16
+    ref, _ = O.mla_decode(q, fp4_cache, token_scale, block_tables, case.seq_lens, case.softmax_scale)
+    assert torch.isfinite(res).all()
+    torch.testing.assert_close(res.float().cpu(), ref, atol=1.5e-3, rtol=0)
+
+
+def test_cuda_graph_capture_and_replay():
+    from flashinfer_mla_fp4_b200 import BatchMLADecodeCuteDSLFP4Wrapper, synth
+
+    case = synth.config_case("uniform", device=_dev(), scale=0.25)
+    w = BatchMLADecodeCuteDSLFP4Wrapper(torch.empty(64 << 20, dtype=torch.int8, device=case.q.device))
+    w.plan(num_heads=case.num_heads, page_size=case.page_size)
+    out = torch.zeros(case.batch, 1, case.num_heads, 512, dtype=torch.bfloat16, device=case.q.device)
+    args = (case.q, case.kv_cache, case.block_tables, case.seq_lens, case.max_seq_len, case.softmax_scale)
+    w.run(*args, out=out, kv_cache_sf=case.kv_cache_sf)
+    torch.cuda.synchronize()
+    eager = out.clone()
+    out.zero_()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        w.run(*args, out=out, kv_cache_sf=case.kv_cache_sf)
+    g.replay()
+    g.replay()
+    torch.cuda.synchronize()
+    w.check_device_status()
+    assert torch.equal(out, eager)
+
+
+def test_merge_partials_matches_oracle():
+    from flashinfer_mla_fp4_b200 import _cabi
+
+    dev = _dev()
+    g = torch.Generator().manual_seed(9)
+    parts, rows = 5, 37
+    po = torch.randn(parts, rows, 512, generator=g)
+    pl = torch.randn(parts, rows, generator=g) * 4
+    pl[2] = float("-inf")
+    pl[:, 3] = float("-inf")
+    ref, ref_lse = O.merge_partials(list(po), list(pl))
+    out = torch.empty(rows, 512, dtype=torch.float32, device=dev)
+    lse = torch.empty(rows, dtype=torch.float32, device=dev)
+    _cabi.check(_cabi.lib.mla_fp4_merge_partials(po.to(dev).data_ptr(), pl.to(dev).data_ptr(), parts, rows,
+                                                out.data_ptr(), _cabi.OUT_F32, lse.data_ptr(),
+                                                ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.cpu(), ref, atol=1e-5, rtol=1e-5)
+    live = torch.isfinite(ref_lse)
+    torch.testing.assert_close(lse.cpu()[live], ref_lse[live], atol=1e-5, rtol=1e-5)
+    assert (lse.cpu()[~live] == float("-inf")).all()

@@ -1,0 +1,170 @@
+"""Host logic without a GPU: the library loads and exports its ABI, the work partition is a
+partition, the package quantiser equals the oracle's, and the wrapper validates like the reference."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+from oracle import mla_fp4_oracle as O
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_library_exports_every_declared_symbol():
+    from flashinfer_mla_fp4_b200 import _cabi
+
+    header = (ROOT / "include" / "mla_fp4_b200.h").read_text()
+    declared = set(re.findall(r"^\s*(?:const\s+)?(?:int|char\s*\*|const char\*)\s+(mla_fp4_\w+)\s*\(", header, re.M))
+    assert declared, "no declarations parsed"
+    lib = ctypes.CDLL(str(_cabi.LIB_PATH))
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+    assert set(_cabi.EXPORTS) == declared
+    assert lib.mla_fp4_abi_version() == 1
+
+
+def test_abi_rejects_bad_arguments_without_a_gpu():
+    from flashinfer_mla_fp4_b200 import _cabi
+
+    assert _cabi.lib.mla_fp4_decode(None) == _cabi.ERR_BAD_ARG
+    assert "null" in _cabi.last_error()
+    n = ctypes.c_size_t(0)
+    assert _cabi.lib.mla_fp4_workspace_bytes(8, 1, 64, 148, ctypes.byref(n)) == 0
+    assert n.value == 2 * 148 * (512 * 64 + 64) * 4
+    assert _cabi.lib.mla_fp4_workspace_bytes(8, 0, 64, 148, ctypes.byref(n)) == _cabi.ERR_BAD_ARG
+    with pytest.raises(ValueError):
+        _cabi.check(_cabi.ERR_WORKSPACE_TOO_SMALL)
+
+
+@pytest.mark.parametrize(
+    "seq_lens,q_len,heads,ctas",
+    [
+        ([32768] * 8, 1, 64, 148),
+        ([4096] * 4, 1, 64, 148),
+        ([256, 256], 1, 16, 148),
+        ([131072, 131072], 2, 128, 148),
+        ([1, 0, 129, 128, 127, 5000, 0, 3], 1, 128, 7),
+        ([0, 0], 1, 64, 4),
+        ([77], 1, 64, 1),
+        (list(range(1, 400, 7)), 1, 64, 148),
+    ],
+)
+def test_partition_is_a_partition(seq_lens, q_len, heads, ctas):
+    from flashinfer_mla_fp4_b200 import planner
+
+    segs = planner.plan_partition(seq_lens, q_len, heads, ctas)
+    groups = planner.num_groups(q_len, heads)
+    covered = {}
+    per_cta = {}
+    for s in segs:
+        assert 0 <= s.tile_begin < s.tile_end <= planner.tiles_of(seq_lens[s.request])
+        for t in range(s.tile_begin, s.tile_end):
+            key = (s.group, s.request, t)
+            assert key not in covered, "tile covered twice"
+            covered[key] = s.cta
+        per_cta.setdefault(s.cta, []).append(s)
+        whole = s.tile_begin == 0 and s.tile_end == planner.tiles_of(seq_lens[s.request])
+        assert (s.slot == -1) == whole
+    total = groups * sum(planner.tiles_of(n) for n in seq_lens)
+    assert len(covered) == total
+    # balance: CTA loads differ by at most one tile
+    loads = [sum(s.tile_end - s.tile_begin for s in per_cta.get(i, [])) for i in range(ctas)]
+    assert max(loads) - min(loads) <= 1
+    # partial slots: unique, at most two per CTA, only at the ends of a CTA's walk
+    slots = [s.slot for s in segs if s.slot >= 0]
+    assert len(slots) == len(set(slots))
+    for i, ss in per_cta.items():
+        partial = [k for k, s in enumerate(ss) if s.slot >= 0]
+        assert all(k in (0, len(ss) - 1) for k in partial)
+        for k in partial:
+            assert ss[k].slot == 2 * i + (0 if k == 0 else 1)
+    assert planner.workspace_bytes(len(seq_lens), q_len, heads, ctas) >= (max(slots) + 1 if slots else 0) * 131328
+
+
+def test_package_quantiser_is_bit_identical_to_the_oracle():
+    from flashinfer_mla_fp4_b200.kvcache import quantize_tokens
+
+    g = torch.Generator().manual_seed(3)
+    lat = torch.randn(5, 16, 512, generator=g) * 3
+    rope = torch.randn(5, 16, 64, generator=g)
+    lat[0, 0] = 0
+    rows, sf = quantize_tokens(lat, rope)
+    ref_sf = O.amax_scale(lat)
+    assert torch.equal(sf, ref_sf)
+    assert torch.equal(rows, O.pack_cache(lat, rope, ref_sf))
+    # round trip: dequantised values are within half a quantisation step of the input
+    deq, _ = O.dequantize_cache(rows, sf)
+    assert ((deq - lat).abs() <= sf * 1.0 + 1e-6).all()
+
+
+def _planned_cpu_wrapper(monkeypatch, **kw):
+    import flashinfer_mla_fp4_b200.wrapper as W
+
+    monkeypatch.setattr(W, "_require_sm100", lambda device: None)
+
+    class _Props:
+        multi_processor_count = 148
+
+    monkeypatch.setattr(torch.cuda, "get_device_properties", lambda d: _Props())
+    w = W.BatchMLADecodeCuteDSLFP4Wrapper(torch.empty(64 << 20, dtype=torch.int8))
+    args = dict(num_heads=16, page_size=64)
+    args.update(kw)
+    w.plan(**args)
+    return w
+
+
+def test_wrapper_plan_validation(monkeypatch):
+    import flashinfer_mla_fp4_b200 as pkg
+
+    with pytest.raises(AssertionError):
+        pkg.BatchMLADecodeCuteDSLFP4Wrapper(torch.empty(16, dtype=torch.uint8))
+    w = pkg.BatchMLADecodeCuteDSLFP4Wrapper(torch.empty(16, dtype=torch.int8))
+    with pytest.raises(RuntimeError, match="plan"):
+        w.run(None, None, None, None, 1, 1.0)
+    for bad in (dict(kv_lora_rank=256), dict(qk_rope_head_dim=32), dict(q_dtype=torch.bfloat16),
+                dict(kv_dtype=torch.float8_e4m3fn), dict(page_size=1), dict(num_heads=129, page_size=64),
+                dict(out_dtype=torch.float16, page_size=64), dict(variant=object(), page_size=64)):
+        with pytest.raises(ValueError):
+            w.plan(**bad)
+    # a CPU workspace cannot be planned: the kernels are sm_100a only
+    with pytest.raises(RuntimeError, match="CUDA"):
+        w.plan(num_heads=16, page_size=64)
+    _planned_cpu_wrapper(monkeypatch)
+
+
+def test_wrapper_run_validation(monkeypatch):
+    w = _planned_cpu_wrapper(monkeypatch)
+    from flashinfer_mla_fp4_b200 import synth
+
+    c = synth.config_case("small")
+    ok = dict(q=c.q, kv_cache=c.kv_cache, block_tables=c.block_tables, seq_lens=c.seq_lens, max_seq_len=256,
+              softmax_scale=c.softmax_scale, kv_cache_sf=c.kv_cache_sf)
+
+    def bad(**kw):
+        a = dict(ok)
+        a.update(kw)
+        with pytest.raises(ValueError):
+            w.run(**a)
+
+    bad(q=c.q[0])
+    bad(q=c.q[..., :512])
+    bad(q=c.q.float())
+    bad(kv_cache=c.kv_cache.to(torch.int8))
+    bad(kv_cache_sf=None)
+    bad(kv_cache_sf=c.kv_cache_sf.double())
+    bad(kv_cache=c.kv_cache[:, :32])
+    bad(kv_cache=c.kv_cache[..., :256])
+    bad(kv_cache=c.kv_cache.unsqueeze(1).expand(-1, 2, -1, -1))
+    bad(kv_cache_sf=c.kv_cache_sf[:, :32])
+    bad(kv_cache=c.kv_cache.transpose(0, 1).contiguous().transpose(0, 1))
+    bad(max_seq_len=0)
+    bad(out=torch.empty(2, 1, 16, 512, dtype=torch.float16))
+    bad(block_tables=c.block_tables.long())
+    # the workspace bound is checked with the reference's message
+    import flashinfer_mla_fp4_b200.wrapper as W
+    small = W.BatchMLADecodeCuteDSLFP4Wrapper(torch.empty(1024, dtype=torch.int8))
+    small.__dict__.update({k: v for k, v in w.__dict__.items() if k != "_workspace_buffer"})
+    with pytest.raises(ValueError, match="are required"):
+        small.run(**ok)
