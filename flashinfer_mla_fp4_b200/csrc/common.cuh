@@ -52,6 +52,9 @@ MLA_HD int cta_of_tile(int64_t Tt, int n, int64_t f) {
   return int(((f + 1) * n + Tt - 1) / Tt) - 1;
 }
 
+// A CTA whose flat range is empty (more CTAs than tiles) has no segment and writes no slot.
+MLA_HD bool cta_is_empty(int64_t Tt, int n, int i) { return cta_lo(Tt, n, i) == cta_lo(Tt, n, i + 1); }
+
 MLA_HD int slot_of(int cta, bool first_segment_of_cta) { return 2 * cta + (first_segment_of_cta ? 0 : 1); }
 
 // Where request (virtual) v with flat start `start` and `tiles` tiles lands: the CTAs that touch it.

@@ -27,7 +27,7 @@ __device__ __forceinline__ void store_out(void* out, int out_dtype, size_t idx, 
 
 // ------------------------------------------------------------------------------------------
 // Split-KV combine.  grid = (groups * batch), block = 256.  Thread t owns dims t and t+256 of
-// all 64 heads?  No: it loops (head, dim) pairs so that global stores are coalesced along dims.
+// all 64 heads, so slot reads are 256-byte rows and output stores are coalesced along dims.
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
 #if __CUDA_ARCH__ >= 900
@@ -77,11 +77,13 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
   if (tid < kGroupHeads) {
     float m = -INFINITY;
     for (int i = sp.cta_first; i <= sp.cta_last; ++i) {
+      if (cta_is_empty(Tt, p.num_ctas, i)) continue;
       int slot = slot_in_span(Tt, p.num_ctas, i, start);
       m = fmaxf(m, ws[size_t(slot) * kSlotFloats + kSlotOFloats + tid]);
     }
     float dsum = 0.f;
     for (int i = sp.cta_first; i <= sp.cta_last; ++i) {
+      if (cta_is_empty(Tt, p.num_ctas, i)) continue;
       int slot = slot_in_span(Tt, p.num_ctas, i, start);
       float l = ws[size_t(slot) * kSlotFloats + kSlotOFloats + tid];
       dsum += (l == -INFINITY) ? 0.f : exp2f(l - m);
@@ -97,6 +99,7 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
 #pragma unroll
   for (int h = 0; h < kGroupHeads; ++h) { acc0[h] = 0.f; acc1[h] = 0.f; }
   for (int i = sp.cta_first; i <= sp.cta_last; ++i) {
+    if (cta_is_empty(Tt, p.num_ctas, i)) continue;  // block-uniform: a CTA without tiles wrote no slot
     int slot = slot_in_span(Tt, p.num_ctas, i, start);
     const float* so = ws + size_t(slot) * kSlotFloats;
     __syncthreads();
