@@ -49,6 +49,7 @@ class DecodeArgs(C.Structure):
         ("kernel", C.c_int32),
         ("num_ctas", C.c_int32),
         ("enable_pdl", C.c_int32),
+        ("phase_mask", C.c_int32),
         ("stream", C.c_void_p),
     ]
 
@@ -81,8 +82,8 @@ def _load() -> C.CDLL:
     lib.mla_fp4_plan_partition.restype = C.c_int
     lib.mla_fp4_decode.argtypes = [C.POINTER(DecodeArgs)]
     lib.mla_fp4_decode.restype = C.c_int
-    lib.mla_fp4_merge_partials.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_int32,
-                                           C.c_void_p, C.c_void_p]
+    lib.mla_fp4_merge_partials.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
+                                           C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]
     lib.mla_fp4_merge_partials.restype = C.c_int
     lib.mla_fp4_dequant_e2m1_to_e4m3.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
     lib.mla_fp4_dequant_e2m1_to_e4m3.restype = C.c_int

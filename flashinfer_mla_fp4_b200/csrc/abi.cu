@@ -135,8 +135,11 @@ int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
   p.out_dtype = a->out_dtype; p.pdl = a->enable_pdl ? 1 : 0;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
 
-  cudaError_t e;
-  if (a->kernel == MLA_FP4_KERNEL_FP32_CHECK) {
+  cudaError_t e = cudaSuccess;
+  const bool do_decode = a->phase_mask == 0 || (a->phase_mask & 1);
+  const bool do_combine = a->phase_mask == 0 || (a->phase_mask & 2);
+  if (!do_decode) {
+  } else if (a->kernel == MLA_FP4_KERNEL_FP32_CHECK) {
     p.pdl = 0;
     e = mla::launch_fp32_check(p, num_ctas, stream);
   } else if (a->kernel == MLA_FP4_KERNEL_TCGEN05) {
@@ -148,23 +151,29 @@ int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
   }
   if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("decode launch: ") + cudaGetErrorString(e));
 
+  if (!do_combine) return MLA_FP4_OK;
   mla::CombineParams c;
   c.seq_lens = a->seq_lens; c.workspace = a->workspace; c.out = a->out; c.lse = a->lse;
   c.batch = a->batch; c.q_len = a->q_len; c.num_heads = a->num_heads; c.groups = p.groups;
-  c.num_ctas = num_ctas; c.out_dtype = a->out_dtype; c.pdl = p.pdl;
+  c.num_ctas = num_ctas; c.out_dtype = a->out_dtype; c.pdl = (p.pdl && do_decode) ? 1 : 0;
   e = mla::launch_combine(c, stream);
   if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("combine launch: ") + cudaGetErrorString(e));
   return MLA_FP4_OK;
 }
 
-int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, int32_t parts, int64_t rows, void* out,
-                           int32_t out_dtype, float* lse, void* stream) {
+int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, int32_t parts, int64_t rows,
+                           int64_t part_stride_out, int64_t part_stride_lse, void* out, int32_t out_dtype, float* lse,
+                           void* stream) {
   if (parts <= 0 || rows < 0) return fail(MLA_FP4_ERR_BAD_ARG, "parts/rows out of range");
   if (rows == 0) return MLA_FP4_OK;
   if (!partial_out || !partial_lse || !out) return fail(MLA_FP4_ERR_BAD_ARG, "null pointer");
   if (out_dtype != MLA_FP4_OUT_BF16 && out_dtype != MLA_FP4_OUT_F32) return fail(MLA_FP4_ERR_UNSUPPORTED, "bad out_dtype");
   if (reinterpret_cast<uintptr_t>(partial_out) % 16) return fail(MLA_FP4_ERR_BAD_ARG, "partial_out must be 16-byte aligned");
-  cudaError_t e = mla::launch_merge_partials(partial_out, partial_lse, parts, rows, out, out_dtype, lse,
+  if (part_stride_out == 0) part_stride_out = rows * mla::kLatent;
+  if (part_stride_lse == 0) part_stride_lse = rows;
+  if (part_stride_out % 4) return fail(MLA_FP4_ERR_BAD_ARG, "part_stride_out must be a multiple of 4 floats");
+  cudaError_t e = mla::launch_merge_partials(partial_out, partial_lse, parts, rows, part_stride_out, part_stride_lse, out,
+                                             out_dtype, lse,
                                              reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("merge launch: ") + cudaGetErrorString(e));
   return MLA_FP4_OK;

@@ -133,22 +133,22 @@ __global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
 // grid = rows, block = 128 (4 dims per thread).
 // ------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) merge_partials_kernel(const float* __restrict__ po, const float* __restrict__ pl,
-                                                             int parts, int64_t rows, void* out, int out_dtype,
-                                                             float* lse) {
+                                                             int parts, int64_t rows, int64_t stride_o, int64_t stride_l,
+                                                             void* out, int out_dtype, float* lse) {
   const int64_t row = blockIdx.x;
   float m = -INFINITY;
-  for (int r = 0; r < parts; ++r) m = fmaxf(m, pl[size_t(r) * rows + row]);
+  for (int r = 0; r < parts; ++r) m = fmaxf(m, pl[size_t(r) * stride_l + row]);
   float den = 0.f;
   for (int r = 0; r < parts; ++r) {
-    float l = pl[size_t(r) * rows + row];
+    float l = pl[size_t(r) * stride_l + row];
     den += (l == -INFINITY) ? 0.f : exp2f(l - m);
   }
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int r = 0; r < parts; ++r) {
-    float l = pl[size_t(r) * rows + row];
+    float l = pl[size_t(r) * stride_l + row];
     if (l == -INFINITY || den <= 0.f) continue;
     float w = exp2f(l - m) / den;
-    float4 v = reinterpret_cast<const float4*>(po + (size_t(r) * rows + row) * kLatent)[threadIdx.x];
+    float4 v = reinterpret_cast<const float4*>(po + size_t(r) * stride_o + size_t(row) * kLatent)[threadIdx.x];
     acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
   }
   size_t o = size_t(row) * kLatent + 4 * threadIdx.x;
@@ -337,10 +337,10 @@ cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream) {
   return cudaLaunchKernelEx(&cfg, combine_kernel, p);
 }
 
-cudaError_t launch_merge_partials(const float* po, const float* pl, int parts, int64_t rows, void* out, int out_dtype,
-                                  float* lse, cudaStream_t stream) {
+cudaError_t launch_merge_partials(const float* po, const float* pl, int parts, int64_t rows, int64_t stride_o,
+                                  int64_t stride_l, void* out, int out_dtype, float* lse, cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
-  merge_partials_kernel<<<dim3((unsigned)rows), 128, 0, stream>>>(po, pl, parts, rows, out, out_dtype, lse);
+  merge_partials_kernel<<<dim3((unsigned)rows), 128, 0, stream>>>(po, pl, parts, rows, stride_o, stride_l, out, out_dtype, lse);
   return cudaGetLastError();
 }
 

@@ -49,6 +49,7 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         self._kernel = _cabi.KERNEL_TCGEN05
         self._status: Optional[torch.Tensor] = None
         self._num_ctas = 0
+        self._phase_mask = 0  # profiling aid: 1 = decode kernel only, 2 = combine kernel only
 
     # ------------------------------------------------------------------ plan
     def plan(
@@ -206,6 +207,7 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         a.kernel = self._kernel
         a.num_ctas = self._num_ctas
         a.enable_pdl = 1 if self._enable_pdl else 0
+        a.phase_mask = self._phase_mask
         a.stream = torch.cuda.current_stream(q.device).cuda_stream
         _cabi.check(_cabi.lib.mla_fp4_decode(C.byref(a)))
         if return_lse:

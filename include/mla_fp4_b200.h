@@ -81,6 +81,7 @@ typedef struct MlaFp4DecodeArgs {
   int32_t kernel;      /* MLA_FP4_KERNEL_* */
   int32_t num_ctas;    /* CTAs of the persistent decode grid; 0 = one per SM of the current device */
   int32_t enable_pdl;  /* programmatic dependent launch between decode and combine (0/1) */
+  int32_t phase_mask;  /* 0 = decode + combine; 1 = decode kernel only; 2 = combine kernel only (profiling) */
   void* stream;        /* cudaStream_t */
 } MlaFp4DecodeArgs;
 
@@ -115,11 +116,14 @@ int mla_fp4_decode(const MlaFp4DecodeArgs* args);
 
 /* Merge `parts` normalised partial outputs with base-2 LSEs (decode context parallel):
    partial_out f32 [parts, rows, 512], partial_lse f32 [parts, rows] ->
-   out [rows, 512] (out_dtype) and optional lse [rows].  Same arithmetic as the split-KV
+   out [rows, 512] (out_dtype) and optional lse [rows].  part_stride_out / part_stride_lse are
+   the distances, in floats, between consecutive parts (0 = dense: rows*512 and rows), so that
+   partials gathered as one packed buffer per rank can be merged in place.  Same arithmetic as the split-KV
    reduction (flashinfer cute_dsl/attention/mla_decode.py:614-710); the reference has no
    multi-GPU path of its own. */
 int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, int32_t parts,
-                           int64_t rows, void* out, int32_t out_dtype, float* lse, void* stream);
+                           int64_t rows, int64_t part_stride_out, int64_t part_stride_lse, void* out,
+                           int32_t out_dtype, float* lse, void* stream);
 
 /* Bit-exact E2M1 nibble -> E4M3 byte dequantisation of `n_bytes` packed bytes on the device
    (out holds 2*n_bytes E4M3 bytes, low nibble first), using the same device routine as the

@@ -190,7 +190,7 @@ def test_merge_partials_matches_oracle():
     out = torch.empty(rows, 512, dtype=torch.float32, device=dev)
     lse = torch.empty(rows, dtype=torch.float32, device=dev)
     po_d, pl_d = po.to(dev), pl.to(dev)
-    _cabi.check(_cabi.lib.mla_fp4_merge_partials(po_d.data_ptr(), pl_d.data_ptr(), parts, rows,
+    _cabi.check(_cabi.lib.mla_fp4_merge_partials(po_d.data_ptr(), pl_d.data_ptr(), parts, rows, 0, 0,
                                                 out.data_ptr(), _cabi.OUT_F32, lse.data_ptr(),
                                                 ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     torch.cuda.synchronize()
