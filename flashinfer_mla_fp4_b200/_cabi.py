@@ -6,9 +6,11 @@ or fails to load, importing this module raises.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libmla_fp4_b200.so"
+# MLA_FP4_B200_LIB overrides the library location (for instance a debug build)
+LIB_PATH = Path(os.environ.get("MLA_FP4_B200_LIB") or (Path(__file__).resolve().parent / "libmla_fp4_b200.so"))
 ABI_VERSION = 1
 
 OK = 0

@@ -9,8 +9,8 @@ from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
-LIB_PATH = PKG_DIR / "libmla_fp4_b200.so"
-SOURCES = ["abi.cu", "kernels_simt.cu", "decode_sm100.cu"]
+LIB_PATH = Path(os.environ.get("MLA_FP4_B200_LIB") or (PKG_DIR / "libmla_fp4_b200.so"))
+SOURCES = ["abi.cu", "kernels_simt.cu", "combine.cu", "decode_sm100.cu"]
 HEADERS = ["common.cuh", "dequant.cuh", "launch.h", "ptx_sm100.cuh", "../../include/mla_fp4_b200.h"]
 
 
@@ -41,7 +41,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         "-gencode", "arch=compute_100a,code=sm_100a",
         "-Xcompiler", "-fPIC", "-Xptxas", "-v" if verbose else "-O3",
         "--expt-relaxed-constexpr",
-    ]
+    ] + os.environ.get("MLA_FP4_NVCC_FLAGS", "").split()
     procs = []
     for s in SOURCES:
         o = build_dir / (s + ".o")

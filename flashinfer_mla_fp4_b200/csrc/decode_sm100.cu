@@ -15,8 +15,11 @@
 // into 128-byte-swizzled shared memory, where the very same bytes serve as the K-major A operand
 // of QK^T and as the MN-major A operand of PV.  RoPE bytes, per-token scales and Q arrive by TMA.
 //
-// Warp roles (512 threads): 0-3 softmax / O rescale / epilogue (TMEM lane = token or dim),
-// 4-11 latent load + dequant, 12 MMA issue, 13 TMA issue, 14-15 idle.
+// Warp roles (448 threads): 0-3 softmax / O rescale / epilogue (TMEM lane = token or dim),
+// 4-11 latent load + dequant, 12 MMA issue (warp-uniform, one elected lane per instruction), 13 TMA issue.
+//
+// The per-role loops are kept small on purpose: the four instruction streams share one
+// instruction cache, and an MMA-issue or softmax loop that misses it starves the tensor pipe.
 //
 // Every wait is bounded: when a wait expires the CTA records MLA_FP4_ERR_DEVICE_TIMEOUT in the
 // status words, stops issuing work, drains and exits normally.
@@ -24,8 +27,6 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
-
-#include <mutex>
 
 #include "common.cuh"
 #include "dequant.cuh"
@@ -36,15 +37,16 @@ namespace mla {
 
 namespace {
 
-constexpr int kThreads = 512;
+constexpr int kThreads = 448;
 constexpr int kSoftmaxThreads = 128;
 constexpr int kDequantThreads = 256;
 constexpr int kDequantWarps = kDequantThreads / 32;
 constexpr int kStages = 2;
 constexpr int kBlocks = 4;                 // 128-dim blocks of the latent
 constexpr int kBlockBytes = kTile * 128;   // 16 KiB: [128 tokens][128 B], 128B swizzle
-constexpr float kPShift = 6.0f;            // P' = 2^(y - M + 6): keeps the E4M3 lo term out of the subnormals
-constexpr float kLazyThreshold = 2.0f;     // running max is refreshed only when exceeded by 2^2
+constexpr int kMaxSeg = 48;                // segments staged per round
+constexpr float kPShift = 4.0f;            // P' = 2^(y - M + 4): keeps the E4M3 lo term out of the subnormals
+constexpr float kLazyThreshold = 4.0f;     // the reference is refreshed only when beaten by 2^4 (P' <= 2^8 < 448)
 
 // shared memory map (bytes from a 1024-aligned base)
 constexpr uint32_t kOffKV = 0;                                            // [2][4][16384]
@@ -53,7 +55,7 @@ constexpr uint32_t kOffQLat = kOffRope + kStages * kTile * 64;            // [4]
 constexpr uint32_t kOffQRope = kOffQLat + kBlocks * kGroupHeads * 128;    // [64][64]      64B swizzle
 constexpr uint32_t kOffP = kOffQRope + kGroupHeads * 64;                  // [2][hi,lo][128][64] 64B swizzle (MN-major)
 constexpr uint32_t kOffScale = kOffP + kStages * 2 * kTile * 64;          // [2][128] f32
-constexpr uint32_t kOffM = kOffScale + kStages * kTile * 4;               // [64] f32 running reference (M - shift)
+constexpr uint32_t kOffM = kOffScale + kStages * kTile * 4;               // [64] f32 NEGATED reference -(M - shift)
 constexpr uint32_t kOffF = kOffM + kGroupHeads * 4;                       // [64] f32 rescale factor
 constexpr uint32_t kOffWmax = kOffF + kGroupHeads * 4;                    // [4][64] f32 per-warp column max / sum
 constexpr uint32_t kOffLinv = kOffWmax + 4 * kGroupHeads * 4;             // [64] f32 output_scale / l
@@ -61,11 +63,13 @@ constexpr uint32_t kOffLse = kOffLinv + kGroupHeads * 4;                  // [64
 constexpr uint32_t kOffBars = kOffLse + kGroupHeads * 4;                  // mbarriers (8 B each)
 constexpr int kNumBars = 2 * 4 /*kv_full*/ + 2 * 4 /*kv_empty*/ + 2 /*aux_full*/ + 2 /*s_full*/ + 2 /*s_empty*/ +
                          2 /*p_full*/ + 1 /*q_full*/ + 1 /*q_empty*/ + 1 /*o_free*/ + 1 /*drain*/;
-constexpr uint32_t kOffMisc = kOffBars + kNumBars * 8;                    // tmem base, abort flag, walker
-constexpr uint32_t kSmemBytes = kOffMisc + 256;
+constexpr uint32_t kOffSegs = kOffBars + kNumBars * 8;                    // Segment[kMaxSeg]
+constexpr uint32_t kOffMisc = kOffSegs + kMaxSeg * 24;                    // tmem base, abort flag, walker
+constexpr uint32_t kSmemBytes = kOffMisc + 128;
 constexpr uint32_t kSmemAlloc = kSmemBytes + 1024;                        // slack for manual 1024-alignment
+static_assert(sizeof(Segment) == 24, "segment staging layout");
 static_assert(kSmemAlloc <= 232448, "shared memory budget exceeded");
-static_assert(kOffBars % 8 == 0 && kOffMisc % 8 == 0, "barrier alignment");
+static_assert(kOffBars % 8 == 0 && kOffSegs % 8 == 0 && kOffMisc % 8 == 0, "alignment");
 
 // barrier indices
 __device__ __forceinline__ constexpr int bar_kv_full(int s, int j) { return s * 4 + j; }
@@ -87,8 +91,11 @@ constexpr uint32_t kIdescPV = ptx::idesc_e4m3(128, kGroupHeads, true, true);
 struct Misc {
   uint32_t tmem_base;
   volatile int abort;
+  int nseg;   // segments staged for the current round
+  int more;   // another round follows
   Walker walker;
 };
+static_assert(sizeof(Misc) <= 128, "misc area");
 
 struct Ctx {
   uint32_t smem;      // shared-space address of the aligned base
@@ -97,15 +104,22 @@ struct Ctx {
   int32_t* status;
 };
 
+// running position of a role across rounds
+struct RoleState {
+  uint32_t it;   // tiles processed so far by this CTA (selects stage and barrier phase)
+  uint32_t seg;  // segments processed so far
+};
+
 __device__ __forceinline__ uint32_t bar_addr(const Ctx& c, int idx) { return c.smem + kOffBars + 8u * idx; }
+__device__ __forceinline__ const Segment* segs(const Ctx& c) { return reinterpret_cast<const Segment*>(c.smem_ptr + kOffSegs); }
 
 // Bounded wait.  Returns false (and flags the CTA) when the wait expires or the CTA is aborting.
-__device__ __forceinline__ bool wait_slow(const Ctx& c, int idx, uint32_t parity) {
+__device__ __noinline__ bool wait_slow(const Ctx& c, int idx, uint32_t parity) {
   const uint32_t bar = bar_addr(c, idx);
   for (uint32_t i = 0; i < (1u << 22); ++i) {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
     if (c.misc->abort) return false;
-    if (i > 64) __nanosleep(64);
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    if (i > 16) __nanosleep(128);
   }
   c.misc->abort = 1;
   if (c.status) {
@@ -119,14 +133,16 @@ __device__ __forceinline__ bool wait_slow(const Ctx& c, int idx, uint32_t parity
   return false;
 }
 __device__ __forceinline__ bool wait(const Ctx& c, int idx, uint32_t parity) {
-  if (c.misc->abort) return false;
   if (ptx::mbar_try_wait(bar_addr(c, idx), parity)) return true;
   return wait_slow(c, idx, parity);
 }
-
-// Bounded wait that ignores the abort flag: used only to let in-flight asynchronous work land
-// before the CTA exits.
-__device__ __forceinline__ void drain_wait(const Ctx& c, int idx, uint32_t parity) {
+// One lane polls for the warp; the warp barrier orders the other lanes after its acquire.
+__device__ __forceinline__ void wait_warp(const Ctx& c, int idx, uint32_t parity) {
+  if ((threadIdx.x & 31) == 0) wait(c, idx, parity);
+  __syncwarp();
+}
+// Bounded wait that ignores the abort flag: lets in-flight asynchronous work land before exit.
+__device__ __noinline__ void drain_wait(const Ctx& c, int idx, uint32_t parity) {
   const uint32_t bar = bar_addr(c, idx);
   for (uint32_t i = 0; i < (1u << 20); ++i) {
     if (ptx::mbar_try_wait(bar, parity)) return;
@@ -134,49 +150,21 @@ __device__ __forceinline__ void drain_wait(const Ctx& c, int idx, uint32_t parit
   }
 }
 
-// Tile cursor: the CTA's tiles in order, with the segment each belongs to.
-struct Cursor {
-  Walker w;
-  Segment s;
-  int t;
-  bool valid;
-  int seg_index;  // running count of segments entered
-  __device__ __forceinline__ void init(const Walker& wk) { w = wk; valid = false; t = 0; seg_index = -1; s.tile_end = 0; }
-  // advance to the next tile; returns false at the end of the CTA's range
-  __device__ __forceinline__ bool advance() {
-    if (valid && t + 1 < s.tile_end) { ++t; return true; }
-    valid = w.next(s);
-    if (valid) { t = s.tile_begin; ++seg_index; }
-    return valid;
-  }
-  __device__ __forceinline__ bool first_of_segment() const { return t == s.tile_begin; }
-  __device__ __forceinline__ bool last_of_segment() const { return t + 1 == s.tile_end; }
-};
+// Optional timeline trace (debug builds only, -DMLA_FP4_TRACE): clock64 stamps of CTA 0 for the
+// first 16 tiles, written after the 8 status words (the status buffer must then be larger).
+#ifdef MLA_FP4_TRACE
+#define MLA_TRACE(role, tile, ev)                                                                      \
+  do {                                                                                                 \
+    if (blockIdx.x == 0 && (tile) < 16u && c.status)                                                   \
+      reinterpret_cast<long long*>(c.status + 8)[((role) * 16 + (tile)) * 8 + (ev)] = clock64();       \
+  } while (0)
+#else
+#define MLA_TRACE(role, tile, ev)
+#endif
 
 // ------------------------------------------------------------------------------------------
 // role: latent load + dequant (warps 4..11)
 // ------------------------------------------------------------------------------------------
-struct RowSrc {
-  const uint8_t* p0;  // row pointer of token (tile*128 + r0), nullptr when the token is beyond seq_len
-  const uint8_t* p1;  // same for r0 + 64
-};
-
-__device__ __forceinline__ RowSrc row_sources(const DecodeParams& p, const Cursor& c, int r0) {
-  RowSrc rs;
-  const uint8_t* cache = reinterpret_cast<const uint8_t*>(p.kv_cache);
-  const int tok0 = c.t * kTile + r0, tok1 = tok0 + 64;
-  rs.p0 = nullptr; rs.p1 = nullptr;
-  if (tok0 < c.s.seq_len) {
-    int pg = __ldg(p.block_tables + size_t(c.s.b) * p.block_table_stride + tok0 / p.page_size);
-    rs.p0 = cache + (size_t(pg) * p.page_size + tok0 % p.page_size) * kRowBytes;
-  }
-  if (tok1 < c.s.seq_len) {
-    int pg = __ldg(p.block_tables + size_t(c.s.b) * p.block_table_stride + tok1 / p.page_size);
-    rs.p1 = cache + (size_t(pg) * p.page_size + tok1 % p.page_size) * kRowBytes;
-  }
-  return rs;
-}
-
 __device__ __forceinline__ uint4 ldg_nc(const uint8_t* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
@@ -185,463 +173,602 @@ __device__ __forceinline__ uint4 ldg_nc(const uint8_t* p) {
   return v;
 }
 
-// 16 packed bytes (32 codes) -> two 16-byte E4M3 chunks stored at dst and dst2 (already swizzled)
-__device__ __forceinline__ void dequant_store(const uint4& v, uint32_t dst_a, uint32_t dst_b) {
-  uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
-  e2m1x8_to_e4m3x8(v.x, a0, a1);
-  e2m1x8_to_e4m3x8(v.y, a2, a3);
-  e2m1x8_to_e4m3x8(v.z, b0, b1);
-  e2m1x8_to_e4m3x8(v.w, b2, b3);
-  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst_a), "r"(a0), "r"(a1), "r"(a2), "r"(a3) : "memory");
-  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst_b), "r"(b0), "r"(b1), "r"(b2), "r"(b3) : "memory");
+// 16 packed bytes (32 codes) -> 32 E4M3 bytes (two 16-byte chunks).  Everything in this loop is
+// inlined on purpose: a call makes the compiler wait, at the call, for every global load still in
+// flight (their destination registers must survive the call), which exposes the memory latency.
+struct E4m3x32 {
+  uint32_t a[4], b[4];
+};
+__device__ __forceinline__ E4m3x32 dequant32(uint4 v) {
+  E4m3x32 r;
+  e2m1x8_to_e4m3x8(v.x, r.a[0], r.a[1]);
+  e2m1x8_to_e4m3x8(v.y, r.a[2], r.a[3]);
+  e2m1x8_to_e4m3x8(v.z, r.b[0], r.b[1]);
+  e2m1x8_to_e4m3x8(v.w, r.b[2], r.b[3]);
+  return r;
+}
+__device__ __forceinline__ void store32(const E4m3x32& r, uint32_t dst_a, uint32_t dst_b) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst_a), "r"(r.a[0]), "r"(r.a[1]), "r"(r.a[2]), "r"(r.a[3]) : "memory");
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst_b), "r"(r.b[0]), "r"(r.b[1]), "r"(r.b[2]), "r"(r.b[3]) : "memory");
 }
 
-__device__ __forceinline__ void dequant_role(const DecodeParams& p, const Ctx& c, int dtid) {
+// Row pointers of this thread's two tokens (r0 and r0 + 64) of tile t of a segment; nullptr beyond seq_len.
+__device__ __forceinline__ void row_sources(const DecodeParams& p, const Segment& sg, int t, int r0, const uint8_t*& p0,
+                                         const uint8_t*& p1) {
+  const uint8_t* cache = reinterpret_cast<const uint8_t*>(p.kv_cache);
+  const int tok0 = t * kTile + r0, tok1 = tok0 + 64;
+  p0 = nullptr;
+  p1 = nullptr;
+  const int32_t* bt = p.block_tables + size_t(sg.b) * p.block_table_stride;
+  if (tok0 < sg.seq_len) p0 = cache + (size_t(__ldg(bt + tok0 / p.page_size)) * p.page_size + tok0 % p.page_size) * kRowBytes;
+  if (tok1 < sg.seq_len) p1 = cache + (size_t(__ldg(bt + tok1 / p.page_size)) * p.page_size + tok1 % p.page_size) * kRowBytes;
+}
+
+__device__ __forceinline__ void dequant_role(const DecodeParams& p, const Ctx& c, int dtid, RoleState& st) {
+  const int nseg = c.misc->nseg;
+  if (nseg == 0) return;
+  const Segment* sg = segs(c);
   const int r0 = dtid >> 2;    // 0..63, second row is r0 + 64
   const int ch = dtid & 3;     // 16-byte packed chunk inside the 64-byte slice of a block
   const int lane = dtid & 31;
-  Cursor cur;
-  cur.init(c.misc->walker);
-  if (!cur.advance()) return;
-
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+  int si = 0, t = sg[0].tile_begin;
+  const uint8_t *p0, *p1;
+  row_sources(p, sg[0], t, r0, p0, p1);
   uint4 regs[kBlocks][2];
-  RowSrc src = row_sources(p, cur, r0);
 #pragma unroll
   for (int j = 0; j < kBlocks; ++j) {
-    regs[j][0] = src.p0 ? ldg_nc(src.p0 + 64 * j + 16 * ch) : zero;
-    regs[j][1] = src.p1 ? ldg_nc(src.p1 + 64 * j + 16 * ch) : zero;
+    regs[j][0] = p0 ? ldg_nc(p0 + 64 * j + 16 * ch) : zero;
+    regs[j][1] = p1 ? ldg_nc(p1 + 64 * j + 16 * ch) : zero;
   }
   // swizzled destinations inside a block: row*128 + ((2*ch + e) ^ (row & 7)) * 16
   const uint32_t sw0 = uint32_t(r0 & 7);  // (r0 + 64) & 7 is the same
   const uint32_t off_a = uint32_t(r0) * 128u + ((uint32_t(2 * ch) ^ sw0) << 4);
   const uint32_t off_b = uint32_t(r0) * 128u + ((uint32_t(2 * ch + 1) ^ sw0) << 4);
 
-  uint32_t it = 0;
   bool more = true;
   while (more) {
-    const int s = it & 1;
-    const uint32_t k = it >> 1;
-    Cursor nxt = cur;
-    more = nxt.advance();
-    RowSrc nsrc;
-    nsrc.p0 = nullptr; nsrc.p1 = nullptr;
-    if (more) nsrc = row_sources(p, nxt, r0);
+    const uint32_t it = st.it;
+    const uint32_t s = it & 1, k = it >> 1;
+    // position of the next tile (prefetched while this one is converted)
+    int nsi = si, nt = t + 1;
+    if (nt == sg[si].tile_end) {
+      ++nsi;
+      more = nsi < nseg;
+      if (more) nt = sg[nsi].tile_begin;
+    }
+    if (more) row_sources(p, sg[nsi], nt, r0, p0, p1);
+    if (dtid == 0) MLA_TRACE(1, it, 0);
 #pragma unroll
     for (int j = 0; j < kBlocks; ++j) {
-      if (k >= 1) wait(c, bar_kv_empty(s, j), (k - 1) & 1);
-      const uint32_t base = c.smem + kOffKV + uint32_t(s * kBlocks + j) * kBlockBytes;
-      dequant_store(regs[j][0], base + off_a, base + off_b);
-      dequant_store(regs[j][1], base + off_a + 64u * 128u, base + off_b + 64u * 128u);
+      // convert first (registers only), then wait for the block to be free, then store
+      const E4m3x32 e0 = dequant32(regs[j][0]);
+      const E4m3x32 e1 = dequant32(regs[j][1]);
+      if (k >= 1) wait_warp(c, bar_kv_empty(s, j), (k - 1) & 1);
+      if (dtid == 0) MLA_TRACE(1, it, 1 + j);
+      const uint32_t base = c.smem + kOffKV + (s * kBlocks + j) * kBlockBytes;
+      store32(e0, base + off_a, base + off_b);
+      store32(e1, base + off_a + 64u * 128u, base + off_b + 64u * 128u);
       ptx::fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar_addr(c, bar_kv_full(s, j)));
       if (more) {
-        regs[j][0] = nsrc.p0 ? ldg_nc(nsrc.p0 + 64 * j + 16 * ch) : zero;
-        regs[j][1] = nsrc.p1 ? ldg_nc(nsrc.p1 + 64 * j + 16 * ch) : zero;
+        regs[j][0] = p0 ? ldg_nc(p0 + 64 * j + 16 * ch) : zero;
+        regs[j][1] = p1 ? ldg_nc(p1 + 64 * j + 16 * ch) : zero;
       }
     }
-    cur = nxt;
-    ++it;
+    if (dtid == 0) MLA_TRACE(1, it, 5);
+    si = nsi;
+    t = nt;
+    ++st.it;
   }
+  st.seg += nseg;
 }
 
 // ------------------------------------------------------------------------------------------
 // role: TMA issue (warp 13, one lane): Q per segment; RoPE bytes + scales per tile
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_role(const DecodeParams& p, const Ctx& c, const CUtensorMap* map_q_lat,
-                                         const CUtensorMap* map_q_rope, const CUtensorMap* map_rope) {
-  Cursor cur;
-  cur.init(c.misc->walker);
-  uint32_t it = 0;
+                                         const CUtensorMap* map_q_rope, const CUtensorMap* map_rope, RoleState& st) {
+  const int nseg = c.misc->nseg;
+  const Segment* sg = segs(c);
   const int ppt = kTile / p.page_size;  // pages per tile
   const uint32_t page_rope_bytes = uint32_t(p.page_size) * 64u;
   const uint32_t page_scale_bytes = uint32_t(p.page_size) * 4u;
-  while (cur.advance()) {
-    if (cur.first_of_segment()) {
-      const uint32_t seg = uint32_t(cur.seg_index);
-      if (seg >= 1) wait(c, kBarQEmpty, (seg - 1) & 1);
-      if (!c.misc->abort) {
-        int qpos, head0;
-        group_coords(cur.s.g, p.num_heads, qpos, head0);
-        const uint32_t bar = bar_addr(c, kBarQFull);
-        ptx::mbar_arrive_expect_tx(bar, kGroupHeads * kQDim);
-#pragma unroll
-        for (int j = 0; j < kBlocks; ++j)
-          ptx::tma_load_4d(c.smem + kOffQLat + j * kGroupHeads * 128, map_q_lat, bar, 128 * j, head0, qpos, cur.s.b);
-        ptx::tma_load_4d(c.smem + kOffQRope, map_q_rope, bar, kLatent, head0, qpos, cur.s.b);
-      }
-    }
-    const int s = it & 1;
-    const uint32_t k = it >> 1;
-    if (k >= 1) wait(c, bar_kv_empty(s, 3), (k - 1) & 1);
+#pragma unroll 1
+  for (int si = 0; si < nseg; ++si, ++st.seg) {
+    const Segment g = sg[si];
+    if (st.seg >= 1) wait(c, kBarQEmpty, (st.seg - 1) & 1);
     if (!c.misc->abort) {
-      const int tok0 = cur.t * kTile;
-      const int pages_total = (cur.s.seq_len + p.page_size - 1) / p.page_size;
-      const int lp0 = tok0 / p.page_size;
+      int qpos, head0;
+      group_coords(g.g, p.num_heads, qpos, head0);
+      const uint32_t bar = bar_addr(c, kBarQFull);
+      ptx::mbar_arrive_expect_tx(bar, kGroupHeads * kQDim);
+#pragma unroll 1
+      for (int j = 0; j < kBlocks; ++j)
+        ptx::tma_load_4d(c.smem + kOffQLat + j * kGroupHeads * 128, map_q_lat, bar, 128 * j, head0, qpos, g.b);
+      ptx::tma_load_4d(c.smem + kOffQRope, map_q_rope, bar, kLatent, head0, qpos, g.b);
+    }
+    const int pages_total = (g.seq_len + p.page_size - 1) / p.page_size;
+#pragma unroll 1
+    for (int t = g.tile_begin; t < g.tile_end; ++t, ++st.it) {
+      const uint32_t s = st.it & 1, k = st.it >> 1;
+      // The RoPE tile of this stage was last read by QK of tile it-2 and the scales by the softmax
+      // of tile it-2; both are over once the softmax threads have released S of that tile.  (Waiting
+      // for PV of tile it-2 instead would put the copy's latency on the critical path.)
+      if (k >= 1) wait(c, bar_s_empty(s), (k - 1) & 1);
+      if (c.misc->abort) continue;
+      const int lp0 = t * ppt;
       const int np = min(ppt, pages_total - lp0);
       const uint32_t bar = bar_addr(c, bar_aux_full(s));
       ptx::mbar_arrive_expect_tx(bar, uint32_t(np) * (page_rope_bytes + page_scale_bytes));
-      const int32_t* bt = p.block_tables + size_t(cur.s.b) * p.block_table_stride + lp0;
+      const int32_t* bt = p.block_tables + size_t(g.b) * p.block_table_stride + lp0;
+#pragma unroll 1
       for (int i = 0; i < np; ++i) {
         const int pg = __ldg(bt + i);
-        ptx::tma_load_3d(c.smem + kOffRope + uint32_t(s) * kTile * 64 + uint32_t(i) * page_rope_bytes, map_rope, bar,
-                         kLatent / 2, 0, pg);
-        ptx::bulk_load(c.smem + kOffScale + uint32_t(s) * kTile * 4 + uint32_t(i) * page_scale_bytes,
+        ptx::tma_load_3d(c.smem + kOffRope + s * kTile * 64 + uint32_t(i) * page_rope_bytes, map_rope, bar, kLatent / 2, 0, pg);
+        ptx::bulk_load(c.smem + kOffScale + s * kTile * 4 + uint32_t(i) * page_scale_bytes,
                        p.kv_cache_sf + size_t(pg) * p.page_size, page_scale_bytes, bar);
       }
     }
-    ++it;
   }
   if (c.misc->abort) {  // let copies that were issued but never consumed land before exit
-    for (int s = 0; s < kStages; ++s) {
-      const uint32_t used = (it + 1 - s) >> 1;  // tiles issued on stage s
+    for (uint32_t s = 0; s < kStages; ++s) {
+      const uint32_t used = (st.it + 1 - s) >> 1;  // tiles issued on stage s
       if (used >= 1) drain_wait(c, bar_aux_full(s), (used - 1) & 1);
     }
-    if (cur.seg_index >= 0) drain_wait(c, kBarQFull, uint32_t(cur.seg_index) & 1);
+    if (st.seg >= 1) drain_wait(c, kBarQFull, (st.seg - 1) & 1);
   }
 }
 
 // ------------------------------------------------------------------------------------------
-// role: MMA issue (warp 12, one lane)
+// role: MMA issue (warp 12).  The whole warp runs this code with uniform control flow; only the
+// tcgen05 instructions sit under elect_one(), so their operands stay in uniform registers.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void issue_qk(const Ctx& c, uint32_t it, uint32_t tmem) {
-  const int s = it & 1;
+// Descriptors of every operand, built once: the per-instruction work is one 32-bit add.
+struct MmaDescs {
+  uint64_t kv_k;    // K tile block, K-major, 128B swizzle          (+ (stage*4+block)*1024 + kstep*2)
+  uint64_t kv_mn;   // same bytes as V^T, MN-major                  (+ (stage*4+block)*1024 + kstep*256)
+  uint64_t q_lat;   // Q latent block, K-major, 128B swizzle        (+ block*512 + kstep*2)
+  uint64_t rope;    // K rope, K-major, 64B swizzle                 (+ stage*512 + kstep*2)
+  uint64_t q_rope;  // Q rope                                       (+ kstep*2)
+  uint64_t p;       // P^T hi, MN-major, 64B swizzle                (+ stage*1024 + lo*512 + kstep*128)
+};
+
+__device__ __forceinline__ void issue_qk(const Ctx& c, const MmaDescs& d, uint32_t it, uint32_t tmem) {
+  const uint32_t s = it & 1;
   const uint32_t k = it >> 1;
+  MLA_TRACE(2, it, 0);
   if (k >= 1) wait(c, bar_s_empty(s), (k - 1) & 1);
   wait(c, bar_aux_full(s), k & 1);
+  MLA_TRACE(2, it, 1);
   const uint32_t d_lat = tmem + kColSLat + 64u * s;
   const uint32_t d_rope = tmem + kColSRope + 64u * s;
-#pragma unroll
-  for (int j = 0; j < kBlocks; ++j) {
+#pragma unroll 1
+  for (uint32_t j = 0; j < kBlocks; ++j) {
     wait(c, bar_kv_full(s, j), k & 1);
-    if (c.misc->abort) continue;
+    if (c.misc->abort) return;
     ptx::tc_fence_after();
-    const uint32_t a_base = c.smem + kOffKV + uint32_t(s * kBlocks + j) * kBlockBytes;
-    const uint32_t b_base = c.smem + kOffQLat + uint32_t(j) * kGroupHeads * 128;
+    const uint64_t ad = d.kv_k + ((s * kBlocks + j) * (kBlockBytes >> 4));
+    const uint64_t bd = d.q_lat + j * ((kGroupHeads * 128) >> 4);
+    if (ptx::elect_one()) {
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-      const uint64_t ad = ptx::smem_desc(a_base + 32 * ks, 16, 1024, 2);
-      const uint64_t bd = ptx::smem_desc(b_base + 32 * ks, 16, 1024, 2);
-      ptx::umma_f8(d_lat, ad, bd, kIdescQK, (j | ks) ? 1u : 0u);
+      for (uint32_t ks = 0; ks < 4; ++ks) ptx::umma_f8(d_lat, ad + 2 * ks, bd + 2 * ks, kIdescQK, (j | ks) ? 1u : 0u);
     }
+    __syncwarp();
   }
-  if (!c.misc->abort) {
-    const uint32_t a_base = c.smem + kOffRope + uint32_t(s) * kTile * 64;
-    const uint32_t b_base = c.smem + kOffQRope;
+  {
+    const uint64_t ad = d.rope + s * ((kTile * 64) >> 4);
+    if (ptx::elect_one()) {
 #pragma unroll
-    for (int ks = 0; ks < 2; ++ks) {
-      const uint64_t ad = ptx::smem_desc(a_base + 32 * ks, 16, 512, 4);
-      const uint64_t bd = ptx::smem_desc(b_base + 32 * ks, 16, 512, 4);
-      ptx::umma_f8(d_rope, ad, bd, kIdescQK, ks ? 1u : 0u);
+      for (uint32_t ks = 0; ks < 2; ++ks) ptx::umma_f8(d_rope, ad + 2 * ks, d.q_rope + 2 * ks, kIdescQK, ks);
+      ptx::umma_commit(bar_addr(c, bar_s_full(s)));
     }
-    ptx::umma_commit(bar_addr(c, bar_s_full(s)));
+    __syncwarp();
   }
+  MLA_TRACE(2, it, 2);
 }
 
-__device__ __forceinline__ void issue_pv(const Ctx& c, uint32_t it, uint32_t tmem, bool first_of_segment, uint32_t seg) {
-  const int s = it & 1;
+__device__ __forceinline__ void issue_pv(const Ctx& c, const MmaDescs& d, uint32_t it, uint32_t tmem, bool first_of_segment,
+                                         uint32_t seg) {
+  const uint32_t s = it & 1;
   const uint32_t k = it >> 1;
+  MLA_TRACE(2, it, 3);
   wait(c, bar_p_full(s), k & 1);
   if (first_of_segment && seg >= 1) wait(c, kBarOFree, (seg - 1) & 1);
+  MLA_TRACE(2, it, 4);
   if (c.misc->abort) return;
   ptx::tc_fence_after();
-  const uint32_t p_hi = c.smem + kOffP + uint32_t(s) * 2 * kTile * 64;
-  const uint32_t p_lo = p_hi + kTile * 64;
+  const uint64_t p_hi = d.p + s * ((2 * kTile * 64) >> 4);
+  const uint64_t p_lo = p_hi + ((kTile * 64) >> 4);
+  const uint32_t acc0 = first_of_segment ? 0u : 1u;
+#pragma unroll 1
+  for (uint32_t j = 0; j < kBlocks; ++j) {
+    // A = V^T block: MN-major, 128-byte swizzle; 32 tokens per step = 4 groups of 8 rows (4096 B)
+    const uint64_t ad = d.kv_mn + ((s * kBlocks + j) * (kBlockBytes >> 4));
+    const uint32_t dd = tmem + kColO + 64u * j;
+    if (ptx::elect_one()) {
 #pragma unroll
-  for (int j = 0; j < kBlocks; ++j) {
-    const uint32_t a_base = c.smem + kOffKV + uint32_t(s * kBlocks + j) * kBlockBytes;
-    const uint32_t d = tmem + kColO + 64u * j;
-#pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-      // A = V^T: MN-major, 128-byte swizzle; 32 tokens per step = 4 groups of 8 rows of 128 B
-      const uint64_t ad = ptx::smem_desc(a_base + 4096 * ks, kBlockBytes, 1024, 2);
-      // B = P^T: MN-major (64 heads contiguous), 64-byte swizzle; 32 tokens per step = 2048 B
-      const uint64_t bh = ptx::smem_desc(p_hi + 2048 * ks, 512, 512, 4);
-      const uint64_t bl = ptx::smem_desc(p_lo + 2048 * ks, 512, 512, 4);
-      ptx::umma_f8(d, ad, bh, kIdescPV, (first_of_segment && ks == 0) ? 0u : 1u);
-      ptx::umma_f8(d, ad, bl, kIdescPV, 1u);
+      for (uint32_t ks = 0; ks < 4; ++ks) {
+        // B = P^T: MN-major (64 heads contiguous), 64-byte swizzle; 32 tokens per step = 2048 B
+        ptx::umma_f8(dd, ad + 256 * ks, p_hi + 128 * ks, kIdescPV, ks ? 1u : acc0);
+        ptx::umma_f8(dd, ad + 256 * ks, p_lo + 128 * ks, kIdescPV, 1u);
+      }
+      ptx::umma_commit(bar_addr(c, bar_kv_empty(s, j)));
     }
-    ptx::umma_commit(bar_addr(c, bar_kv_empty(s, j)));
+    __syncwarp();
   }
+  MLA_TRACE(2, it, 5);
 }
 
-__device__ __forceinline__ void mma_role(const Ctx& c, uint32_t tmem) {
-  Cursor cur;
-  cur.init(c.misc->walker);
-  uint32_t it = 0;
-  bool have = cur.advance();
-  while (have) {
-    // one segment
-    const uint32_t seg = uint32_t(cur.seg_index);
-    const int n = cur.s.tile_end - cur.s.tile_begin;
-    wait(c, kBarQFull, seg & 1);
-    issue_qk(c, it, tmem);
+__device__ __forceinline__ void mma_role(const Ctx& c, uint32_t tmem, RoleState& st) {
+  MmaDescs d;
+  d.kv_k = ptx::smem_desc(c.smem + kOffKV, 16, 1024, 2);
+  d.kv_mn = ptx::smem_desc(c.smem + kOffKV, kBlockBytes, 1024, 2);
+  d.q_lat = ptx::smem_desc(c.smem + kOffQLat, 16, 1024, 2);
+  d.rope = ptx::smem_desc(c.smem + kOffRope, 16, 512, 4);
+  d.q_rope = ptx::smem_desc(c.smem + kOffQRope, 16, 512, 4);
+  d.p = ptx::smem_desc(c.smem + kOffP, 512, 512, 4);
+  const int nseg = c.misc->nseg;
+  const Segment* sg = segs(c);
+#pragma unroll 1
+  for (int si = 0; si < nseg; ++si, ++st.seg) {
+    const int n = sg[si].tile_end - sg[si].tile_begin;
+    wait(c, kBarQFull, st.seg & 1);
+    issue_qk(c, d, st.it, tmem);
+#pragma unroll 1
     for (int i = 0; i < n; ++i) {
-      if (i + 1 < n) issue_qk(c, it + i + 1, tmem);
-      else if (!c.misc->abort) ptx::umma_commit(bar_addr(c, kBarQEmpty));  // every QK of this segment has been issued
-      issue_pv(c, it + i, tmem, i == 0, seg);
+      if (i + 1 < n) {
+        issue_qk(c, d, st.it + i + 1, tmem);
+      } else if (!c.misc->abort) {  // every QK of this segment has been issued
+        if (ptx::elect_one()) ptx::umma_commit(bar_addr(c, kBarQEmpty));
+        __syncwarp();
+      }
+      issue_pv(c, d, st.it + i, tmem, i == 0, st.seg);
     }
-    it += n;
-    // skip the cursor to the next segment
-    for (int i = 0; i < n; ++i) have = cur.advance();
+    st.it += n;
   }
-  // drain: everything issued has completed before TMEM is released
-  ptx::umma_commit(bar_addr(c, kBarDrain));
-  drain_wait(c, kBarDrain, 0);
 }
 
 // ------------------------------------------------------------------------------------------
 // role: softmax / rescale / epilogue (warps 0..3, thread = TMEM lane)
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ float* smem_f(const Ctx& c, uint32_t off) { return reinterpret_cast<float*>(c.smem_ptr + off); }
-
-__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float cc, float d, uint32_t& lo_out) {
-  // two-term split of four values: hi = e4m3(v), lo = e4m3(v - hi)
-  __half2 h01 = __floats2half2_rn(a, b), h23 = __floats2half2_rn(cc, d);
-  __nv_fp8x2_storage_t hi01 = __nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<__half2_raw*>(&h01), __NV_SATFINITE, __NV_E4M3);
-  __nv_fp8x2_storage_t hi23 = __nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<__half2_raw*>(&h23), __NV_SATFINITE, __NV_E4M3);
-  __half2_raw b01 = __nv_cvt_fp8x2_to_halfraw2(hi01, __NV_E4M3);
-  __half2_raw b23 = __nv_cvt_fp8x2_to_halfraw2(hi23, __NV_E4M3);
-  __half2 r01 = __hsub2(h01, *reinterpret_cast<__half2*>(&b01));
-  __half2 r23 = __hsub2(h23, *reinterpret_cast<__half2*>(&b23));
-  __nv_fp8x2_storage_t lo01 = __nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<__half2_raw*>(&r01), __NV_SATFINITE, __NV_E4M3);
-  __nv_fp8x2_storage_t lo23 = __nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<__half2_raw*>(&r23), __NV_SATFINITE, __NV_E4M3);
-  lo_out = uint32_t(lo01) | (uint32_t(lo23) << 16);
-  return uint32_t(hi01) | (uint32_t(hi23) << 16);
+// ---- packed FP32 pairs (sm_100 f32x2 arithmetic)
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ void lds_pairs(uint32_t addr, uint64_t& p0, uint64_t& p1) {
+  asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(p0), "=l"(p1) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
-__device__ __forceinline__ void store_out_elem(void* out, int out_dtype, size_t idx, float v) {
-  if (out_dtype == MLA_FP4_OUT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
-  else reinterpret_cast<float*>(out)[idx] = v;
+// two-term E4M3 split of a pair: hi = e4m3(v), lo = e4m3(v - hi); returns hi (16 bits), lo via reference
+__device__ __forceinline__ uint32_t split_e4m3x2(uint64_t v2, uint32_t& lo) {
+  float a, b;
+  unpack2(v2, a, b);
+  __half2 h = __floats2half2_rn(a, b);
+  const __nv_fp8x2_storage_t hi = __nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<__half2_raw*>(&h), __NV_SATFINITE, __NV_E4M3);
+  __half2_raw back = __nv_cvt_fp8x2_to_halfraw2(hi, __NV_E4M3);
+  __half2 r = __hsub2(h, *reinterpret_cast<__half2*>(&back));
+  lo = __nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<__half2_raw*>(&r), __NV_SATFINITE, __NV_E4M3);
+  return hi;
 }
 
-__device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c, uint32_t tmem, int tid) {
+// Sum over the 32 lanes of 64 per-lane values held as 32 pairs; lane L ends with the totals of
+// heads 2L and 2L+1.
+__device__ __forceinline__ void warp_transpose_sum64(uint64_t (&l2)[kGroupHeads / 2], int lane, float& r0, float& r1) {
+  float v[kGroupHeads];
+#pragma unroll
+  for (int i = 0; i < kGroupHeads / 2; ++i) unpack2(l2[i], v[2 * i], v[2 * i + 1]);
+#pragma unroll
+  for (int o = 16, n = kGroupHeads; o > 0; o >>= 1, n >>= 1) {
+    const bool up = (lane & o) != 0;
+#pragma unroll
+    for (int i = 0; i < n / 2; ++i) {
+      const float keep = up ? v[i + n / 2] : v[i];
+      const float send = up ? v[i] : v[i + n / 2];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+    }
+  }
+  r0 = v[0];
+  r1 = v[1];
+}
+
+struct SoftmaxTile {
+  uint32_t t_lat, t_rope;  // TMEM addresses of this thread's lane, S columns of the stage
+  uint32_t negm;           // shared address of the 64 negated references (-m)
+  uint32_t p_hi, p_lo;     // shared addresses of this thread's P' rows
+  uint32_t psw;            // swizzle term of the row
+  uint64_t sc2, cs2;       // (scale_t, scale_t), (c, c)
+  bool valid;
+};
+
+// One pass over the 64 heads of this thread's token: e = exp2(x*c - m), l += acc * e, and
+// P' = e*scale_t split into two E4M3 terms and written to the swizzled P rows.  Returns the
+// largest exponent argument seen (for the lazy-reference check).
+__device__ __forceinline__ float softmax_pass(const SoftmaxTile& t, uint64_t (&l2)[kGroupHeads / 2], uint64_t acc2) {
+  float mx = -INFINITY;
+#pragma unroll
+  for (int cidx = 0; cidx < 4; ++cidx) {
+    uint32_t a[16], b[16];
+    ptx::tmem_ld16(t.t_lat + 16 * cidx, a);
+    ptx::tmem_ld16(t.t_rope + 16 * cidx, b);
+    ptx::tmem_wait_ld();
+    const uint32_t off = ((uint32_t(cidx) ^ t.psw) << 4);
+    if (t.valid) {
+      uint32_t hi16[8], lo16[8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {  // 4 heads per shared load of the references
+        uint64_t nm0, nm1;
+        lds_pairs(t.negm + 64 * cidx + 16 * q, nm0, nm1);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int i = 4 * q + 2 * h;
+          const uint64_t x2 = fma2(pack2u(a[i], a[i + 1]), t.sc2, pack2u(b[i], b[i + 1]));
+          const uint64_t arg2 = fma2(x2, t.cs2, h ? nm1 : nm0);
+          float a0, a1;
+          unpack2(arg2, a0, a1);
+          mx = fmaxf(mx, fmaxf(a0, a1));
+          const uint64_t e2 = pack2(ptx::ex2(a0), ptx::ex2(a1));
+          l2[8 * cidx + 2 * q + h] = fma2(e2, acc2, l2[8 * cidx + 2 * q + h]);
+          hi16[2 * q + h] = split_e4m3x2(mul2(e2, t.sc2), lo16[2 * q + h]);
+        }
+      }
+      asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(t.p_hi + off), "r"(hi16[0] | (hi16[1] << 16)),
+                   "r"(hi16[2] | (hi16[3] << 16)), "r"(hi16[4] | (hi16[5] << 16)), "r"(hi16[6] | (hi16[7] << 16)) : "memory");
+      asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(t.p_lo + off), "r"(lo16[0] | (lo16[1] << 16)),
+                   "r"(lo16[2] | (lo16[3] << 16)), "r"(lo16[4] | (lo16[5] << 16)), "r"(lo16[6] | (lo16[7] << 16)) : "memory");
+    } else {  // token beyond seq_len: weight exactly zero, whatever its row holds
+      asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(t.p_hi + off), "r"(0u) : "memory");
+      asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(t.p_lo + off), "r"(0u) : "memory");
+    }
+  }
+  return mx;
+}
+
+// Refresh the per-head reference: column max of y = x*c + log2(scale_t) over the tile's tokens,
+// m = max(m_old, colmax - shift); f = 2^(m_old - m) (0 when there was no reference yet).
+__device__ __noinline__ void refresh_reference(const Ctx& c, uint32_t t_lat, uint32_t t_rope, float sc, bool valid,
+                                               float cscale, float lg, bool have_m, int tid) {
   const int warp = tid >> 5, lane = tid & 31;
-  const uint32_t lane_base = (uint32_t(warp) * 32u) << 16;
-  const float cscale = p.softmax_scale * kLog2e;
-  float* m_s = smem_f(c, kOffM);
-  float* f_s = smem_f(c, kOffF);
-  float* wred = smem_f(c, kOffWmax);
-  float* linv_s = smem_f(c, kOffLinv);
-  float* lse_s = smem_f(c, kOffLse);
-
-  Cursor cur;
-  cur.init(c.misc->walker);
-  uint32_t it = 0;
-  float l[kGroupHeads];
-  bool have_m = false;
-
-  while (cur.advance()) {
-    const int s = it & 1;
-    const uint32_t k = it >> 1;
-    if (cur.first_of_segment()) {
-#pragma unroll
-      for (int h = 0; h < kGroupHeads; ++h) l[h] = 0.f;
-      have_m = false;
-    }
-    // per-token scale
-    wait(c, bar_aux_full(s), k & 1);
-    const bool valid = (cur.t * kTile + tid) < cur.s.seq_len;
-    float sc = smem_f(c, kOffScale)[s * kTile + tid];
-    sc = valid ? sc : 0.f;
-    const float lg = valid ? log2f(fmaxf(fabsf(sc), 8.67361738e-19f)) : 0.f;  // floor 2^-60
-
-    wait(c, bar_s_full(s), k & 1);
-    ptx::tc_fence_after();
-    const uint32_t t_lat = tmem + lane_base + kColSLat + 64u * s;
-    const uint32_t t_rope = tmem + lane_base + kColSRope + 64u * s;
-
-    // ---- pass 1: does any score exceed the running reference by more than the lazy threshold?
-    bool need = !have_m;
-    if (have_m) {
-      float mx = -INFINITY;
-#pragma unroll
-      for (int cidx = 0; cidx < 4; ++cidx) {
-        uint32_t a[16], b[16];
-        ptx::tmem_ld16(t_lat + 16 * cidx, a);
-        ptx::tmem_ld16(t_rope + 16 * cidx, b);
-        ptx::tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float x = fmaf(__uint_as_float(a[i]), sc, __uint_as_float(b[i])) * cscale;
-          mx = fmaxf(mx, x - m_s[16 * cidx + i]);
-        }
-      }
-      need = valid && (mx > (kPShift + kLazyThreshold) - lg);
-    }
-    const bool update = ptx::bar_or(1, kSoftmaxThreads, need);
-
-    if (update) {
-      // ---- column max of y = x + log2(scale_t) over the 128 tokens of the tile
-      float mine0 = -INFINITY, mine1 = -INFINITY;
-#pragma unroll
-      for (int cidx = 0; cidx < 4; ++cidx) {
-        uint32_t a[16], b[16];
-        ptx::tmem_ld16(t_lat + 16 * cidx, a);
-        ptx::tmem_ld16(t_rope + 16 * cidx, b);
-        ptx::tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float x = fmaf(__uint_as_float(a[i]), sc, __uint_as_float(b[i])) * cscale;
-          float y = valid ? x + lg : -INFINITY;
-          float r = ptx::redux_max_f32(y);
-          const int h = 16 * cidx + i;
-          if (lane == (h & 31)) { if (h < 32) mine0 = r; else mine1 = r; }
-        }
-      }
-      wred[warp * kGroupHeads + lane] = mine0;
-      wred[warp * kGroupHeads + 32 + lane] = mine1;
-      ptx::bar_sync(1, kSoftmaxThreads);
-      if (tid < kGroupHeads) {
-        float mnew = fmaxf(fmaxf(wred[tid], wred[kGroupHeads + tid]),
-                           fmaxf(wred[2 * kGroupHeads + tid], wred[3 * kGroupHeads + tid])) - kPShift;
-        float mold = have_m ? m_s[tid] : -INFINITY;
-        mnew = fmaxf(mnew, mold);
-        f_s[tid] = have_m ? ptx::ex2(mold - mnew) : 0.f;
-        m_s[tid] = mnew;
-      }
-      ptx::bar_sync(1, kSoftmaxThreads);
-      if (have_m) {
-#pragma unroll
-        for (int h = 0; h < kGroupHeads; ++h) l[h] *= f_s[h];
-        // O^T is rescaled in place once the previous tile's PV has completed
-        const uint32_t pit = it - 1;
-        wait(c, bar_kv_empty(pit & 1, 3), (pit >> 1) & 1);
-        ptx::tc_fence_after();
+  const uint32_t wred = c.smem + kOffWmax;
 #pragma unroll 1
-        for (int j = 0; j < kBlocks; ++j) {
+  for (int cidx = 0; cidx < 4; ++cidx) {
+    uint32_t a[16], b[16];
+    ptx::tmem_ld16(t_lat + 16 * cidx, a);
+    ptx::tmem_ld16(t_rope + 16 * cidx, b);
+    ptx::tmem_wait_ld();
+    float mine = -INFINITY;
 #pragma unroll
-          for (int cidx = 0; cidx < 4; ++cidx) {
-            uint32_t o[16];
-            const uint32_t ta = tmem + lane_base + kColO + 64u * j + 16u * cidx;
-            ptx::tmem_ld16(ta, o);
-            ptx::tmem_wait_ld();
+    for (int i = 0; i < 16; ++i) {
+      const float y = fmaf(fmaf(__uint_as_float(a[i]), sc, __uint_as_float(b[i])), cscale, lg);
+      const float r = ptx::redux_max_f32(valid ? y : -INFINITY);
+      if ((lane & 15) == i) mine = r;
+    }
+    if (lane < 16) sts_f32(wred + 4 * (warp * kGroupHeads + 16 * cidx + lane), mine);
+  }
+  ptx::bar_sync(1, kSoftmaxThreads);
+  if (tid < kGroupHeads) {
+    float mnew = fmaxf(fmaxf(lds_f32(wred + 4 * tid), lds_f32(wred + 4 * (kGroupHeads + tid))),
+                       fmaxf(lds_f32(wred + 4 * (2 * kGroupHeads + tid)), lds_f32(wred + 4 * (3 * kGroupHeads + tid)))) - kPShift;
+    const float mold = have_m ? -lds_f32(c.smem + kOffM + 4 * tid) : -INFINITY;
+    mnew = fmaxf(mnew, mold);
+    sts_f32(c.smem + kOffF + 4 * tid, have_m ? ptx::ex2(mold - mnew) : 0.f);
+    sts_f32(c.smem + kOffM + 4 * tid, -mnew);
+  }
+  ptx::bar_sync(1, kSoftmaxThreads);
+}
+
+// O^T *= f per head column, in TMEM (all four 128-dim blocks of this thread's lane)
+__device__ __noinline__ void rescale_output(const Ctx& c, uint32_t tmem_lane) {
+#pragma unroll 1
+  for (int jc = 0; jc < kBlocks * 4; ++jc) {
+    uint32_t o[16];
+    const uint32_t ta = tmem_lane + kColO + 16u * jc;
+    ptx::tmem_ld16(ta, o);
+    ptx::tmem_wait_ld();
+    const uint32_t f = c.smem + kOffF + 64 * (jc & 3);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f_s[16 * cidx + i]);
-            ptx::tmem_st16(ta, o);
-          }
+    for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * lds_f32(f + 4 * i));
+    ptx::tmem_st16(ta, o);
+  }
+  ptx::tmem_wait_st();
+}
+
+// Normalise O^T and write it: to the output tensor (slot < 0) or to a split-KV partial slot.
+__device__ __noinline__ void write_output(const DecodeParams& p, const Ctx& c, uint32_t tmem_lane, int tid, int b, int g,
+                                          int slot) {
+  int qpos, head0;
+  group_coords(g, p.num_heads, qpos, head0);
+  const int heads_here = min(kGroupHeads, p.num_heads - head0);
+  const size_t row0 = (size_t(b) * p.q_len + qpos) * p.num_heads + head0;
+  const bool direct = slot < 0;
+  float* so = reinterpret_cast<float*>(p.workspace) + size_t(direct ? 0 : slot) * kSlotFloats;
+  const uint32_t linv = c.smem + kOffLinv;
+#pragma unroll 1
+  for (int jc = 0; jc < kBlocks * 4; ++jc) {
+    uint32_t o[16];
+    ptx::tmem_ld16(tmem_lane + kColO + 16u * jc, o);
+    ptx::tmem_wait_ld();
+    const int h0 = 16 * (jc & 3);
+    const int dim = 128 * (jc >> 2) + tid;
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(o[i]) * lds_f32(linv + 4 * (h0 + i));
+    if (!direct) {
+      float4* dst = reinterpret_cast<float4*>(so + size_t(dim) * kGroupHeads + h0);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
+    } else if (p.out_dtype == MLA_FP4_OUT_BF16) {
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (row0 + h0) * kLatent + dim;
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if (h0 + i < heads_here) dst[size_t(i) * kLatent] = __float2bfloat16_rn(v[i]);
+    } else {
+      float* dst = reinterpret_cast<float*>(p.out) + (row0 + h0) * kLatent + dim;
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if (h0 + i < heads_here) dst[size_t(i) * kLatent] = v[i];
+    }
+  }
+  const float lse = lds_f32(c.smem + kOffLse + 4 * (tid & 63));
+  if (direct) {
+    if (p.lse && tid < heads_here) p.lse[row0 + tid] = lse;
+  } else if (tid < kGroupHeads) {
+    so[kSlotOFloats + tid] = lse;
+  }
+}
+
+__device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c, uint32_t tmem, int tid, RoleState& st) {
+  const int nseg = c.misc->nseg;
+  const Segment* sg = segs(c);
+  const int warp = tid >> 5, lane = tid & 31;
+  const uint32_t tmem_lane = tmem + ((uint32_t(warp) * 32u) << 16);
+  const float cscale = p.softmax_scale * kLog2e;
+  const uint64_t one2 = pack2(1.f, 1.f);
+  SoftmaxTile t;
+  t.negm = c.smem + kOffM;
+  t.cs2 = pack2(cscale, cscale);
+  t.psw = (uint32_t(tid) >> 1) & 3u;
+
+#pragma unroll 1
+  for (int si = 0; si < nseg; ++si, ++st.seg) {
+    const Segment g = sg[si];
+    uint64_t l2[kGroupHeads / 2];
+#pragma unroll
+    for (int h = 0; h < kGroupHeads / 2; ++h) l2[h] = 0ull;
+#pragma unroll 1
+    for (int tt = g.tile_begin; tt < g.tile_end; ++tt, ++st.it) {
+      const uint32_t it = st.it;
+      const uint32_t s = it & 1, k = it >> 1;
+      const bool first = tt == g.tile_begin;
+      if (tid == 0) MLA_TRACE(0, it, 0);
+      // per-token scale
+      wait(c, bar_aux_full(s), k & 1);
+      t.valid = (tt * kTile + tid) < g.seq_len;
+      float sc = lds_f32(c.smem + kOffScale + 4 * (s * kTile + tid));
+      sc = t.valid ? sc : 0.f;
+      const float lg = t.valid ? __log2f(fmaxf(fabsf(sc), 8.67361738e-19f)) : 0.f;  // floor 2^-60
+      t.sc2 = pack2(sc, sc);
+      t.t_lat = tmem_lane + kColSLat + 64u * s;
+      t.t_rope = tmem_lane + kColSRope + 64u * s;
+      t.p_hi = c.smem + kOffP + s * 2 * kTile * 64 + uint32_t(tid) * 64u;
+      t.p_lo = t.p_hi + kTile * 64;
+
+      // the P buffer of this stage is free once PV of tile it-2 has completed
+      if (k >= 1) wait(c, bar_kv_empty(s, 3), (k - 1) & 1);
+      wait(c, bar_s_full(s), k & 1);
+      if (tid == 0) MLA_TRACE(0, it, 1);
+      ptx::tc_fence_after();
+
+      // first tile of a segment: set the reference before anything is exponentiated
+      if (first) refresh_reference(c, t.t_lat, t.t_rope, sc, t.valid, cscale, lg, false, tid);
+      if (tid == 0) MLA_TRACE(0, it, 2);
+
+      // Speculative pass with the current reference.  It stands unless some score beat the
+      // reference by more than the lazy threshold (P' would leave the E4M3 range).
+      const float mx = softmax_pass(t, l2, one2);
+      const bool need = t.valid && (mx + lg > kPShift + kLazyThreshold);
+      if (ptx::bar_or(1, kSoftmaxThreads, need)) {
+        // Refresh the reference.  (l + e_old) * f equals l * f + e_new, so the row sums only need
+        // the factor; O^T is rescaled in TMEM; P' is recomputed with the new reference.
+        refresh_reference(c, t.t_lat, t.t_rope, sc, t.valid, cscale, lg, true, tid);
+#pragma unroll
+        for (int q = 0; q < kGroupHeads / 4; ++q) {
+          uint64_t f0, f1;
+          lds_pairs(c.smem + kOffF + 16 * q, f0, f1);
+          l2[2 * q] = mul2(l2[2 * q], f0);
+          l2[2 * q + 1] = mul2(l2[2 * q + 1], f1);
         }
-        ptx::tmem_wait_st();
+        if (!first) {  // O^T holds earlier tiles: rescale once their PV has completed
+          const uint32_t pit = it - 1;
+          wait(c, bar_kv_empty(pit & 1, 3), (pit >> 1) & 1);
+          ptx::tc_fence_after();
+          rescale_output(c, tmem_lane);
+        }
+        (void)softmax_pass(t, l2, 0ull);
       }
-      have_m = true;
+      if (tid == 0) MLA_TRACE(0, it, 3);
+      ptx::tc_fence_before();  // orders the S reads and any O rescale before the arrives
+      ptx::mbar_arrive(bar_addr(c, bar_s_empty(s)));
+      ptx::fence_proxy_async_smem();
+      ptx::mbar_arrive(bar_addr(c, bar_p_full(s)));
+      if (tid == 0) MLA_TRACE(0, it, 5);
     }
-
-    // ---- the P buffer of this stage is free once PV of tile it-2 has completed
-    if (k >= 1) wait(c, bar_kv_empty(s, 3), (k - 1) & 1);
-
-    // ---- pass 2: probabilities, row sums, two-term E4M3 P' into shared memory
-    const uint32_t p_hi = c.smem + kOffP + uint32_t(s) * 2 * kTile * 64 + uint32_t(tid) * 64u;
-    const uint32_t p_lo = p_hi + kTile * 64;
-    const uint32_t psw = (uint32_t(tid) >> 1) & 3u;
-#pragma unroll
-    for (int cidx = 0; cidx < 4; ++cidx) {
-      uint32_t a[16], b[16];
-      ptx::tmem_ld16(t_lat + 16 * cidx, a);
-      ptx::tmem_ld16(t_rope + 16 * cidx, b);
-      ptx::tmem_wait_ld();
-      if (cidx == 3) {  // every S column of this stage has been read
-        ptx::tc_fence_before();
-        ptx::mbar_arrive(bar_addr(c, bar_s_empty(s)));
-      }
-      float pv[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float x = fmaf(__uint_as_float(a[i]), sc, __uint_as_float(b[i])) * cscale;
-        float e = valid ? ptx::ex2(x - m_s[16 * cidx + i]) : 0.f;
-        l[16 * cidx + i] += e;
-        pv[i] = e * sc;
-      }
-      uint32_t hi[4], lo[4];
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) hi[q4] = pack_e4m3x4(pv[4 * q4], pv[4 * q4 + 1], pv[4 * q4 + 2], pv[4 * q4 + 3], lo[q4]);
-      const uint32_t off = ((uint32_t(cidx) ^ psw) << 4);
-      asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(p_hi + off), "r"(hi[0]), "r"(hi[1]), "r"(hi[2]), "r"(hi[3]) : "memory");
-      asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(p_lo + off), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]) : "memory");
-    }
-    ptx::fence_proxy_async_smem();
-    ptx::tc_fence_before();  // orders the O rescale (tcgen05.st) before the arrive as well
-    ptx::mbar_arrive(bar_addr(c, bar_p_full(s)));
 
     // ---- segment epilogue
-    if (cur.last_of_segment()) {
-      // total row sums: reduce the per-token partial sums over the 128 token threads
-      float mine0 = 0.f, mine1 = 0.f;
-#pragma unroll
-      for (int h = 0; h < kGroupHeads; ++h) {
-        float v = l[h];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == (h & 31)) { if (h < 32) mine0 = v; else mine1 = v; }
-      }
-      ptx::bar_sync(1, kSoftmaxThreads);  // wred is free (column-max readers are done)
-      wred[warp * kGroupHeads + lane] = mine0;
-      wred[warp * kGroupHeads + 32 + lane] = mine1;
+    {
+      const uint32_t lit = st.it - 1;  // last tile of the segment
+      float r0, r1;
+      warp_transpose_sum64(l2, lane, r0, r1);
+      const uint32_t wred = c.smem + kOffWmax;
+      sts_f32(wred + 4 * (warp * kGroupHeads + 2 * lane), r0);
+      sts_f32(wred + 4 * (warp * kGroupHeads + 2 * lane + 1), r1);
       ptx::bar_sync(1, kSoftmaxThreads);
       if (tid < kGroupHeads) {
-        float L = (wred[tid] + wred[kGroupHeads + tid]) + (wred[2 * kGroupHeads + tid] + wred[3 * kGroupHeads + tid]);
-        linv_s[tid] = p.output_scale / L;
-        lse_s[tid] = log2f(L) + m_s[tid];
+        const float L = (lds_f32(wred + 4 * tid) + lds_f32(wred + 4 * (kGroupHeads + tid))) +
+                        (lds_f32(wred + 4 * (2 * kGroupHeads + tid)) + lds_f32(wred + 4 * (3 * kGroupHeads + tid)));
+        sts_f32(c.smem + kOffLinv + 4 * tid, p.output_scale / L);
+        sts_f32(c.smem + kOffLse + 4 * tid, __log2f(L) - lds_f32(c.smem + kOffM + 4 * tid));
       }
       ptx::bar_sync(1, kSoftmaxThreads);
-
-      int qpos, head0;
-      group_coords(cur.s.g, p.num_heads, qpos, head0);
-      const int heads_here = min(kGroupHeads, p.num_heads - head0);
-      const size_t row0 = (size_t(cur.s.b) * p.q_len + qpos) * p.num_heads + head0;
-      // wait for the PV of this (last) tile
-      wait(c, bar_kv_empty(s, 3), k & 1);
+      // wait for the PV of the last tile
+      wait(c, bar_kv_empty(lit & 1, 3), (lit >> 1) & 1);
       ptx::tc_fence_after();
-      const bool ok = !c.misc->abort;
-      if (cur.s.slot < 0) {
-#pragma unroll 1
-        for (int j = 0; j < kBlocks; ++j) {
-#pragma unroll
-          for (int cidx = 0; cidx < 4; ++cidx) {
-            uint32_t o[16];
-            ptx::tmem_ld16(tmem + lane_base + kColO + 64u * j + 16u * cidx, o);
-            ptx::tmem_wait_ld();
-            if (ok) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const int h = 16 * cidx + i;
-                if (h < heads_here)
-                  store_out_elem(p.out, p.out_dtype, (row0 + h) * kLatent + 128 * j + tid, __uint_as_float(o[i]) * linv_s[h]);
-              }
-            }
-          }
-        }
-        if (ok && p.lse && tid < heads_here) p.lse[row0 + tid] = lse_s[tid];
-      } else {
-        float* so = reinterpret_cast<float*>(p.workspace) + size_t(cur.s.slot) * kSlotFloats;
-#pragma unroll 1
-        for (int j = 0; j < kBlocks; ++j) {
-          float4* dst = reinterpret_cast<float4*>(so + size_t(128 * j + tid) * kGroupHeads);
-#pragma unroll
-          for (int cidx = 0; cidx < 4; ++cidx) {
-            uint32_t o[16];
-            ptx::tmem_ld16(tmem + lane_base + kColO + 64u * j + 16u * cidx, o);
-            ptx::tmem_wait_ld();
-            if (ok) {
-#pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4) {
-                float4 v;
-                v.x = __uint_as_float(o[4 * q4 + 0]) * linv_s[16 * cidx + 4 * q4 + 0];
-                v.y = __uint_as_float(o[4 * q4 + 1]) * linv_s[16 * cidx + 4 * q4 + 1];
-                v.z = __uint_as_float(o[4 * q4 + 2]) * linv_s[16 * cidx + 4 * q4 + 2];
-                v.w = __uint_as_float(o[4 * q4 + 3]) * linv_s[16 * cidx + 4 * q4 + 3];
-                dst[4 * cidx + q4] = v;
-              }
-            }
-          }
-        }
-        if (ok && tid < kGroupHeads) so[kSlotOFloats + tid] = lse_s[tid];
-      }
+      if (!c.misc->abort) write_output(p, c, tmem_lane, tid, g.b, g.g, g.slot);
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar_addr(c, kBarOFree));
+      if (tid == 0) MLA_TRACE(0, lit, 6);
     }
-    ++it;
   }
+}
+
+// Stage up to kMaxSeg segments of this CTA's walk into shared memory (one thread).
+__device__ __noinline__ void stage_segments(const Ctx& c) {
+  Walker w = c.misc->walker;
+  Segment* out = reinterpret_cast<Segment*>(c.smem_ptr + kOffSegs);
+  int n = 0;
+  Segment s;
+  bool more = false;
+  while (n < kMaxSeg) {
+    if (!w.next(s)) break;
+    out[n++] = s;
+  }
+  if (n == kMaxSeg) {  // is there anything left?
+    Walker probe = w;
+    more = probe.next(s);
+  }
+  c.misc->walker = w;
+  c.misc->nseg = n;
+  c.misc->more = more ? 1 : 0;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -668,6 +795,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
     if (tid == 0) {
       c.misc->walker = w;
       c.misc->abort = 0;
+      stage_segments(c);
     }
     __syncwarp();
     ptx::tmem_alloc(c.smem + kOffMisc + offsetof(Misc, tmem_base), 512);
@@ -697,26 +825,41 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = c.misc->tmem_base;
+  if (tid == 0) MLA_TRACE(3, 0u, 0);
 
-  if (warp < 4) {
-    ptx::setmaxnreg_inc<216>();
-    softmax_role(p, c, tmem, tid);
-  } else if (warp < 12) {
-    ptx::setmaxnreg_dec<96>();
-    dequant_role(p, c, tid - 128);
-  } else {
-    ptx::setmaxnreg_dec<88>();
-    if (warp == 12) {
-      if ((tid & 31) == 0) mma_role(c, tmem);
-      __syncwarp();
-    } else if (warp == 13) {
-      if ((tid & 31) == 0) tma_role(p, c, &map_q_lat, &map_q_rope, &map_rope);
+  RoleState st;
+  st.it = 0;
+  st.seg = 0;
+  // Rounds: almost always exactly one; more only when a CTA's range spans more than kMaxSeg requests.
+  for (;;) {
+    if (warp < 4) {
+      softmax_role(p, c, tmem, tid, st);
+    } else if (warp < 12) {
+      dequant_role(p, c, tid - 128, st);
+    } else if (warp == 12) {
+      mma_role(c, tmem, st);
+    } else {
+      if ((tid & 31) == 0) tma_role(p, c, &map_q_lat, &map_q_rope, &map_rope, st);
       __syncwarp();
     }
+    const int more = c.misc->more;
+    __syncthreads();  // every role is done with the staged segments
+    if (!more) break;
+    if (tid == 0) stage_segments(c);
+    __syncthreads();
   }
 
+  // drain: everything issued has completed before TMEM is released
+  if (warp == 12) {
+    if (ptx::elect_one()) {
+      ptx::umma_commit(bar_addr(c, kBarDrain));
+      drain_wait(c, kBarDrain, 0);
+    }
+    __syncwarp();
+  }
   ptx::tc_fence_before();
   __syncthreads();
+  if (tid == 0) MLA_TRACE(3, 0u, 1);
   if (warp == 0) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, 512);
@@ -730,15 +873,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
+  static EncodeTiledFn fn = [] {
     void* ptr = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
         qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  });
+      return reinterpret_cast<EncodeTiledFn>(ptr);
+    return static_cast<EncodeTiledFn>(nullptr);
+  }();
   return fn;
 }
 

@@ -1,6 +1,4 @@
 // CUDA-core kernels of the FP4 MLA decode engine:
-//   * combine_kernel       - split-KV combine (merges the partial slots of every split request,
-//                            zero-fills requests with seq_len == 0)
 //   * merge_partials_kernel- context-parallel merge of per-rank partial outputs + LSE
 //   * fp32_check_kernel    - plain-FP32 decode over the same work partition; a slow, exact-
 //                            arithmetic cross-check of the tcgen05 kernel used by tests
@@ -23,109 +21,6 @@ __device__ __forceinline__ float e4m3_to_float(uint8_t v) {
 __device__ __forceinline__ void store_out(void* out, int out_dtype, size_t idx, float v) {
   if (out_dtype == MLA_FP4_OUT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
   else reinterpret_cast<float*>(out)[idx] = v;
-}
-
-// ------------------------------------------------------------------------------------------
-// Split-KV combine.  grid = (groups * batch), block = 256.  Thread t owns dims t and t+256 of
-// all 64 heads, so slot reads are 256-byte rows and output stores are coalesced along dims.
-// ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) combine_kernel(CombineParams p) {
-#if __CUDA_ARCH__ >= 900
-  if (p.pdl) cudaGridDependencySynchronize();
-#endif
-  __shared__ float w_s[kGroupHeads];      // weight of the current slot per head
-  __shared__ float lse_max[kGroupHeads];
-  __shared__ float den[kGroupHeads];
-  __shared__ int64_t s_T;
-  __shared__ int64_t s_start;
-
-  const int v = blockIdx.x;
-  const int g = v / p.batch, b = v % p.batch;
-  const int tid = threadIdx.x;
-  if (tid < 32) {
-    int64_t T = warp_total_tiles(p.seq_lens, p.batch);
-    // flat start of request b inside one group
-    int64_t run = 0;
-    for (int i = tid; i < b; i += 32) run += tiles_of(p.seq_lens[i]);
-    for (int o = 16; o > 0; o >>= 1) run += __shfl_xor_sync(0xffffffffu, run, o);
-    if (tid == 0) { s_T = T; s_start = run; }
-  }
-  __syncthreads();
-  const int64_t T = s_T;
-  const int64_t Tt = T * p.groups;
-  const int seq = p.seq_lens[b];
-  const int tiles = tiles_of(seq);
-  int qpos, head0;
-  group_coords(g, p.num_heads, qpos, head0);
-  const int heads_here = min(kGroupHeads, p.num_heads - head0);
-  const size_t row0 = (size_t(b) * p.q_len + qpos) * p.num_heads + head0;
-
-  if (tiles == 0) {  // empty request: zeros and lse = -inf
-    for (int i = tid; i < heads_here * kLatent; i += blockDim.x) {
-      int h = i / kLatent, d = i % kLatent;
-      store_out(p.out, p.out_dtype, (row0 + h) * kLatent + d, 0.f);
-    }
-    if (p.lse && tid < heads_here) p.lse[row0 + tid] = -INFINITY;
-    return;
-  }
-  const int64_t start = int64_t(g) * T + s_start;
-  Span sp = span_of(Tt, p.num_ctas, start, tiles);
-  if (!sp.split) return;  // the decode kernel wrote the final output itself
-
-  const float* ws = reinterpret_cast<const float*>(p.workspace);
-  // pass 1: per-head max and denominator of the partial LSEs
-  if (tid < kGroupHeads) {
-    float m = -INFINITY;
-    for (int i = sp.cta_first; i <= sp.cta_last; ++i) {
-      if (cta_is_empty(Tt, p.num_ctas, i)) continue;
-      int slot = slot_in_span(Tt, p.num_ctas, i, start);
-      m = fmaxf(m, ws[size_t(slot) * kSlotFloats + kSlotOFloats + tid]);
-    }
-    float dsum = 0.f;
-    for (int i = sp.cta_first; i <= sp.cta_last; ++i) {
-      if (cta_is_empty(Tt, p.num_ctas, i)) continue;
-      int slot = slot_in_span(Tt, p.num_ctas, i, start);
-      float l = ws[size_t(slot) * kSlotFloats + kSlotOFloats + tid];
-      dsum += (l == -INFINITY) ? 0.f : exp2f(l - m);
-    }
-    lse_max[tid] = m;
-    den[tid] = dsum;
-    if (p.lse && tid < heads_here) p.lse[row0 + tid] = (dsum > 0.f) ? (log2f(dsum) + m) : -INFINITY;
-  }
-  __syncthreads();
-  // pass 2: thread owns dims (tid, tid+256) x heads [0,64): accumulate over slots.
-  // The slot layout is [dim][head], so each thread reads 64 contiguous floats per dim.
-  float acc0[kGroupHeads], acc1[kGroupHeads];
-#pragma unroll
-  for (int h = 0; h < kGroupHeads; ++h) { acc0[h] = 0.f; acc1[h] = 0.f; }
-  for (int i = sp.cta_first; i <= sp.cta_last; ++i) {
-    if (cta_is_empty(Tt, p.num_ctas, i)) continue;  // block-uniform: a CTA without tiles wrote no slot
-    int slot = slot_in_span(Tt, p.num_ctas, i, start);
-    const float* so = ws + size_t(slot) * kSlotFloats;
-    __syncthreads();
-    if (tid < kGroupHeads) {
-      float l = so[kSlotOFloats + tid];
-      w_s[tid] = (l == -INFINITY || den[tid] <= 0.f) ? 0.f : exp2f(l - lse_max[tid]) / den[tid];
-    }
-    __syncthreads();
-    const float4* r0 = reinterpret_cast<const float4*>(so + size_t(tid) * kGroupHeads);
-    const float4* r1 = reinterpret_cast<const float4*>(so + size_t(tid + 256) * kGroupHeads);
-#pragma unroll
-    for (int h4 = 0; h4 < kGroupHeads / 4; ++h4) {
-      float4 a = r0[h4], c = r1[h4];
-      acc0[4 * h4 + 0] += w_s[4 * h4 + 0] * a.x; acc0[4 * h4 + 1] += w_s[4 * h4 + 1] * a.y;
-      acc0[4 * h4 + 2] += w_s[4 * h4 + 2] * a.z; acc0[4 * h4 + 3] += w_s[4 * h4 + 3] * a.w;
-      acc1[4 * h4 + 0] += w_s[4 * h4 + 0] * c.x; acc1[4 * h4 + 1] += w_s[4 * h4 + 1] * c.y;
-      acc1[4 * h4 + 2] += w_s[4 * h4 + 2] * c.z; acc1[4 * h4 + 3] += w_s[4 * h4 + 3] * c.w;
-    }
-  }
-#pragma unroll
-  for (int h = 0; h < kGroupHeads; ++h) {
-    if (h < heads_here) {
-      store_out(p.out, p.out_dtype, (row0 + h) * kLatent + tid, acc0[h]);
-      store_out(p.out, p.out_dtype, (row0 + h) * kLatent + tid + 256, acc1[h]);
-    }
-  }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -322,20 +217,6 @@ __global__ void dequant_kernel(const uint32_t* __restrict__ in, uint2* __restric
 }
 
 // ------------------------------------------------------------------------------------------ launchers
-
-cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream) {
-  if (p.batch * p.groups == 0) return cudaSuccess;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(p.batch * p.groups);
-  cfg.blockDim = dim3(256);
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = p.pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, combine_kernel, p);
-}
 
 cudaError_t launch_merge_partials(const float* po, const float* pl, int parts, int64_t rows, int64_t stride_o,
                                   int64_t stride_l, void* out, int out_dtype, float* lse, cudaStream_t stream) {

@@ -97,6 +97,15 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 
+// One lane of a converged warp is elected; the others get false.  tcgen05.mma operands live in
+// uniform registers, so the issuing code must stay warp-uniform and only the instruction itself
+// sits under the election: a loop run by a single diverged lane issues 1.5-4x slower.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
 // ---------------------------------------------------------------- UMMA
 // D[tmem] (+)= A[smem desc] * B[smem desc]; kind::f8f6f4, one CTA.  accumulate == 0 overwrites D.
 __device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
