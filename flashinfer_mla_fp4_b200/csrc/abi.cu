@@ -115,6 +115,7 @@ int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
     int rc = sm_count(&num_ctas);
     if (rc) return rc;
   }
+  if (num_ctas > mla::kMaxCombineSlots) return fail(MLA_FP4_ERR_UNSUPPORTED, "num_ctas must be <= 148");
   size_t need = size_t(2) * size_t(num_ctas) * mla::kSlotBytes;
   if (!a->workspace || a->workspace_bytes < need) {
     char buf[160];

@@ -1,26 +1,28 @@
 // Split-KV combine: merges the partial slots of every request that the decode kernel split
 // across CTAs, and zero-fills requests with seq_len == 0.
 //
-// grid = (512 / 32 dim chunks, groups * batch), block = 256.  A CTA owns 32 output dims of the
+// grid = (512 / 16 dim chunks, groups * batch), block = 256.  A CTA owns 16 output dims of the
 // 64 heads of one (request, head group).  It re-derives which CTAs touched the request from the
-// same partition arithmetic the decode kernel used, reads their slots ([dim][head] f32 + 64
-// base-2 LSEs) and accumulates  sum_i exp2(lse_i - max) / den * O_i .
+// same partition arithmetic the decode kernel used, reads their slots ([dim][head] fp16 + 64
+// base-2 LSEs) and accumulates  sum_i exp2(lse_i - max) / den * O_i ; its 8 warps split the slots.
 #include "common.cuh"
 #include "launch.h"
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 namespace mla {
 
 namespace {
-constexpr int kCombDims = 32;
+constexpr int kCombDims = 16;
 constexpr int kCombThreads = 256;
 }
 
 __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) {
-  __shared__ float lse_max[kGroupHeads];
-  __shared__ float inv_den[kGroupHeads];
+  __shared__ float lse_s[kMaxCombineSlots][kGroupHeads];  // LSE of every slot of the request, then its weight
   __shared__ float tile[kGroupHeads][kCombDims + 1];
+  __shared__ int slot_list[kMaxCombineSlots];
+  __shared__ int n_slots;
   __shared__ int64_t s_T;
   __shared__ int64_t s_start;
 
@@ -44,17 +46,15 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
   const int heads_here = min(kGroupHeads, p.num_heads - head0);
   const size_t row0 = (size_t(b) * p.q_len + qpos) * p.num_heads + head0;
   const int h_out = tid >> 2;             // output phase: head
-  const int d_out = (tid & 3) * 8;        // output phase: 8 consecutive dims of the chunk
+  const int d_out = (tid & 3) * 4;        // output phase: 4 consecutive dims of the chunk
   const size_t out_idx = (row0 + h_out) * kLatent + size_t(dchunk) * kCombDims + d_out;
 
   if (tiles == 0) {  // empty request: zeros and lse = -inf
     if (h_out < heads_here) {
       if (p.out_dtype == MLA_FP4_OUT_BF16) {
-        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + out_idx) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + out_idx) = make_uint2(0u, 0u);
       } else {
-        float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + out_idx);
-        o[0] = make_float4(0.f, 0.f, 0.f, 0.f);
-        o[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + out_idx) = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
     if (dchunk == 0 && p.lse && tid < heads_here) p.lse[row0 + tid] = -INFINITY;
@@ -64,65 +64,98 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
   const Span sp = span_of(Tt, p.num_ctas, start, tiles);
   if (!sp.split) return;  // the decode kernel wrote the final output itself
 
+  // slots of this request, computed once (the partition arithmetic is 64-bit division heavy)
+  if (tid < 32) {
+    int n = 0;
+    for (int base = sp.cta_first; base <= sp.cta_last; base += 32) {
+      const int i = base + tid;
+      const bool live = i <= sp.cta_last && !cta_is_empty(Tt, p.num_ctas, i);
+      const unsigned m = __ballot_sync(0xffffffffu, live);
+      if (live) {
+        const int pos = n + __popc(m & ((1u << tid) - 1u));
+        if (pos < kMaxCombineSlots) slot_list[pos] = slot_in_span(Tt, p.num_ctas, i, start);
+      }
+      n += __popc(m);
+    }
+    if (tid == 0) n_slots = min(n, kMaxCombineSlots);
+  }
+  for (int i = tid; i < kGroupHeads * (kCombDims + 1); i += kCombThreads) (&tile[0][0])[i] = 0.f;
 #if __CUDA_ARCH__ >= 900
   if (p.pdl) cudaGridDependencySynchronize();  // from here on the decode kernel's slots are read
 #endif
-  const float* ws = reinterpret_cast<const float*>(p.workspace);
+  __syncthreads();
+  const int ns = n_slots;
+  const void* ws = p.workspace;
+  // all LSEs of the request in one round of independent loads
+  for (int idx = tid; idx < ns * kGroupHeads; idx += kCombThreads) {
+    const int i = idx >> 6, h = idx & 63;
+    lse_s[i][h] = slot_lse(ws, slot_list[i])[h];
+  }
+  __syncthreads();
   if (tid < kGroupHeads) {
     float m = -INFINITY;
-    for (int i = sp.cta_first; i <= sp.cta_last; ++i) {
-      if (cta_is_empty(Tt, p.num_ctas, i)) continue;
-      m = fmaxf(m, ws[size_t(slot_in_span(Tt, p.num_ctas, i, start)) * kSlotFloats + kSlotOFloats + tid]);
-    }
+    for (int i = 0; i < ns; ++i) m = fmaxf(m, lse_s[i][tid]);
     float dsum = 0.f;
-    for (int i = sp.cta_first; i <= sp.cta_last; ++i) {
-      if (cta_is_empty(Tt, p.num_ctas, i)) continue;
-      float l = ws[size_t(slot_in_span(Tt, p.num_ctas, i, start)) * kSlotFloats + kSlotOFloats + tid];
+    for (int i = 0; i < ns; ++i) {
+      const float l = lse_s[i][tid];
       dsum += (l == -INFINITY) ? 0.f : exp2f(l - m);
     }
-    lse_max[tid] = m;
-    inv_den[tid] = dsum > 0.f ? 1.f / dsum : 0.f;
+    const float inv = dsum > 0.f ? 1.f / dsum : 0.f;
+    for (int i = 0; i < ns; ++i) {  // the LSEs become the weights (times the slot's fp16 scale)
+      const float l = lse_s[i][tid];
+      lse_s[i][tid] = (l == -INFINITY) ? 0.f : exp2f(l - m) * inv * slot_scale(ws, slot_list[i])[0];
+    }
     if (dchunk == 0 && p.lse && tid < heads_here) p.lse[row0 + tid] = (dsum > 0.f) ? (log2f(dsum) + m) : -INFINITY;
   }
   __syncthreads();
 
-  // accumulate: thread = 4 heads (h4) x 2 dims (dsub, dsub + 16) of the chunk
-  const int h4 = tid & 15, dsub = tid >> 4;
-  const float4 mx = *reinterpret_cast<const float4*>(&lse_max[4 * h4]);
-  const float4 iv = *reinterpret_cast<const float4*>(&inv_den[4 * h4]);
-  float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
-  for (int i = sp.cta_first; i <= sp.cta_last; ++i) {
-    if (cta_is_empty(Tt, p.num_ctas, i)) continue;
-    const float* so = ws + size_t(slot_in_span(Tt, p.num_ctas, i, start)) * kSlotFloats;
-    const float4 l = *reinterpret_cast<const float4*>(so + kSlotOFloats + 4 * h4);
-    float4 w;
-    w.x = (l.x == -INFINITY) ? 0.f : exp2f(l.x - mx.x) * iv.x;
-    w.y = (l.y == -INFINITY) ? 0.f : exp2f(l.y - mx.y) * iv.y;
-    w.z = (l.z == -INFINITY) ? 0.f : exp2f(l.z - mx.z) * iv.z;
-    w.w = (l.w == -INFINITY) ? 0.f : exp2f(l.w - mx.w) * iv.w;
-    const float4 a = *reinterpret_cast<const float4*>(so + size_t(dchunk * kCombDims + dsub) * kGroupHeads + 4 * h4);
-    const float4 c = *reinterpret_cast<const float4*>(so + size_t(dchunk * kCombDims + dsub + 16) * kGroupHeads + 4 * h4);
-    acc0.x += w.x * a.x; acc0.y += w.y * a.y; acc0.z += w.z * a.z; acc0.w += w.w * a.w;
-    acc1.x += w.x * c.x; acc1.y += w.y * c.y; acc1.z += w.z * c.z; acc1.w += w.w * c.w;
+  // accumulate: the 8 warps split the slots; a lane owns 8 heads (h8) x 4 dims (dq, dq+4, dq+8, dq+12),
+  // i.e. 4 independent 16-byte loads (8 fp16 each) per slot
+  const int warp = tid >> 5, lane = tid & 31;
+  const int h8 = lane & 7, dq = lane >> 3;
+  float acc[kCombDims / 4][8];
+#pragma unroll
+  for (int q = 0; q < kCombDims / 4; ++q)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[q][e] = 0.f;
+#pragma unroll 4
+  for (int i = warp; i < ns; i += kCombThreads / 32) {
+    const uint16_t* so = slot_o(ws, slot_list[i]);
+    const float4 w0 = *reinterpret_cast<const float4*>(&lse_s[i][8 * h8]);
+    const float4 w1 = *reinterpret_cast<const float4*>(&lse_s[i][8 * h8 + 4]);
+    const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    const uint16_t* row = so + size_t(dchunk * kCombDims + dq) * kGroupHeads + 8 * h8;
+#pragma unroll
+    for (int q = 0; q < kCombDims / 4; ++q) {
+      const uint4 a = *reinterpret_cast<const uint4*>(row + size_t(4 * q) * kGroupHeads);
+      const uint32_t u[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u[e]));
+        acc[q][2 * e] += w[2 * e] * f.x;
+        acc[q][2 * e + 1] += w[2 * e + 1] * f.y;
+      }
+    }
   }
-  tile[4 * h4 + 0][dsub] = acc0.x; tile[4 * h4 + 1][dsub] = acc0.y;
-  tile[4 * h4 + 2][dsub] = acc0.z; tile[4 * h4 + 3][dsub] = acc0.w;
-  tile[4 * h4 + 0][dsub + 16] = acc1.x; tile[4 * h4 + 1][dsub + 16] = acc1.y;
-  tile[4 * h4 + 2][dsub + 16] = acc1.z; tile[4 * h4 + 3][dsub + 16] = acc1.w;
-  __syncthreads();
+  // fixed-order reduction over the warps (bit-reproducible from run to run)
+  for (int wsel = 0; wsel < kCombThreads / 32; ++wsel) {
+    if (warp == wsel) {
+#pragma unroll
+      for (int q = 0; q < kCombDims / 4; ++q)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) tile[8 * h8 + e][4 * q + dq] += acc[q][e];
+    }
+    __syncthreads();
+  }
   if (h_out < heads_here) {
     const float* t = &tile[h_out][d_out];
     if (p.out_dtype == MLA_FP4_OUT_BF16) {
       __nv_bfloat162 v0 = __floats2bfloat162_rn(t[0], t[1]), v1 = __floats2bfloat162_rn(t[2], t[3]);
-      __nv_bfloat162 v2 = __floats2bfloat162_rn(t[4], t[5]), v3 = __floats2bfloat162_rn(t[6], t[7]);
-      uint4 pk;
+      uint2 pk;
       pk.x = *reinterpret_cast<uint32_t*>(&v0); pk.y = *reinterpret_cast<uint32_t*>(&v1);
-      pk.z = *reinterpret_cast<uint32_t*>(&v2); pk.w = *reinterpret_cast<uint32_t*>(&v3);
-      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + out_idx) = pk;
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + out_idx) = pk;
     } else {
-      float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + out_idx);
-      o[0] = make_float4(t[0], t[1], t[2], t[3]);
-      o[1] = make_float4(t[4], t[5], t[6], t[7]);
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + out_idx) = make_float4(t[0], t[1], t[2], t[3]);
     }
   }
 }

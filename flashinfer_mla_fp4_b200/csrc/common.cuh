@@ -20,11 +20,24 @@ constexpr int kTile = MLA_FP4_TILE_TOKENS;         // 128 KV tokens per tile
 constexpr int kGroupHeads = MLA_FP4_GROUP_HEADS;   // 64 query heads per CTA
 constexpr float kLog2e = 1.4426950408889634f;
 
-// Split-KV partial slot in the workspace: normalised O as f32 [512 dims][64 heads] followed by
-// the base-2 LSE of the 64 heads.
-constexpr size_t kSlotOFloats = size_t(kLatent) * kGroupHeads;
-constexpr size_t kSlotFloats = kSlotOFloats + kGroupHeads;
-constexpr size_t kSlotBytes = kSlotFloats * sizeof(float);
+// Split-KV partial slot in the workspace: normalised O as fp16 [512 dims][64 heads] divided by a
+// per-slot scale, then the base-2 LSE of the 64 heads as f32, then that scale (f32, padded to 16 B).
+// The scale is 6 * max|token scale| * |output_scale| / 32768 rounded up to a power of two: an
+// upper bound of |O| mapped below the fp16 maximum, so the 11-bit partials can neither overflow nor
+// lose the small values (fp16 spans 29 binades below that bound).  Half the bytes of f32 partials.
+constexpr size_t kSlotOBytes = size_t(kLatent) * kGroupHeads * 2;
+constexpr size_t kSlotBytes = kSlotOBytes + kGroupHeads * sizeof(float) + 16;
+constexpr float kSlotHalfRange = 32768.f;
+MLA_HD uint16_t* slot_o(void* ws, int slot) { return reinterpret_cast<uint16_t*>(static_cast<char*>(ws) + size_t(slot) * kSlotBytes); }
+MLA_HD float* slot_lse(void* ws, int slot) { return reinterpret_cast<float*>(static_cast<char*>(ws) + size_t(slot) * kSlotBytes + kSlotOBytes); }
+MLA_HD const uint16_t* slot_o(const void* ws, int slot) { return reinterpret_cast<const uint16_t*>(static_cast<const char*>(ws) + size_t(slot) * kSlotBytes); }
+MLA_HD float* slot_scale(void* ws, int slot) { return slot_lse(ws, slot) + kGroupHeads; }
+MLA_HD const float* slot_lse(const void* ws, int slot) { return reinterpret_cast<const float*>(static_cast<const char*>(ws) + size_t(slot) * kSlotBytes + kSlotOBytes); }
+MLA_HD const float* slot_scale(const void* ws, int slot) { return slot_lse(ws, slot) + kGroupHeads; }
+// power-of-two scale that maps `bound` (an upper bound of |O|) to at most kSlotHalfRange
+MLA_HD float slot_scale_for(float bound) { return exp2f(ceilf(log2f(fmaxf(bound, 1e-30f) / kSlotHalfRange))); }
+// A request can be split over at most this many CTAs (= the largest decode grid accepted).
+constexpr int kMaxCombineSlots = 148;
 
 // ----------------------------------------------------------------------------------------------
 // Work partition.

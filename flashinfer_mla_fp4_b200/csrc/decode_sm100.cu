@@ -15,8 +15,9 @@
 // into 128-byte-swizzled shared memory, where the very same bytes serve as the K-major A operand
 // of QK^T and as the MN-major A operand of PV.  RoPE bytes, per-token scales and Q arrive by TMA.
 //
-// Warp roles (448 threads): 0-3 softmax / O rescale / epilogue (TMEM lane = token or dim),
-// 4-11 latent load + dequant, 12 MMA issue (warp-uniform, one elected lane per instruction), 13 TMA issue.
+// Warp roles (576 threads): 0-7 softmax / O rescale / epilogue (TMEM lane = token or dim; two warps
+// share a lane quarter and split the 64 heads), 8-15 latent load + dequant, 16 MMA issue (warp-uniform,
+// one elected lane per instruction), 17 TMA issue.
 //
 // The per-role loops are kept small on purpose: the four instruction streams share one
 // instruction cache, and an MMA-issue or softmax loop that misses it starves the tensor pipe.
@@ -37,8 +38,8 @@ namespace mla {
 
 namespace {
 
-constexpr int kThreads = 448;
-constexpr int kSoftmaxThreads = 128;
+constexpr int kThreads = 576;           // 18 warps: five per scheduler, hence at most 96 registers per thread
+constexpr int kSoftmaxThreads = 256;   // 8 warps: warp w works on TMEM lanes 32*(w%4).. and heads 32*(w/4)..
 constexpr int kDequantThreads = 256;
 constexpr int kDequantWarps = kDequantThreads / 32;
 constexpr int kStages = 2;
@@ -60,7 +61,8 @@ constexpr uint32_t kOffF = kOffM + kGroupHeads * 4;                       // [64
 constexpr uint32_t kOffWmax = kOffF + kGroupHeads * 4;                    // [4][64] f32 per-warp column max / sum
 constexpr uint32_t kOffLinv = kOffWmax + 4 * kGroupHeads * 4;             // [64] f32 output_scale / l
 constexpr uint32_t kOffLse = kOffLinv + kGroupHeads * 4;                  // [64] f32
-constexpr uint32_t kOffBars = kOffLse + kGroupHeads * 4;                  // mbarriers (8 B each)
+constexpr uint32_t kOffScMax = kOffLse + kGroupHeads * 4;                 // [8] f32 per-warp largest token scale
+constexpr uint32_t kOffBars = kOffScMax + 8 * 4;                          // mbarriers (8 B each)
 constexpr int kNumBars = 2 * 4 /*kv_full*/ + 2 * 4 /*kv_empty*/ + 2 /*aux_full*/ + 2 /*s_full*/ + 2 /*s_empty*/ +
                          2 /*p_full*/ + 1 /*q_full*/ + 1 /*q_empty*/ + 1 /*o_free*/ + 1 /*drain*/;
 constexpr uint32_t kOffSegs = kOffBars + kNumBars * 8;                    // Segment[kMaxSeg]
@@ -193,37 +195,36 @@ __device__ __forceinline__ void store32(const E4m3x32& r, uint32_t dst_a, uint32
 }
 
 // Row pointers of this thread's two tokens (r0 and r0 + 64) of tile t of a segment; nullptr beyond seq_len.
-__device__ __forceinline__ void row_sources(const DecodeParams& p, const Segment& sg, int t, int r0, const uint8_t*& p0,
-                                         const uint8_t*& p1) {
+__device__ __forceinline__ void row_sources(const DecodeParams& p, const Segment& sg, int t, int r0, const uint8_t* (&ptr)[2]) {
   const uint8_t* cache = reinterpret_cast<const uint8_t*>(p.kv_cache);
-  const int tok0 = t * kTile + r0, tok1 = tok0 + 64;
-  p0 = nullptr;
-  p1 = nullptr;
   const int32_t* bt = p.block_tables + size_t(sg.b) * p.block_table_stride;
-  if (tok0 < sg.seq_len) p0 = cache + (size_t(__ldg(bt + tok0 / p.page_size)) * p.page_size + tok0 % p.page_size) * kRowBytes;
-  if (tok1 < sg.seq_len) p1 = cache + (size_t(__ldg(bt + tok1 / p.page_size)) * p.page_size + tok1 % p.page_size) * kRowBytes;
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int tok = t * kTile + r0 + 64 * u;
+    ptr[u] = nullptr;
+    if (tok < sg.seq_len) ptr[u] = cache + (size_t(__ldg(bt + tok / p.page_size)) * p.page_size + tok % p.page_size) * kRowBytes;
+  }
 }
 
 __device__ __forceinline__ void dequant_role(const DecodeParams& p, const Ctx& c, int dtid, RoleState& st) {
   const int nseg = c.misc->nseg;
   if (nseg == 0) return;
   const Segment* sg = segs(c);
-  const int r0 = dtid >> 2;    // 0..63, second row is r0 + 64
+  const int r0 = dtid >> 2;    // 0..63; this thread's rows are r0 and r0 + 64
   const int ch = dtid & 3;     // 16-byte packed chunk inside the 64-byte slice of a block
   const int lane = dtid & 31;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
   int si = 0, t = sg[0].tile_begin;
-  const uint8_t *p0, *p1;
-  row_sources(p, sg[0], t, r0, p0, p1);
+  const uint8_t* src[2];
+  row_sources(p, sg[0], t, r0, src);
   uint4 regs[kBlocks][2];
 #pragma unroll
-  for (int j = 0; j < kBlocks; ++j) {
-    regs[j][0] = p0 ? ldg_nc(p0 + 64 * j + 16 * ch) : zero;
-    regs[j][1] = p1 ? ldg_nc(p1 + 64 * j + 16 * ch) : zero;
-  }
-  // swizzled destinations inside a block: row*128 + ((2*ch + e) ^ (row & 7)) * 16
-  const uint32_t sw0 = uint32_t(r0 & 7);  // (r0 + 64) & 7 is the same
+  for (int j = 0; j < kBlocks; ++j)
+#pragma unroll
+    for (int u = 0; u < 2; ++u) regs[j][u] = src[u] ? ldg_nc(src[u] + 64 * j + 16 * ch) : zero;
+  // swizzled destinations inside a block: row*128 + ((2*ch + e) ^ (row & 7)) * 16; (r0 + 64) & 7 == r0 & 7
+  const uint32_t sw0 = uint32_t(r0 & 7);
   const uint32_t off_a = uint32_t(r0) * 128u + ((uint32_t(2 * ch) ^ sw0) << 4);
   const uint32_t off_b = uint32_t(r0) * 128u + ((uint32_t(2 * ch + 1) ^ sw0) << 4);
 
@@ -238,7 +239,7 @@ __device__ __forceinline__ void dequant_role(const DecodeParams& p, const Ctx& c
       more = nsi < nseg;
       if (more) nt = sg[nsi].tile_begin;
     }
-    if (more) row_sources(p, sg[nsi], nt, r0, p0, p1);
+    if (more) row_sources(p, sg[nsi], nt, r0, src);
     if (dtid == 0) MLA_TRACE(1, it, 0);
 #pragma unroll
     for (int j = 0; j < kBlocks; ++j) {
@@ -254,8 +255,8 @@ __device__ __forceinline__ void dequant_role(const DecodeParams& p, const Ctx& c
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar_addr(c, bar_kv_full(s, j)));
       if (more) {
-        regs[j][0] = p0 ? ldg_nc(p0 + 64 * j + 16 * ch) : zero;
-        regs[j][1] = p1 ? ldg_nc(p1 + 64 * j + 16 * ch) : zero;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) regs[j][u] = src[u] ? ldg_nc(src[u] + 64 * j + 16 * ch) : zero;
       }
     }
     if (dtid == 0) MLA_TRACE(1, it, 5);
@@ -267,7 +268,7 @@ __device__ __forceinline__ void dequant_role(const DecodeParams& p, const Ctx& c
 }
 
 // ------------------------------------------------------------------------------------------
-// role: TMA issue (warp 13, one lane): Q per segment; RoPE bytes + scales per tile
+// role: TMA issue (warp 17, one lane): Q per segment; RoPE bytes + scales per tile
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_role(const DecodeParams& p, const Ctx& c, const CUtensorMap* map_q_lat,
                                          const CUtensorMap* map_q_rope, const CUtensorMap* map_rope, RoleState& st) {
@@ -323,7 +324,7 @@ __device__ __forceinline__ void tma_role(const DecodeParams& p, const Ctx& c, co
 }
 
 // ------------------------------------------------------------------------------------------
-// role: MMA issue (warp 12).  The whole warp runs this code with uniform control flow; only the
+// role: MMA issue (warp 16).  The whole warp runs this code with uniform control flow; only the
 // tcgen05 instructions sit under elect_one(), so their operands stay in uniform registers.
 // ------------------------------------------------------------------------------------------
 // Descriptors of every operand, built once: the per-instruction work is one 32-bit add.
@@ -392,8 +393,9 @@ __device__ __forceinline__ void issue_pv(const Ctx& c, const MmaDescs& d, uint32
 #pragma unroll
       for (uint32_t ks = 0; ks < 4; ++ks) {
         // B = P^T: MN-major (64 heads contiguous), 64-byte swizzle; 32 tokens per step = 2048 B
-        ptx::umma_f8(dd, ad + 256 * ks, p_hi + 128 * ks, kIdescPV, ks ? 1u : acc0);
-        ptx::umma_f8(dd, ad + 256 * ks, p_lo + 128 * ks, kIdescPV, 1u);
+        // the hi and the lo term share A: it is fetched once and kept in the collector for the second
+        ptx::umma_f8_a_fill(dd, ad + 256 * ks, p_hi + 128 * ks, kIdescPV, ks ? 1u : acc0);
+        ptx::umma_f8_a_lastuse(dd, ad + 256 * ks, p_lo + 128 * ks, kIdescPV, 1u);
       }
       ptx::umma_commit(bar_addr(c, bar_kv_empty(s, j)));
     }
@@ -482,14 +484,14 @@ __device__ __forceinline__ uint32_t split_e4m3x2(uint64_t v2, uint32_t& lo) {
   return hi;
 }
 
-// Sum over the 32 lanes of 64 per-lane values held as 32 pairs; lane L ends with the totals of
-// heads 2L and 2L+1.
-__device__ __forceinline__ void warp_transpose_sum64(uint64_t (&l2)[kGroupHeads / 2], int lane, float& r0, float& r1) {
-  float v[kGroupHeads];
+// Sum over the 32 lanes of 32 per-lane values held as 16 pairs; lane L ends with the total of value L.
+constexpr int kHalfHeads = kGroupHeads / 2;  // heads per softmax warp
+__device__ __forceinline__ float warp_transpose_sum32(uint64_t (&l2)[kHalfHeads / 2], int lane) {
+  float v[kHalfHeads];
 #pragma unroll
-  for (int i = 0; i < kGroupHeads / 2; ++i) unpack2(l2[i], v[2 * i], v[2 * i + 1]);
+  for (int i = 0; i < kHalfHeads / 2; ++i) unpack2(l2[i], v[2 * i], v[2 * i + 1]);
 #pragma unroll
-  for (int o = 16, n = kGroupHeads; o > 0; o >>= 1, n >>= 1) {
+  for (int o = 16, n = kHalfHeads; o > 0; o >>= 1, n >>= 1) {
     const bool up = (lane & o) != 0;
 #pragma unroll
     for (int i = 0; i < n / 2; ++i) {
@@ -498,31 +500,31 @@ __device__ __forceinline__ void warp_transpose_sum64(uint64_t (&l2)[kGroupHeads 
       v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
     }
   }
-  r0 = v[0];
-  r1 = v[1];
+  return v[0];
 }
 
 struct SoftmaxTile {
   uint32_t t_lat, t_rope;  // TMEM addresses of this thread's lane, S columns of the stage
-  uint32_t negm;           // shared address of the 64 negated references (-m)
+  uint32_t negm;           // shared address of the negated references (-m) of this warp's 32 heads
   uint32_t p_hi, p_lo;     // shared addresses of this thread's P' rows
   uint32_t psw;            // swizzle term of the row
+  uint32_t half;           // which 32 heads this warp owns
   uint64_t sc2, cs2;       // (scale_t, scale_t), (c, c)
   bool valid;
 };
 
-// One pass over the 64 heads of this thread's token: e = exp2(x*c - m), l += acc * e, and
+// One pass over the 32 heads this thread owns of its token: e = exp2(x*c - m), l += acc * e, and
 // P' = e*scale_t split into two E4M3 terms and written to the swizzled P rows.  Returns the
 // largest exponent argument seen (for the lazy-reference check).
-__device__ __forceinline__ float softmax_pass(const SoftmaxTile& t, uint64_t (&l2)[kGroupHeads / 2], uint64_t acc2) {
+__device__ __forceinline__ float softmax_pass(const SoftmaxTile& t, uint64_t (&l2)[kHalfHeads / 2], uint64_t acc2) {
   float mx = -INFINITY;
 #pragma unroll
-  for (int cidx = 0; cidx < 4; ++cidx) {
+  for (int cidx = 0; cidx < 2; ++cidx) {
     uint32_t a[16], b[16];
     ptx::tmem_ld16(t.t_lat + 16 * cidx, a);
     ptx::tmem_ld16(t.t_rope + 16 * cidx, b);
     ptx::tmem_wait_ld();
-    const uint32_t off = ((uint32_t(cidx) ^ t.psw) << 4);
+    const uint32_t off = (((2 * t.half + uint32_t(cidx)) ^ t.psw) << 4);
     if (t.valid) {
       uint32_t hi16[8], lo16[8];
 #pragma unroll
@@ -559,9 +561,10 @@ __device__ __forceinline__ float softmax_pass(const SoftmaxTile& t, uint64_t (&l
 __device__ __noinline__ void refresh_reference(const Ctx& c, uint32_t t_lat, uint32_t t_rope, float sc, bool valid,
                                                float cscale, float lg, bool have_m, int tid) {
   const int warp = tid >> 5, lane = tid & 31;
+  const int quarter = warp & 3, half = warp >> 2;  // t_lat / t_rope already point at this warp's 32 columns
   const uint32_t wred = c.smem + kOffWmax;
 #pragma unroll 1
-  for (int cidx = 0; cidx < 4; ++cidx) {
+  for (int cidx = 0; cidx < 2; ++cidx) {
     uint32_t a[16], b[16];
     ptx::tmem_ld16(t_lat + 16 * cidx, a);
     ptx::tmem_ld16(t_rope + 16 * cidx, b);
@@ -573,7 +576,7 @@ __device__ __noinline__ void refresh_reference(const Ctx& c, uint32_t t_lat, uin
       const float r = ptx::redux_max_f32(valid ? y : -INFINITY);
       if ((lane & 15) == i) mine = r;
     }
-    if (lane < 16) sts_f32(wred + 4 * (warp * kGroupHeads + 16 * cidx + lane), mine);
+    if (lane < 16) sts_f32(wred + 4 * (quarter * kGroupHeads + 32 * half + 16 * cidx + lane), mine);
   }
   ptx::bar_sync(1, kSoftmaxThreads);
   if (tid < kGroupHeads) {
@@ -588,14 +591,15 @@ __device__ __noinline__ void refresh_reference(const Ctx& c, uint32_t t_lat, uin
 }
 
 // O^T *= f per head column, in TMEM (all four 128-dim blocks of this thread's lane)
-__device__ __noinline__ void rescale_output(const Ctx& c, uint32_t tmem_lane) {
+__device__ __noinline__ void rescale_output(const Ctx& c, uint32_t tmem_lane, uint32_t half) {
 #pragma unroll 1
-  for (int jc = 0; jc < kBlocks * 4; ++jc) {
+  for (int jc = 0; jc < kBlocks * 2; ++jc) {
     uint32_t o[16];
-    const uint32_t ta = tmem_lane + kColO + 16u * jc;
+    const uint32_t col = 64u * (jc >> 1) + 32u * half + 16u * (jc & 1);
+    const uint32_t ta = tmem_lane + kColO + col;
     ptx::tmem_ld16(ta, o);
     ptx::tmem_wait_ld();
-    const uint32_t f = c.smem + kOffF + 64 * (jc & 3);
+    const uint32_t f = c.smem + kOffF + 4 * (col & 63);
 #pragma unroll
     for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * lds_f32(f + 4 * i));
     ptx::tmem_st16(ta, o);
@@ -604,29 +608,36 @@ __device__ __noinline__ void rescale_output(const Ctx& c, uint32_t tmem_lane) {
 }
 
 // Normalise O^T and write it: to the output tensor (slot < 0) or to a split-KV partial slot.
-__device__ __noinline__ void write_output(const DecodeParams& p, const Ctx& c, uint32_t tmem_lane, int tid, int b, int g,
-                                          int slot) {
+__device__ __noinline__ void write_output(const DecodeParams& p, const Ctx& c, uint32_t tmem_lane, int row, int half,
+                                          int tid, int b, int g, int slot, float slot_scale_v) {
   int qpos, head0;
   group_coords(g, p.num_heads, qpos, head0);
   const int heads_here = min(kGroupHeads, p.num_heads - head0);
   const size_t row0 = (size_t(b) * p.q_len + qpos) * p.num_heads + head0;
   const bool direct = slot < 0;
-  float* so = reinterpret_cast<float*>(p.workspace) + size_t(direct ? 0 : slot) * kSlotFloats;
+  __half* so = reinterpret_cast<__half*>(slot_o(p.workspace, direct ? 0 : slot));
+  const float inv_slot_scale = 1.f / slot_scale_v;
   const uint32_t linv = c.smem + kOffLinv;
 #pragma unroll 1
-  for (int jc = 0; jc < kBlocks * 4; ++jc) {
+  for (int jc = 0; jc < kBlocks * 2; ++jc) {
     uint32_t o[16];
-    ptx::tmem_ld16(tmem_lane + kColO + 16u * jc, o);
+    const int h0 = 32 * half + 16 * (jc & 1);
+    ptx::tmem_ld16(tmem_lane + kColO + 64u * (jc >> 1) + uint32_t(h0), o);
     ptx::tmem_wait_ld();
-    const int h0 = 16 * (jc & 3);
-    const int dim = 128 * (jc >> 2) + tid;
+    const int dim = 128 * (jc >> 1) + row;
     float v[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(o[i]) * lds_f32(linv + 4 * (h0 + i));
     if (!direct) {
-      float4* dst = reinterpret_cast<float4*>(so + size_t(dim) * kGroupHeads + h0);
+      uint32_t pk[8];
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_float4(v[4 * q4], v[4 * q4 + 1], v[4 * q4 + 2], v[4 * q4 + 3]);
+      for (int q = 0; q < 8; ++q) {
+        __half2 h2 = __floats2half2_rn(v[2 * q] * inv_slot_scale, v[2 * q + 1] * inv_slot_scale);
+        pk[q] = *reinterpret_cast<uint32_t*>(&h2);
+      }
+      uint4* dst = reinterpret_cast<uint4*>(so + size_t(dim) * kGroupHeads + h0);
+      dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
     } else if (p.out_dtype == MLA_FP4_OUT_BF16) {
       __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (row0 + h0) * kLatent + dim;
 #pragma unroll
@@ -643,7 +654,8 @@ __device__ __noinline__ void write_output(const DecodeParams& p, const Ctx& c, u
   if (direct) {
     if (p.lse && tid < heads_here) p.lse[row0 + tid] = lse;
   } else if (tid < kGroupHeads) {
-    so[kSlotOFloats + tid] = lse;
+    slot_lse(p.workspace, slot)[tid] = lse;
+    if (tid == 0) slot_scale(p.workspace, slot)[0] = slot_scale_v;
   }
 }
 
@@ -651,20 +663,25 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
   const int nseg = c.misc->nseg;
   const Segment* sg = segs(c);
   const int warp = tid >> 5, lane = tid & 31;
-  const uint32_t tmem_lane = tmem + ((uint32_t(warp) * 32u) << 16);
+  const int quarter = warp & 3;           // TMEM lane quarter this warp may access
+  const int half = warp >> 2;             // heads [32*half, 32*half + 32)
+  const int row = quarter * 32 + lane;    // token of the tile (S) / dim of the block (O) of this thread
+  const uint32_t tmem_lane = tmem + ((uint32_t(quarter) * 32u) << 16);
   const float cscale = p.softmax_scale * kLog2e;
   const uint64_t one2 = pack2(1.f, 1.f);
   SoftmaxTile t;
-  t.negm = c.smem + kOffM;
+  t.negm = c.smem + kOffM + 4 * kHalfHeads * half;
   t.cs2 = pack2(cscale, cscale);
-  t.psw = (uint32_t(tid) >> 1) & 3u;
+  t.psw = (uint32_t(row) >> 1) & 3u;
+  t.half = uint32_t(half);
 
 #pragma unroll 1
   for (int si = 0; si < nseg; ++si, ++st.seg) {
     const Segment g = sg[si];
-    uint64_t l2[kGroupHeads / 2];
+    uint64_t l2[kHalfHeads / 2];
 #pragma unroll
-    for (int h = 0; h < kGroupHeads / 2; ++h) l2[h] = 0ull;
+    for (int h = 0; h < kHalfHeads / 2; ++h) l2[h] = 0ull;
+    float sc_max = 0.f;  // largest |token scale| this thread has seen in the segment
 #pragma unroll 1
     for (int tt = g.tile_begin; tt < g.tile_end; ++tt, ++st.it) {
       const uint32_t it = st.it;
@@ -673,14 +690,15 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       if (tid == 0) MLA_TRACE(0, it, 0);
       // per-token scale
       wait(c, bar_aux_full(s), k & 1);
-      t.valid = (tt * kTile + tid) < g.seq_len;
-      float sc = lds_f32(c.smem + kOffScale + 4 * (s * kTile + tid));
+      t.valid = (tt * kTile + row) < g.seq_len;
+      float sc = lds_f32(c.smem + kOffScale + 4 * (s * kTile + row));
       sc = t.valid ? sc : 0.f;
+      sc_max = fmaxf(sc_max, fabsf(sc));
       const float lg = t.valid ? __log2f(fmaxf(fabsf(sc), 8.67361738e-19f)) : 0.f;  // floor 2^-60
       t.sc2 = pack2(sc, sc);
-      t.t_lat = tmem_lane + kColSLat + 64u * s;
-      t.t_rope = tmem_lane + kColSRope + 64u * s;
-      t.p_hi = c.smem + kOffP + s * 2 * kTile * 64 + uint32_t(tid) * 64u;
+      t.t_lat = tmem_lane + kColSLat + 64u * s + uint32_t(kHalfHeads * half);
+      t.t_rope = tmem_lane + kColSRope + 64u * s + uint32_t(kHalfHeads * half);
+      t.p_hi = c.smem + kOffP + s * 2 * kTile * 64 + uint32_t(row) * 64u;
       t.p_lo = t.p_hi + kTile * 64;
 
       // the P buffer of this stage is free once PV of tile it-2 has completed
@@ -702,9 +720,9 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
         // the factor; O^T is rescaled in TMEM; P' is recomputed with the new reference.
         refresh_reference(c, t.t_lat, t.t_rope, sc, t.valid, cscale, lg, true, tid);
 #pragma unroll
-        for (int q = 0; q < kGroupHeads / 4; ++q) {
+        for (int q = 0; q < kHalfHeads / 4; ++q) {
           uint64_t f0, f1;
-          lds_pairs(c.smem + kOffF + 16 * q, f0, f1);
+          lds_pairs(c.smem + kOffF + 4 * kHalfHeads * half + 16 * q, f0, f1);
           l2[2 * q] = mul2(l2[2 * q], f0);
           l2[2 * q + 1] = mul2(l2[2 * q + 1], f1);
         }
@@ -712,7 +730,7 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
           const uint32_t pit = it - 1;
           wait(c, bar_kv_empty(pit & 1, 3), (pit >> 1) & 1);
           ptx::tc_fence_after();
-          rescale_output(c, tmem_lane);
+          rescale_output(c, tmem_lane, uint32_t(half));
         }
         (void)softmax_pass(t, l2, 0ull);
       }
@@ -727,11 +745,11 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
     // ---- segment epilogue
     {
       const uint32_t lit = st.it - 1;  // last tile of the segment
-      float r0, r1;
-      warp_transpose_sum64(l2, lane, r0, r1);
+      const float r = warp_transpose_sum32(l2, lane);  // lane L: this warp's tokens, head 32*half + L
       const uint32_t wred = c.smem + kOffWmax;
-      sts_f32(wred + 4 * (warp * kGroupHeads + 2 * lane), r0);
-      sts_f32(wred + 4 * (warp * kGroupHeads + 2 * lane + 1), r1);
+      sts_f32(wred + 4 * (quarter * kGroupHeads + kHalfHeads * half + lane), r);
+      const float sc_warp = ptx::redux_max_f32(sc_max);
+      if (lane == 0) sts_f32(c.smem + kOffScMax + 4 * warp, sc_warp);
       ptx::bar_sync(1, kSoftmaxThreads);
       if (tid < kGroupHeads) {
         const float L = (lds_f32(wred + 4 * tid) + lds_f32(wred + 4 * (kGroupHeads + tid))) +
@@ -743,7 +761,11 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       // wait for the PV of the last tile
       wait(c, bar_kv_empty(lit & 1, 3), (lit >> 1) & 1);
       ptx::tc_fence_after();
-      if (!c.misc->abort) write_output(p, c, tmem_lane, tid, g.b, g.g, g.slot);
+      float sc_all = 0.f;
+#pragma unroll
+      for (int w8 = 0; w8 < kSoftmaxThreads / 32; ++w8) sc_all = fmaxf(sc_all, lds_f32(c.smem + kOffScMax + 4 * w8));
+      const float slot_scale_v = slot_scale_for(6.f * sc_all * fabsf(p.output_scale));
+      if (!c.misc->abort) write_output(p, c, tmem_lane, row, half, tid, g.b, g.g, g.slot, slot_scale_v);
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar_addr(c, kBarOFree));
       if (tid == 0) MLA_TRACE(0, lit, 6);
@@ -774,7 +796,7 @@ __device__ __noinline__ void stage_segments(const Ctx& c) {
 // ------------------------------------------------------------------------------------------
 // kernel
 // ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(640, 1)  // register budget of five warps per scheduler (kThreads = 576 are launched)
 mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map_q_lat,
                             const __grid_constant__ CUtensorMap map_q_rope, const __grid_constant__ CUtensorMap map_rope) {
   extern __shared__ uint8_t smem_raw[];
@@ -816,7 +838,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
     ptx::mbar_init(bar_addr(c, kBarOFree), kSoftmaxThreads);
     ptx::mbar_init(bar_addr(c, kBarDrain), 1);
     ptx::fence_barrier_init();
-  } else if (warp == 13 && (tid & 31) == 0) {
+  } else if (warp == 17 && (tid & 31) == 0) {
     ptx::prefetch_tensormap(&map_q_lat);
     ptx::prefetch_tensormap(&map_q_rope);
     ptx::prefetch_tensormap(&map_rope);
@@ -826,17 +848,20 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   ptx::tc_fence_after();
   const uint32_t tmem = c.misc->tmem_base;
   if (tid == 0) MLA_TRACE(3, 0u, 0);
+  // Let a dependent kernel (the split-KV combine) start its launch and prologue early; it still waits
+  // for this whole grid before it reads the partial slots.
+  if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   RoleState st;
   st.it = 0;
   st.seg = 0;
   // Rounds: almost always exactly one; more only when a CTA's range spans more than kMaxSeg requests.
   for (;;) {
-    if (warp < 4) {
+    if (warp < 8) {
       softmax_role(p, c, tmem, tid, st);
-    } else if (warp < 12) {
-      dequant_role(p, c, tid - 128, st);
-    } else if (warp == 12) {
+    } else if (warp < 16) {
+      dequant_role(p, c, tid - kSoftmaxThreads, st);
+    } else if (warp == 16) {
       mma_role(c, tmem, st);
     } else {
       if ((tid & 31) == 0) tma_role(p, c, &map_q_lat, &map_q_rope, &map_rope, st);
@@ -850,7 +875,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   }
 
   // drain: everything issued has completed before TMEM is released
-  if (warp == 12) {
+  if (warp == 16) {
     if (ptx::elect_one()) {
       ptx::umma_commit(bar_addr(c, kBarDrain));
       drain_wait(c, kBarDrain, 0);

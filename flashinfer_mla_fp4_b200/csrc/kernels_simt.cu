@@ -9,6 +9,7 @@
 #include "launch.h"
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
 namespace mla {
@@ -195,14 +196,29 @@ __global__ void __launch_bounds__(256) fp32_check_kernel(DecodeParams p) {
       }
       if (p.lse && tid < heads_here) p.lse[row0 + tid] = log2f(l_s[tid]) + m_s[tid];
     } else {
-      float* so = reinterpret_cast<float*>(p.workspace) + size_t(s.slot) * kSlotFloats;
+      // slot scale from the largest |O| of the segment (any bound of |O| is a valid slot scale)
+      float amax = 0.f;
 #pragma unroll
       for (int h = 0; h < kGroupHeads; ++h) {
         float inv = p.output_scale / l_s[h];
-        so[size_t(tid) * kGroupHeads + h] = o0[h] * inv;
-        so[size_t(tid + 256) * kGroupHeads + h] = o1[h] * inv;
+        amax = fmaxf(amax, fmaxf(fabsf(o0[h] * inv), fabsf(o1[h] * inv)));
       }
-      if (tid < kGroupHeads) so[kSlotOFloats + tid] = log2f(l_s[tid]) + m_s[tid];
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      __syncthreads();
+      if ((tid & 31) == 0) f_s[tid >> 5] = amax;
+      __syncthreads();
+      amax = 0.f;
+      for (int w8 = 0; w8 < 8; ++w8) amax = fmaxf(amax, f_s[w8]);
+      const float sscale = slot_scale_for(amax);
+      __half* so = reinterpret_cast<__half*>(slot_o(p.workspace, s.slot));
+#pragma unroll
+      for (int h = 0; h < kGroupHeads; ++h) {
+        float inv = p.output_scale / l_s[h] / sscale;
+        so[size_t(tid) * kGroupHeads + h] = __float2half_rn(o0[h] * inv);
+        so[size_t(tid + 256) * kGroupHeads + h] = __float2half_rn(o1[h] * inv);
+      }
+      if (tid == 0) slot_scale(p.workspace, s.slot)[0] = sscale;
+      if (tid < kGroupHeads) slot_lse(p.workspace, s.slot)[tid] = log2f(l_s[tid]) + m_s[tid];
     }
   }
 }

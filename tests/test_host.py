@@ -32,7 +32,7 @@ def test_abi_rejects_bad_arguments_without_a_gpu():
     assert "null" in _cabi.last_error()
     n = ctypes.c_size_t(0)
     assert _cabi.lib.mla_fp4_workspace_bytes(8, 1, 64, 148, ctypes.byref(n)) == 0
-    assert n.value == 2 * 148 * (512 * 64 + 64) * 4
+    assert n.value == 2 * 148 * (512 * 64 * 2 + 64 * 4 + 16)
     assert _cabi.lib.mla_fp4_workspace_bytes(8, 0, 64, 148, ctypes.byref(n)) == _cabi.ERR_BAD_ARG
     with pytest.raises(ValueError):
         _cabi.check(_cabi.ERR_WORKSPACE_TOO_SMALL)
@@ -80,7 +80,7 @@ def test_partition_is_a_partition(seq_lens, q_len, heads, ctas):
         assert all(k in (0, len(ss) - 1) for k in partial)
         for k in partial:
             assert ss[k].slot == 2 * i + (0 if k == 0 else 1)
-    assert planner.workspace_bytes(len(seq_lens), q_len, heads, ctas) >= (max(slots) + 1 if slots else 0) * 131328
+    assert planner.workspace_bytes(len(seq_lens), q_len, heads, ctas) >= (max(slots) + 1 if slots else 0) * 65808
 
 
 def test_package_quantiser_is_bit_identical_to_the_oracle():
