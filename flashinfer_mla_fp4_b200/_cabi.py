@@ -64,6 +64,7 @@ EXPORTS = (
     "mla_fp4_decode",
     "mla_fp4_merge_partials",
     "mla_fp4_dequant_e2m1_to_e4m3",
+    "mla_fp4_decode_static",
 )
 
 
@@ -84,6 +85,8 @@ def _load() -> C.CDLL:
     lib.mla_fp4_plan_partition.restype = C.c_int
     lib.mla_fp4_decode.argtypes = [C.POINTER(DecodeArgs)]
     lib.mla_fp4_decode.restype = C.c_int
+    lib.mla_fp4_decode_static.argtypes = [C.POINTER(DecodeArgs)]
+    lib.mla_fp4_decode_static.restype = C.c_int
     lib.mla_fp4_merge_partials.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
                                            C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]
     lib.mla_fp4_merge_partials.restype = C.c_int

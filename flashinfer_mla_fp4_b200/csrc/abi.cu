@@ -162,6 +162,48 @@ int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
   return MLA_FP4_OK;
 }
 
+}  // extern "C"
+
+// Scratch of the allocation-free entry point: the split-KV partial slots of the largest accepted
+// grid.  On the host this name is only a handle; the device address is looked up per device.
+static __device__ __align__(256) unsigned char g_static_scratch[MLA_FP4_STATIC_SCRATCH_BYTES];
+static_assert(MLA_FP4_STATIC_SCRATCH_BYTES == 2 * MLA_FP4_STATIC_MAX_CTAS * mla::kSlotBytes, "static scratch size");
+
+extern "C" {
+
+int mla_fp4_decode_static(const MlaFp4DecodeArgs* a) {
+  if (!a) return fail(MLA_FP4_ERR_BAD_ARG, "args is null");
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(MLA_FP4_ERR_UNSUPPORTED, "device ordinal out of range for the static scratch table");
+  int num_ctas = a->num_ctas;
+  if (num_ctas <= 0) {
+    int rc = sm_count(&num_ctas);
+    if (rc) return rc;
+  }
+  if (num_ctas > MLA_FP4_STATIC_MAX_CTAS) {
+    char buf[160];
+    snprintf(buf, sizeof buf, "mla_fp4_decode_static supports at most %d CTAs (built-in scratch of %d bytes), got %d",
+             MLA_FP4_STATIC_MAX_CTAS, int(MLA_FP4_STATIC_SCRATCH_BYTES), num_ctas);
+    return fail(MLA_FP4_ERR_UNSUPPORTED, buf);
+  }
+  // set-up, once per device, with that device current: the device address of the scratch array
+  static void* scratch_addr[64] = {};
+  if (!scratch_addr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || !ptr)
+      return fail(MLA_FP4_ERR_CUDA, std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(e));
+    scratch_addr[dev] = ptr;
+  }
+  MlaFp4DecodeArgs b = *a;
+  b.workspace = scratch_addr[dev];
+  b.workspace_bytes = size_t(MLA_FP4_STATIC_SCRATCH_BYTES);
+  b.num_ctas = num_ctas;
+  return mla_fp4_decode(&b);
+}
+
 int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, int32_t parts, int64_t rows,
                            int64_t part_stride_out, int64_t part_stride_lse, void* out, int32_t out_dtype, float* lse,
                            void* stream) {

@@ -130,6 +130,29 @@ int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, i
    decode kernel.  Pins the table of tests/test_cute_dsl_mla_fp4.py:80-84. */
 int mla_fp4_dequant_e2m1_to_e4m3(const void* packed, void* out, int64_t n_bytes, void* stream);
 
+/* Largest decode grid the allocation-free variant below accepts, and the bytes of device memory
+   its built-in scratch occupies on every GPU that loads the library (until the process exits). */
+#define MLA_FP4_STATIC_MAX_CTAS 148
+#define MLA_FP4_STATIC_SCRATCH_BYTES (2 * MLA_FP4_STATIC_MAX_CTAS * 65808)
+
+/* No counterpart in the reference.  Same decode step as mla_fp4_decode, for callers that may not
+   allocate device memory and have no workspace buffer to lend: plugins running inside an engine
+   whose memory pool owns the whole device, code running under a framework that forbids cudaMalloc
+   on its worker threads, or a step that has to run when the caching allocator is exhausted.
+   args->workspace and args->workspace_bytes are ignored; the split-KV partials go to a scratch
+   array built into the library (MLA_FP4_STATIC_SCRATCH_BYTES of device memory per GPU, reserved
+   when the library is loaded on that GPU).  q, cache, block tables, seq_lens, out, lse and the
+   status words are still the caller's.  Nothing is allocated or freed, here or in the kernels.
+   - Limit: the decode grid (args->num_ctas, or the SM count when 0) must not exceed
+     MLA_FP4_STATIC_MAX_CTAS; a larger grid is rejected with MLA_FP4_ERR_UNSUPPORTED.
+   - The first call on a device looks the scratch address up once (with that device current) and
+     keeps it; make that first call before any stream capture begins.
+   - All calls on a device share the one scratch array.  It keeps the previous call's partials, which
+     is harmless: a step only reads the slots it has just written, so nothing has to start at zero.
+     Two calls whose kernels overlap on the GPU (different streams) would overwrite each other's
+     partials: run them in order on one stream, or use mla_fp4_decode with separate workspaces. */
+int mla_fp4_decode_static(const MlaFp4DecodeArgs* args);
+
 #ifdef __cplusplus
 }
 #endif
