@@ -38,7 +38,11 @@ namespace mla {
 
 namespace {
 
-constexpr int kThreads = 576;           // 18 warps: five per scheduler, hence at most 96 registers per thread
+#ifdef MLA_FP4_TRACE
+constexpr int kThreads = 640;           // trace builds add an observer warp
+#else
+constexpr int kThreads = 608;           // 19 warps; at most five per scheduler, hence at most 96 registers per thread
+#endif
 constexpr int kSoftmaxThreads = 256;   // 8 warps: warp w works on TMEM lanes 32*(w%4).. and heads 32*(w/4)..
 constexpr int kDequantThreads = 256;
 constexpr int kDequantWarps = kDequantThreads / 32;
@@ -115,14 +119,8 @@ struct RoleState {
 __device__ __forceinline__ uint32_t bar_addr(const Ctx& c, int idx) { return c.smem + kOffBars + 8u * idx; }
 __device__ __forceinline__ const Segment* segs(const Ctx& c) { return reinterpret_cast<const Segment*>(c.smem_ptr + kOffSegs); }
 
-// Bounded wait.  Returns false (and flags the CTA) when the wait expires or the CTA is aborting.
-__device__ __noinline__ bool wait_slow(const Ctx& c, int idx, uint32_t parity) {
-  const uint32_t bar = bar_addr(c, idx);
-  for (uint32_t i = 0; i < (1u << 22); ++i) {
-    if (c.misc->abort) return false;
-    if (ptx::mbar_try_wait(bar, parity)) return true;
-    if (i > 16) __nanosleep(128);
-  }
+// A bounded wait expired: flag the CTA (every role then stops issuing and drains) and leave a record.
+__device__ __noinline__ void flag_timeout(const Ctx& c, int idx, uint32_t parity) {
   c.misc->abort = 1;
   if (c.status) {
     if (atomicCAS(c.status, 0, MLA_FP4_ERR_DEVICE_TIMEOUT) == 0) {
@@ -132,6 +130,16 @@ __device__ __noinline__ bool wait_slow(const Ctx& c, int idx, uint32_t parity) {
       c.status[4] = int(parity);
     }
   }
+}
+// Bounded wait.  Returns false (and flags the CTA) when the wait expires or the CTA is aborting.
+__device__ __noinline__ bool wait_slow(const Ctx& c, int idx, uint32_t parity) {
+  const uint32_t bar = bar_addr(c, idx);
+  for (uint32_t i = 0; i < (1u << 22); ++i) {
+    if (c.misc->abort) return false;
+    if (ptx::mbar_try_wait(bar, parity)) return true;  // suspends in hardware for a while: not a hot spin
+    if (i > 4096) __nanosleep(128);
+  }
+  flag_timeout(c, idx, parity);
   return false;
 }
 __device__ __forceinline__ bool wait(const Ctx& c, int idx, uint32_t parity) {
@@ -139,9 +147,10 @@ __device__ __forceinline__ bool wait(const Ctx& c, int idx, uint32_t parity) {
   return wait_slow(c, idx, parity);
 }
 // One lane polls for the warp; the warp barrier orders the other lanes after its acquire.
-__device__ __forceinline__ void wait_warp(const Ctx& c, int idx, uint32_t parity) {
-  if ((threadIdx.x & 31) == 0) wait(c, idx, parity);
-  __syncwarp();
+__device__ __forceinline__ bool wait_warp(const Ctx& c, int idx, uint32_t parity) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = wait(c, idx, parity) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 // Bounded wait that ignores the abort flag: lets in-flight asynchronous work land before exit.
 __device__ __noinline__ void drain_wait(const Ctx& c, int idx, uint32_t parity) {
@@ -244,16 +253,23 @@ __device__ __forceinline__ void dequant_role(const DecodeParams& p, const Ctx& c
 #pragma unroll
     for (int j = 0; j < kBlocks; ++j) {
       // convert first (registers only), then wait for the block to be free, then store
+      if (dtid == 0 && j == 1) MLA_TRACE(4, it, 4);
       const E4m3x32 e0 = dequant32(regs[j][0]);
       const E4m3x32 e1 = dequant32(regs[j][1]);
+#ifdef MLA_FP4_TRACE
+      if (dtid == 0 && j == 1 && (e0.a[0] ^ e1.b[3]) != 0x12345678u) MLA_TRACE(4, it, 5);
+#endif
       if (k >= 1) wait_warp(c, bar_kv_empty(s, j), (k - 1) & 1);
       if (dtid == 0) MLA_TRACE(1, it, 1 + j);
       const uint32_t base = c.smem + kOffKV + (s * kBlocks + j) * kBlockBytes;
       store32(e0, base + off_a, base + off_b);
       store32(e1, base + off_a + 64u * 128u, base + off_b + 64u * 128u);
+      if (dtid == 0 && j == 1) MLA_TRACE(4, it, 6);
       ptx::fence_proxy_async_smem();
       __syncwarp();
+      if (dtid == 0 && j == 1) MLA_TRACE(4, it, 7);
       if (lane == 0) ptx::mbar_arrive(bar_addr(c, bar_kv_full(s, j)));
+      if (lane == 0) MLA_TRACE(4 + (dtid >> 5), it, j);
       if (more) {
 #pragma unroll
         for (int u = 0; u < 2; ++u) regs[j][u] = src[u] ? ldg_nc(src[u] + 64 * j + 16 * ch) : zero;
@@ -324,7 +340,7 @@ __device__ __forceinline__ void tma_role(const DecodeParams& p, const Ctx& c, co
 }
 
 // ------------------------------------------------------------------------------------------
-// role: MMA issue (warp 16).  The whole warp runs this code with uniform control flow; only the
+// role: MMA issue (warps 16 and 18).  The whole warp runs this code with uniform control flow; only the
 // tcgen05 instructions sit under elect_one(), so their operands stay in uniform registers.
 // ------------------------------------------------------------------------------------------
 // Descriptors of every operand, built once: the per-instruction work is one 32-bit add.
@@ -337,49 +353,31 @@ struct MmaDescs {
   uint64_t p;       // P^T hi, MN-major, 64B swizzle                (+ stage*1024 + lo*512 + kstep*128)
 };
 
-__device__ __forceinline__ void issue_qk(const Ctx& c, const MmaDescs& d, uint32_t it, uint32_t tmem) {
+// QK^T of one 128-dim block of tile `it` (4 MMAs); after the last block also the RoPE part and the
+// commit that hands S to the softmax warps.  The caller has seen the operands' barriers complete.
+__device__ __forceinline__ void issue_qk_block(const Ctx& c, const MmaDescs& d, uint32_t it, uint32_t j, uint32_t tmem) {
   const uint32_t s = it & 1;
-  const uint32_t k = it >> 1;
-  MLA_TRACE(2, it, 0);
-  if (k >= 1) wait(c, bar_s_empty(s), (k - 1) & 1);
-  wait(c, bar_aux_full(s), k & 1);
-  MLA_TRACE(2, it, 1);
   const uint32_t d_lat = tmem + kColSLat + 64u * s;
-  const uint32_t d_rope = tmem + kColSRope + 64u * s;
-#pragma unroll 1
-  for (uint32_t j = 0; j < kBlocks; ++j) {
-    wait(c, bar_kv_full(s, j), k & 1);
-    if (c.misc->abort) return;
-    ptx::tc_fence_after();
-    const uint64_t ad = d.kv_k + ((s * kBlocks + j) * (kBlockBytes >> 4));
-    const uint64_t bd = d.q_lat + j * ((kGroupHeads * 128) >> 4);
-    if (ptx::elect_one()) {
+  const uint64_t ad = d.kv_k + ((s * kBlocks + j) * (kBlockBytes >> 4));
+  const uint64_t bd = d.q_lat + j * ((kGroupHeads * 128) >> 4);
+  ptx::tc_fence_after();
+  if (ptx::elect_one()) {
 #pragma unroll
-      for (uint32_t ks = 0; ks < 4; ++ks) ptx::umma_f8(d_lat, ad + 2 * ks, bd + 2 * ks, kIdescQK, (j | ks) ? 1u : 0u);
-    }
-    __syncwarp();
-  }
-  {
-    const uint64_t ad = d.rope + s * ((kTile * 64) >> 4);
-    if (ptx::elect_one()) {
+    for (uint32_t ks = 0; ks < 4; ++ks) ptx::umma_f8(d_lat, ad + 2 * ks, bd + 2 * ks, kIdescQK, (j | ks) ? 1u : 0u);
+    if (j == kBlocks - 1) {
+      const uint32_t d_rope = tmem + kColSRope + 64u * s;
+      const uint64_t ar = d.rope + s * ((kTile * 64) >> 4);
 #pragma unroll
-      for (uint32_t ks = 0; ks < 2; ++ks) ptx::umma_f8(d_rope, ad + 2 * ks, d.q_rope + 2 * ks, kIdescQK, ks);
+      for (uint32_t ks = 0; ks < 2; ++ks) ptx::umma_f8(d_rope, ar + 2 * ks, d.q_rope + 2 * ks, kIdescQK, ks);
       ptx::umma_commit(bar_addr(c, bar_s_full(s)));
     }
-    __syncwarp();
   }
-  MLA_TRACE(2, it, 2);
+  __syncwarp();
 }
 
-__device__ __forceinline__ void issue_pv(const Ctx& c, const MmaDescs& d, uint32_t it, uint32_t tmem, bool first_of_segment,
-                                         uint32_t seg) {
+// PV of tile `it`: 4 blocks x 4 token steps x (hi, lo); every block commits the barrier that frees it.
+__device__ __forceinline__ void issue_pv(const Ctx& c, const MmaDescs& d, uint32_t it, uint32_t tmem, bool first_of_segment) {
   const uint32_t s = it & 1;
-  const uint32_t k = it >> 1;
-  MLA_TRACE(2, it, 3);
-  wait(c, bar_p_full(s), k & 1);
-  if (first_of_segment && seg >= 1) wait(c, kBarOFree, (seg - 1) & 1);
-  MLA_TRACE(2, it, 4);
-  if (c.misc->abort) return;
   ptx::tc_fence_after();
   const uint64_t p_hi = d.p + s * ((2 * kTile * 64) >> 4);
   const uint64_t p_lo = p_hi + ((kTile * 64) >> 4);
@@ -392,8 +390,8 @@ __device__ __forceinline__ void issue_pv(const Ctx& c, const MmaDescs& d, uint32
     if (ptx::elect_one()) {
 #pragma unroll
       for (uint32_t ks = 0; ks < 4; ++ks) {
-        // B = P^T: MN-major (64 heads contiguous), 64-byte swizzle; 32 tokens per step = 2048 B
-        // the hi and the lo term share A: it is fetched once and kept in the collector for the second
+        // B = P^T: MN-major (64 heads contiguous), 64-byte swizzle; 32 tokens per step = 2048 B.
+        // The hi and the lo term share A: it is fetched once and kept in the collector for the second.
         ptx::umma_f8_a_fill(dd, ad + 256 * ks, p_hi + 128 * ks, kIdescPV, ks ? 1u : acc0);
         ptx::umma_f8_a_lastuse(dd, ad + 256 * ks, p_lo + 128 * ks, kIdescPV, 1u);
       }
@@ -401,10 +399,13 @@ __device__ __forceinline__ void issue_pv(const Ctx& c, const MmaDescs& d, uint32
     }
     __syncwarp();
   }
-  MLA_TRACE(2, it, 5);
 }
 
-__device__ __forceinline__ void mma_role(const Ctx& c, uint32_t tmem, RoleState& st) {
+// QK^T and PV are issued by two different warps.  Each runs straight-line code with blocking waits, so
+// neither's issue latency (a few hundred cycles per block of MMAs, on one warp with no parallelism
+// to hide it) delays the other; the tensor pipe serialises the two streams in hardware, and every
+// data hazard between them is already covered by a barrier.
+__device__ __forceinline__ MmaDescs make_descs(const Ctx& c) {
   MmaDescs d;
   d.kv_k = ptx::smem_desc(c.smem + kOffKV, 16, 1024, 2);
   d.kv_mn = ptx::smem_desc(c.smem + kOffKV, kBlockBytes, 1024, 2);
@@ -412,22 +413,57 @@ __device__ __forceinline__ void mma_role(const Ctx& c, uint32_t tmem, RoleState&
   d.rope = ptx::smem_desc(c.smem + kOffRope, 16, 512, 4);
   d.q_rope = ptx::smem_desc(c.smem + kOffQRope, 16, 512, 4);
   d.p = ptx::smem_desc(c.smem + kOffP, 512, 512, 4);
+  return d;
+}
+
+// role: QK^T issue (warp 16)
+__device__ __forceinline__ void qk_role(const Ctx& c, uint32_t tmem, RoleState& st) {
+  const MmaDescs d = make_descs(c);
   const int nseg = c.misc->nseg;
   const Segment* sg = segs(c);
 #pragma unroll 1
   for (int si = 0; si < nseg; ++si, ++st.seg) {
-    const int n = sg[si].tile_end - sg[si].tile_begin;
-    wait(c, kBarQFull, st.seg & 1);
-    issue_qk(c, d, st.it, tmem);
+    const uint32_t n = uint32_t(sg[si].tile_end - sg[si].tile_begin);
+    bool ok = wait_warp(c, kBarQFull, st.seg & 1);
 #pragma unroll 1
-    for (int i = 0; i < n; ++i) {
-      if (i + 1 < n) {
-        issue_qk(c, d, st.it + i + 1, tmem);
-      } else if (!c.misc->abort) {  // every QK of this segment has been issued
-        if (ptx::elect_one()) ptx::umma_commit(bar_addr(c, kBarQEmpty));
-        __syncwarp();
+    for (uint32_t t = 0; t < n && ok; ++t) {
+      const uint32_t it = st.it + t, s = it & 1, k = it >> 1;
+      // S of this stage has been read by the softmax of tile it-2; RoPE bytes of this tile have landed
+      if (k >= 1) ok = wait_warp(c, bar_s_empty(s), (k - 1) & 1);
+      ok = ok && wait_warp(c, bar_aux_full(s), k & 1);
+      MLA_TRACE(2, it, 0);
+#pragma unroll 1
+      for (uint32_t j = 0; j < kBlocks && ok; ++j) {
+        ok = wait_warp(c, bar_kv_full(s, j), k & 1);
+        if (ok) issue_qk_block(c, d, it, j, tmem);
       }
-      issue_pv(c, d, st.it + i, tmem, i == 0, st.seg);
+      MLA_TRACE(2, it, 2);
+    }
+    // every QK^T of this segment has been issued: Q may be overwritten once they complete
+    if (ptx::elect_one()) ptx::umma_commit(bar_addr(c, kBarQEmpty));
+    __syncwarp();
+    st.it += n;
+  }
+}
+
+// role: PV issue (warp 18)
+__device__ __forceinline__ void pv_role(const Ctx& c, uint32_t tmem, RoleState& st) {
+  const MmaDescs d = make_descs(c);
+  const int nseg = c.misc->nseg;
+  const Segment* sg = segs(c);
+#pragma unroll 1
+  for (int si = 0; si < nseg; ++si, ++st.seg) {
+    const uint32_t n = uint32_t(sg[si].tile_end - sg[si].tile_begin);
+    // O^T of the previous segment has been read out
+    bool ok = st.seg == 0 || wait_warp(c, kBarOFree, (st.seg - 1) & 1);
+#pragma unroll 1
+    for (uint32_t t = 0; t < n && ok; ++t) {
+      const uint32_t it = st.it + t, s = it & 1, k = it >> 1;
+      ok = wait_warp(c, bar_p_full(s), k & 1);
+      if (!ok) break;
+      MLA_TRACE(2, it, 4);
+      issue_pv(c, d, it, tmem, t == 0);
+      MLA_TRACE(2, it, 5);
     }
     st.it += n;
   }
@@ -796,7 +832,7 @@ __device__ __noinline__ void stage_segments(const Ctx& c) {
 // ------------------------------------------------------------------------------------------
 // kernel
 // ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(640, 1)  // register budget of five warps per scheduler (kThreads = 576 are launched)
+__global__ void __launch_bounds__(640, 1)  // register budget of five warps per scheduler (kThreads are launched)
 mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map_q_lat,
                             const __grid_constant__ CUtensorMap map_q_rope, const __grid_constant__ CUtensorMap map_rope) {
   extern __shared__ uint8_t smem_raw[];
@@ -836,7 +872,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
     ptx::mbar_init(bar_addr(c, kBarQFull), 1);
     ptx::mbar_init(bar_addr(c, kBarQEmpty), 1);
     ptx::mbar_init(bar_addr(c, kBarOFree), kSoftmaxThreads);
-    ptx::mbar_init(bar_addr(c, kBarDrain), 1);
+    ptx::mbar_init(bar_addr(c, kBarDrain), 2);
     ptx::fence_barrier_init();
   } else if (warp == 17 && (tid & 31) == 0) {
     ptx::prefetch_tensormap(&map_q_lat);
@@ -862,7 +898,30 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
     } else if (warp < 16) {
       dequant_role(p, c, tid - kSoftmaxThreads, st);
     } else if (warp == 16) {
-      mma_role(c, tmem, st);
+      qk_role(c, tmem, st);
+    } else if (warp == 18) {
+      pv_role(c, tmem, st);
+#ifdef MLA_FP4_TRACE
+    } else if (warp == 19) {  // observers: lane 0 QK^T completion, lane 1 PV completion (block 0 and whole tile)
+      if (blockIdx.x == 0 && (tid & 31) < 2) {
+        const int nseg = c.misc->nseg;
+        uint32_t it = 0;
+        for (int si = 0; si < nseg; ++si)
+          for (int tt = segs(c)[si].tile_begin; tt < segs(c)[si].tile_end; ++tt, ++it) {
+            const uint32_t s = it & 1, k = it >> 1;
+            if ((tid & 31) == 0) {
+              while (!ptx::mbar_try_wait(bar_addr(c, bar_s_full(s)), k & 1) && !c.misc->abort) {}
+              MLA_TRACE(3, it, 2);
+            } else {
+              while (!ptx::mbar_try_wait(bar_addr(c, bar_kv_empty(s, 0)), k & 1) && !c.misc->abort) {}
+              MLA_TRACE(3, it, 4);
+              while (!ptx::mbar_try_wait(bar_addr(c, bar_kv_empty(s, 3)), k & 1) && !c.misc->abort) {}
+              MLA_TRACE(3, it, 3);
+            }
+          }
+      }
+      __syncwarp();
+#endif
     } else {
       if ((tid & 31) == 0) tma_role(p, c, &map_q_lat, &map_q_rope, &map_rope, st);
       __syncwarp();
@@ -875,7 +934,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   }
 
   // drain: everything issued has completed before TMEM is released
-  if (warp == 16) {
+  if (warp == 16 || warp == 18) {  // a commit covers the MMAs of the thread that executes it
     if (ptx::elect_one()) {
       ptx::umma_commit(bar_addr(c, kBarDrain));
       drain_wait(c, kBarDrain, 0);
