@@ -173,6 +173,11 @@ def main() -> None:
     ap.add_argument("--copies", type=int, default=0, help="cache copies rotated for cold L2 (0 = enough to exceed L2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--repeats", type=int, default=5, help="timed graph replays; the median is reported")
+    ap.add_argument("--kernel", default="fused", choices=["fused", "2pass"],
+                    help="fused: one kernel that also merges the split-KV partials (the product path); "
+                         "2pass: the same decode kernel followed by a separate combine kernel")
+    ap.add_argument("--profile-steps", type=int, default=0,
+                    help="run this many plain (no graph) steps after the warm-up and exit: the command line for ncu captures")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -206,6 +211,9 @@ def main() -> None:
     ws = torch.empty(64 << 20, dtype=torch.int8, device=device)
     wrapper = BatchMLADecodeCuteDSLFP4Wrapper(ws)
     wrapper.plan(num_heads=H, page_size=case.page_size, out_dtype=torch.bfloat16, is_var_seq=True)
+    from flashinfer_mla_fp4_b200 import _cabi
+    wrapper._kernel = _cabi.KERNEL_TCGEN05 if args.kernel == "fused" else _cabi.KERNEL_TCGEN05_2PASS
+    launches_per_step = 1 if args.kernel == "fused" else 2
     out = torch.empty(B, ql, H, 512, dtype=torch.bfloat16, device=device)
     cp = ContextParallelDecoder(wrapper, dist.group.WORLD) if (args.mode == "cp" and world > 1) else None
 
@@ -227,6 +235,13 @@ def main() -> None:
         step(i)
     torch.cuda.synchronize()
     wrapper.check_device_status()
+    if args.profile_steps > 0:
+        for i in range(args.profile_steps):
+            step(i)
+        torch.cuda.synchronize()
+        wrapper.check_device_status()
+        print(json.dumps({"profile_steps": args.profile_steps, "workload": case.name, "kernel": args.kernel}), flush=True)
+        return
 
     # ---- device-timed K steps: one CUDA graph holding the K steps, replayed `repeats` times
     K = args.steps
@@ -260,6 +275,7 @@ def main() -> None:
     us_local = statistics.median(times)
 
     # ---- decode kernel alone (roofline of the dominant kernel), same rotation, events on the launching stream
+    # (in the fused mode the decode kernel is the whole step; in the two-kernel mode the combine kernel is left out)
     wrapper._phase_mask = 1
     kgraph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(stream):
@@ -345,11 +361,11 @@ def main() -> None:
             "tflops": flops_all / (us * 1e-6) / 1e12,
             "roofline": {"bound": "hbm" if t_hbm >= t_fp8 else "tensor", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                          "frac": achieved / hbm_peak, "traffic": None, "peak_kind": peak_kind,
-                         "kernel": "mla_fp4_decode_sm100_kernel", "kernel_us": kernel_us, "algorithmic_bytes": case.step_bytes(),
+                         "kernel": "mla_fp4_decode_sm100_kernel", "kernel_mode": args.kernel, "kernel_us": kernel_us, "algorithmic_bytes": case.step_bytes(),
                          "roofline_us": max(t_hbm, t_fp8), "step_frac_of_roofline": max(t_hbm, t_fp8) / us,
                          "fp8_peak_tflops_assumed": fp8_peak},
             "e2e": {"value": e2e_us, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": 2 * K + (1 if cp is not None else 0) * K,
+            "gpu_launches": launches_per_step * K + (1 if cp is not None else 0) * K,
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:

@@ -11,7 +11,7 @@ from pathlib import Path
 
 # MLA_FP4_B200_LIB overrides the library location (for instance a debug build)
 LIB_PATH = Path(os.environ.get("MLA_FP4_B200_LIB") or (Path(__file__).resolve().parent / "libmla_fp4_b200.so"))
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 OK = 0
 ERR_BAD_ARG = 1
@@ -23,6 +23,8 @@ ERR_NOT_BUILT = 6
 
 KERNEL_TCGEN05 = 0
 KERNEL_FP32_CHECK = 1
+KERNEL_TCGEN05_2PASS = 2
+WORKSPACE_HEADER_BYTES = 2048
 OUT_BF16 = 0
 OUT_F32 = 1
 
@@ -60,6 +62,7 @@ EXPORTS = (
     "mla_fp4_abi_version",
     "mla_fp4_last_error",
     "mla_fp4_workspace_bytes",
+    "mla_fp4_workspace_init",
     "mla_fp4_plan_partition",
     "mla_fp4_decode",
     "mla_fp4_merge_partials",
@@ -79,6 +82,8 @@ def _load() -> C.CDLL:
     lib.mla_fp4_last_error.restype = C.c_char_p
     lib.mla_fp4_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_size_t)]
     lib.mla_fp4_workspace_bytes.restype = C.c_int
+    lib.mla_fp4_workspace_init.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.mla_fp4_workspace_init.restype = C.c_int
     i32p = C.POINTER(C.c_int32)
     lib.mla_fp4_plan_partition.argtypes = [i32p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                            i32p, i32p, i32p, i32p, i32p, i32p, i32p]
@@ -113,6 +118,11 @@ def check(rc: int) -> None:
     if rc in (ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE_TOO_SMALL):
         raise ValueError(msg)
     raise RuntimeError(f"mla_fp4 error {rc}: {msg}")
+
+
+def workspace_init(ptr: int, nbytes: int, stream: int) -> None:
+    """Zero the counter header of a workspace (asynchronous, on `stream`)."""
+    check(lib.mla_fp4_workspace_init(ptr, nbytes, stream))
 
 
 def workspace_bytes(batch: int, q_len: int, num_heads: int, num_ctas: int) -> int:

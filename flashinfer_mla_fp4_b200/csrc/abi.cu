@@ -43,8 +43,8 @@ int mla_fp4_workspace_bytes(int32_t batch, int32_t q_len, int32_t num_heads, int
     int rc = sm_count(&num_ctas);
     if (rc) return rc;
   }
-  // two partial slots per CTA (its first and its last segment), whatever the batch is
-  *bytes_out = size_t(2) * size_t(num_ctas) * mla::kSlotBytes;
+  // the counter header, then two partial slots per CTA (its first and its last segment), whatever the batch is
+  *bytes_out = mla::kWsHeaderBytes + size_t(2) * size_t(num_ctas) * mla::kSlotBytes;
   return MLA_FP4_OK;
 }
 
@@ -92,6 +92,14 @@ int mla_fp4_plan_partition(const int32_t* seq_lens_host, int32_t batch, int32_t 
   return MLA_FP4_OK;
 }
 
+int mla_fp4_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+  if (!workspace) return fail(MLA_FP4_ERR_BAD_ARG, "workspace is null");
+  if (workspace_bytes < mla::kWsHeaderBytes) return fail(MLA_FP4_ERR_WORKSPACE_TOO_SMALL, "workspace is smaller than its header");
+  cudaError_t e = cudaMemsetAsync(workspace, 0, mla::kWsHeaderBytes, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
+  return MLA_FP4_OK;
+}
+
 int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
   if (!a) return fail(MLA_FP4_ERR_BAD_ARG, "args is null");
   if (a->batch < 0 || a->q_len <= 0 || a->num_heads <= 0) return fail(MLA_FP4_ERR_BAD_ARG, "batch/q_len/num_heads out of range");
@@ -116,7 +124,7 @@ int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
     if (rc) return rc;
   }
   if (num_ctas > mla::kMaxCombineSlots) return fail(MLA_FP4_ERR_UNSUPPORTED, "num_ctas must be <= 148");
-  size_t need = size_t(2) * size_t(num_ctas) * mla::kSlotBytes;
+  size_t need = mla::kWsHeaderBytes + size_t(2) * size_t(num_ctas) * mla::kSlotBytes;
   if (!a->workspace || a->workspace_bytes < need) {
     char buf[160];
     snprintf(buf, sizeof buf, "workspace has %zu bytes, but %zu are required", a->workspace ? a->workspace_bytes : size_t(0), need);
@@ -137,13 +145,15 @@ int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
 
   cudaError_t e = cudaSuccess;
-  const bool do_decode = a->phase_mask == 0 || (a->phase_mask & 1);
-  const bool do_combine = a->phase_mask == 0 || (a->phase_mask & 2);
+  const bool fused = a->kernel == MLA_FP4_KERNEL_TCGEN05;
+  p.fused_merge = fused ? 1 : 0;
+  const bool do_decode = fused || a->phase_mask == 0 || (a->phase_mask & 1);
+  const bool do_combine = !fused && (a->phase_mask == 0 || (a->phase_mask & 2));
   if (!do_decode) {
   } else if (a->kernel == MLA_FP4_KERNEL_FP32_CHECK) {
     p.pdl = 0;
     e = mla::launch_fp32_check(p, num_ctas, stream);
-  } else if (a->kernel == MLA_FP4_KERNEL_TCGEN05) {
+  } else if (a->kernel == MLA_FP4_KERNEL_TCGEN05 || a->kernel == MLA_FP4_KERNEL_TCGEN05_2PASS) {
     const char* why = nullptr;
     e = mla::launch_decode_sm100(p, num_ctas, stream, &why);
     if (e != cudaSuccess && why) return fail(MLA_FP4_ERR_UNSUPPORTED, why);
@@ -164,10 +174,10 @@ int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
 
 }  // extern "C"
 
-// Scratch of the allocation-free entry point: the split-KV partial slots of the largest accepted
-// grid.  On the host this name is only a handle; the device address is looked up per device.
+// Scratch of the allocation-free entry point: the counter header (zero-initialised static storage)
+// and the split-KV partial slots of the largest accepted grid.  On the host this name is only a handle; the device address is looked up per device.
 static __device__ __align__(256) unsigned char g_static_scratch[MLA_FP4_STATIC_SCRATCH_BYTES];
-static_assert(MLA_FP4_STATIC_SCRATCH_BYTES == 2 * MLA_FP4_STATIC_MAX_CTAS * mla::kSlotBytes, "static scratch size");
+static_assert(MLA_FP4_STATIC_SCRATCH_BYTES == mla::kWsHeaderBytes + 2 * MLA_FP4_STATIC_MAX_CTAS * mla::kSlotBytes, "static scratch size");
 
 extern "C" {
 

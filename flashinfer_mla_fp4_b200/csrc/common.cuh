@@ -28,11 +28,20 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr size_t kSlotOBytes = size_t(kLatent) * kGroupHeads * 2;
 constexpr size_t kSlotBytes = kSlotOBytes + kGroupHeads * sizeof(float) + 16;
 constexpr float kSlotHalfRange = 32768.f;
-MLA_HD uint16_t* slot_o(void* ws, int slot) { return reinterpret_cast<uint16_t*>(static_cast<char*>(ws) + size_t(slot) * kSlotBytes); }
-MLA_HD float* slot_lse(void* ws, int slot) { return reinterpret_cast<float*>(static_cast<char*>(ws) + size_t(slot) * kSlotBytes + kSlotOBytes); }
-MLA_HD const uint16_t* slot_o(const void* ws, int slot) { return reinterpret_cast<const uint16_t*>(static_cast<const char*>(ws) + size_t(slot) * kSlotBytes); }
+// The workspace starts with a header of counters that are zero whenever no decode step is running
+// (a step that completes leaves them zero again); the slots follow.  Counter pair c belongs to the
+// split request whose first CTA is c: how many of its partials have been published, how many of
+// its CTAs have finished merging.
+constexpr size_t kWsHeaderBytes = MLA_FP4_WORKSPACE_HEADER_BYTES;
+MLA_HD int32_t* ws_arrived(void* ws) { return static_cast<int32_t*>(ws); }
+MLA_HD int32_t* ws_done(void* ws) { return static_cast<int32_t*>(ws) + 256; }
+MLA_HD char* slot_base(void* ws, int slot) { return static_cast<char*>(ws) + kWsHeaderBytes + size_t(slot) * kSlotBytes; }
+MLA_HD const char* slot_base(const void* ws, int slot) { return static_cast<const char*>(ws) + kWsHeaderBytes + size_t(slot) * kSlotBytes; }
+MLA_HD uint16_t* slot_o(void* ws, int slot) { return reinterpret_cast<uint16_t*>(slot_base(ws, slot)); }
+MLA_HD float* slot_lse(void* ws, int slot) { return reinterpret_cast<float*>(slot_base(ws, slot) + kSlotOBytes); }
+MLA_HD const uint16_t* slot_o(const void* ws, int slot) { return reinterpret_cast<const uint16_t*>(slot_base(ws, slot)); }
 MLA_HD float* slot_scale(void* ws, int slot) { return slot_lse(ws, slot) + kGroupHeads; }
-MLA_HD const float* slot_lse(const void* ws, int slot) { return reinterpret_cast<const float*>(static_cast<const char*>(ws) + size_t(slot) * kSlotBytes + kSlotOBytes); }
+MLA_HD const float* slot_lse(const void* ws, int slot) { return reinterpret_cast<const float*>(slot_base(ws, slot) + kSlotOBytes); }
 MLA_HD const float* slot_scale(const void* ws, int slot) { return slot_lse(ws, slot) + kGroupHeads; }
 // power-of-two scale that maps `bound` (an upper bound of |O|) to at most kSlotHalfRange
 MLA_HD float slot_scale_for(float bound) { return exp2f(ceilf(log2f(fmaxf(bound, 1e-30f) / kSlotHalfRange))); }
@@ -49,7 +58,8 @@ constexpr int kMaxCombineSlots = 148;
 // of segments (v, tile_begin, tile_end); only its first and its last segment can cover a request
 // partially.  A partial segment writes a split-KV partial into workspace slot 2*i (first
 // segment of the CTA) or 2*i+1 (any later one); a segment that covers its request completely
-// writes the final output itself.  The combine kernel merges the slots of every split request.
+// writes the final output itself.  The slots of every split request are merged at the end of the
+// decode kernel by the CTAs that wrote them (or, in the two-kernel mode, by the combine kernel).
 // ----------------------------------------------------------------------------------------------
 
 MLA_HD int tiles_of(int seq_len) { return seq_len > 0 ? (seq_len + kTile - 1) / kTile : 0; }
@@ -104,6 +114,7 @@ struct Walker {
   int b, g, t;     // current request, group, tile inside the request
   bool first;      // next segment is the first of this CTA
   int cta;
+  int64_t Tt;      // size of the flat tile space (device walkers only)
 
   MLA_HD bool next(Segment& s) {
     while (f < hi) {
@@ -177,6 +188,7 @@ __device__ __forceinline__ Walker make_walker(const int32_t* seq_lens, int batch
   w.seq_lens = seq_lens; w.batch = batch; w.groups = groups; w.cta = cta; w.first = true;
   int64_t T = warp_total_tiles(seq_lens, batch);
   int64_t Tt = T * groups;
+  w.Tt = Tt;
   w.f = cta_lo(Tt, n, cta);
   w.hi = cta_lo(Tt, n, cta + 1);
   w.b = 0; w.g = groups; w.t = 0;

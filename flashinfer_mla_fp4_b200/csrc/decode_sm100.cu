@@ -15,9 +15,13 @@
 // into 128-byte-swizzled shared memory, where the very same bytes serve as the K-major A operand
 // of QK^T and as the MN-major A operand of PV.  RoPE bytes, per-token scales and Q arrive by TMA.
 //
-// Warp roles (576 threads): 0-7 softmax / O rescale / epilogue (TMEM lane = token or dim; two warps
-// share a lane quarter and split the 64 heads), 8-15 latent load + dequant, 16 MMA issue (warp-uniform,
-// one elected lane per instruction), 17 TMA issue.
+// Warp roles (608 threads): 0-7 softmax / O rescale / epilogue (TMEM lane = token or dim; two warps
+// share a lane quarter and split the 64 heads), 8-15 latent load + dequant, 16 QK^T issue, 17 TMA issue,
+// 18 PV issue (issue warps run warp-uniform code, one elected lane per instruction).
+//
+// Requests that are split across CTAs are merged at the end of the same kernel (tail_merge): the
+// CTAs publish their partials through counters in the workspace header and each takes a share of
+// the output dims.  The two-kernel mode leaves the merge to the combine kernel instead.
 //
 // The per-role loops are kept small on purpose: the four instruction streams share one
 // instruction cache, and an MMA-issue or softmax loop that misses it starves the tensor pipe.
@@ -71,7 +75,7 @@ constexpr int kNumBars = 2 * 4 /*kv_full*/ + 2 * 4 /*kv_empty*/ + 2 /*aux_full*/
                          2 /*p_full*/ + 1 /*q_full*/ + 1 /*q_empty*/ + 1 /*o_free*/ + 1 /*drain*/;
 constexpr uint32_t kOffSegs = kOffBars + kNumBars * 8;                    // Segment[kMaxSeg]
 constexpr uint32_t kOffMisc = kOffSegs + kMaxSeg * 24;                    // tmem base, abort flag, walker
-constexpr uint32_t kSmemBytes = kOffMisc + 128;
+constexpr uint32_t kSmemBytes = kOffMisc + 256;
 constexpr uint32_t kSmemAlloc = kSmemBytes + 1024;                        // slack for manual 1024-alignment
 static_assert(sizeof(Segment) == 24, "segment staging layout");
 static_assert(kSmemAlloc <= 232448, "shared memory budget exceeded");
@@ -94,14 +98,26 @@ constexpr uint32_t kColO = 256;      // + 64 * block
 constexpr uint32_t kIdescQK = ptx::idesc_e4m3(128, kGroupHeads, false, false);
 constexpr uint32_t kIdescPV = ptx::idesc_e4m3(128, kGroupHeads, true, true);
 
+// A split request this CTA wrote a partial for (at most two: its first and its last segment).
+struct MergeReq {
+  int b, g, tiles;
+  int counter;    // index of the request's counters in the workspace header: the first CTA of its span
+  int slot;       // the slot this CTA wrote (even: the segment was the CTA's first)
+  int64_t start;  // flat tile index of the request's first tile
+};
 struct Misc {
   uint32_t tmem_base;
   volatile int abort;
   int nseg;   // segments staged for the current round
   int more;   // another round follows
   Walker walker;
+  int n_merge;
+  MergeReq merge[2];
+  // scratch of the tail merge
+  int64_t total_tiles;
+  int n_slots, n_part, rank;
 };
-static_assert(sizeof(Misc) <= 128, "misc area");
+static_assert(sizeof(Misc) <= 256, "misc area");
 
 struct Ctx {
   uint32_t smem;      // shared-space address of the aligned base
@@ -114,6 +130,7 @@ struct Ctx {
 struct RoleState {
   uint32_t it;   // tiles processed so far by this CTA (selects stage and barrier phase)
   uint32_t seg;  // segments processed so far
+  uint32_t part; // partial segments processed so far (softmax role)
 };
 
 __device__ __forceinline__ uint32_t bar_addr(const Ctx& c, int idx) { return c.smem + kOffBars + 8u * idx; }
@@ -134,6 +151,7 @@ __device__ __noinline__ void flag_timeout(const Ctx& c, int idx, uint32_t parity
 // Bounded wait.  Returns false (and flags the CTA) when the wait expires or the CTA is aborting.
 __device__ __noinline__ bool wait_slow(const Ctx& c, int idx, uint32_t parity) {
   const uint32_t bar = bar_addr(c, idx);
+#pragma unroll 1
   for (uint32_t i = 0; i < (1u << 22); ++i) {
     if (c.misc->abort) return false;
     if (ptx::mbar_try_wait(bar, parity)) return true;  // suspends in hardware for a while: not a hot spin
@@ -155,6 +173,7 @@ __device__ __forceinline__ bool wait_warp(const Ctx& c, int idx, uint32_t parity
 // Bounded wait that ignores the abort flag: lets in-flight asynchronous work land before exit.
 __device__ __noinline__ void drain_wait(const Ctx& c, int idx, uint32_t parity) {
   const uint32_t bar = bar_addr(c, idx);
+#pragma unroll 1
   for (uint32_t i = 0; i < (1u << 20); ++i) {
     if (ptx::mbar_try_wait(bar, parity)) return;
     __nanosleep(64);
@@ -804,6 +823,14 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       if (!c.misc->abort) write_output(p, c, tmem_lane, row, half, tid, g.b, g.g, g.slot, slot_scale_v);
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar_addr(c, kBarOFree));
+      if (g.slot >= 0) {
+        if (p.fused_merge) {  // publish the partial: the tail merge of the request's CTAs waits for this count
+          __threadfence();
+          ptx::bar_sync(1, kSoftmaxThreads);
+          if (tid == 0) atomicAdd(ws_arrived(p.workspace) + c.misc->merge[st.part].counter, 1);
+        }
+        ++st.part;
+      }
       if (tid == 0) MLA_TRACE(0, lit, 6);
     }
   }
@@ -819,6 +846,15 @@ __device__ __noinline__ void stage_segments(const Ctx& c) {
   while (n < kMaxSeg) {
     if (!w.next(s)) break;
     out[n++] = s;
+    if (s.slot >= 0 && c.misc->n_merge < 2) {
+      MergeReq& m = c.misc->merge[c.misc->n_merge++];
+      m.b = s.b;
+      m.g = s.g;
+      m.tiles = tiles_of(s.seq_len);
+      m.start = w.f - int64_t(s.tile_end);  // w.f is the flat index just past this segment
+      m.counter = cta_of_tile(w.Tt, int(gridDim.x), m.start);
+      m.slot = s.slot;
+    }
   }
   if (n == kMaxSeg) {  // is there anything left?
     Walker probe = w;
@@ -827,6 +863,235 @@ __device__ __noinline__ void stage_segments(const Ctx& c) {
   c.misc->walker = w;
   c.misc->nseg = n;
   c.misc->more = more ? 1 : 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// tail: merge of the split-KV partials inside the decode kernel
+// ------------------------------------------------------------------------------------------
+// Every CTA that wrote a partial of a split request publishes it (a counter in the workspace
+// header) right after writing it.  In the tail, the CTAs whose partial of a request was their
+// first segment wait until all partials of that request are there and then merge, each, a share
+// of the 512 output dims: out = sum_i w_i * O_i with w_i = 2^(lse_i - max) / sum * slot scale, the
+// same arithmetic as the combine kernel.  A CTA has published everything it will ever publish
+// before it waits for anybody else, so the waits cannot form a cycle; the launch is cooperative,
+// so every CTA of the grid is resident; the waits are bounded like all others.  The last CTA to
+// finish a request's merge zeroes its counters again.
+constexpr int kTailLseStride = kGroupHeads + 4;                        // padded: the slot lanes of a unit hit different banks
+constexpr uint32_t kTailLse = kOffKV;                                  // [148][68] f32: LSEs, then weights
+constexpr uint32_t kTailList = kTailLse + kMaxCombineSlots * kTailLseStride * 4;  // [148] slot ids
+constexpr uint32_t kTailScale = kTailList + kMaxCombineSlots * 4;      // [148] f32 slot scales
+static_assert(kTailScale + kMaxCombineSlots * 4 <= kOffKV + kStages * kBlocks * kBlockBytes, "tail scratch fits the idle KV ring");
+
+__device__ __forceinline__ int ld_acquire(const int32_t* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// The tail runs once per CTA, so its instructions are fetched cold: it is written for few
+// instructions (rolled loops, no 64-bit division, approximate exp2/log2), not for peak throughput.
+__device__ __noinline__ void zero_empty_requests(const DecodeParams& p, int tid) {
+  const int total = p.groups * p.batch;
+  const uint32_t esz = p.out_dtype == MLA_FP4_OUT_BF16 ? 2u : 4u;
+#pragma unroll 1
+  for (int v = blockIdx.x; v < total; v += gridDim.x) {
+    const int g = v / p.batch, b = v - g * p.batch;
+    if (p.seq_lens[b] > 0) continue;
+    int qpos, head0;
+    group_coords(g, p.num_heads, qpos, head0);
+    const int heads_here = min(kGroupHeads, p.num_heads - head0);
+    const size_t row0 = (size_t(b) * p.q_len + qpos) * p.num_heads + head0;
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(p.out) + row0 * kLatent * esz);
+    const uint32_t n16 = uint32_t(heads_here) * kLatent * esz / 16u;
+#pragma unroll 1
+    for (uint32_t i = tid; i < n16; i += kThreads) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (p.lse && tid < heads_here) p.lse[row0 + tid] = -INFINITY;
+  }
+}
+
+__device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int tid) {
+  Misc* misc = c.misc;
+  float* lse_s = reinterpret_cast<float*>(c.smem_ptr + kTailLse);
+  int* list_s = reinterpret_cast<int*>(c.smem_ptr + kTailList);
+  float* scale_s = reinterpret_cast<float*>(c.smem_ptr + kTailScale);
+  void* ws = p.workspace;
+  const int n = gridDim.x;
+  const int n_merge = misc->n_merge;
+
+#pragma unroll 1
+  for (int k = 0; k < n_merge; ++k) {
+    const MergeReq m = misc->merge[k];
+    // A CTA merges only the request of its first segment (even slot): every CTA then takes part in
+    // at most one merge, and the first writer of a request, which reaches it last, in none.
+    if (m.slot & 1) continue;
+    int32_t* arrived = ws_arrived(ws) + m.counter;
+    int32_t* done = ws_done(ws) + m.counter;
+    if (tid == 0) {
+      // Writers of the request: CTA m.counter, then every following CTA whose range starts before
+      // the request ends.  lo(i) = floor(Tt*i/n) is advanced without division: lo(i+1) = lo(i) + q
+      // + carry of the remainders.  The first writer uses slot 2i+1 unless its range starts with
+      // the request; the others start inside the request and use slot 2i; empty ranges write nothing.
+      const int64_t Tt = misc->walker.Tt;
+      const int64_t q = Tt / n, r = Tt - q * n;
+      const int64_t end = m.start + m.tiles;
+      int64_t lo = cta_lo(Tt, n, m.counter), rem = (r * m.counter) % n;
+      int cnt = 0, part = 0, rank = 0;
+#pragma unroll 1
+      for (int i = m.counter; i < n && lo < end; ++i) {
+        int64_t nlo = lo + q;
+        rem += r;
+        if (rem >= n) { rem -= n; ++nlo; }
+        if (nlo > lo) {  // a non-empty range
+          const bool first_seg = lo >= m.start;
+          if (cnt < kMaxCombineSlots) list_s[cnt] = slot_of(i, first_seg);
+          ++cnt;
+          if (first_seg) {  // this writer takes part in the merge
+            if (i == int(blockIdx.x)) rank = part;
+            ++part;
+          }
+        }
+        lo = nlo;
+      }
+      const int ns = min(cnt, kMaxCombineSlots);
+      misc->n_slots = ns;
+      misc->n_part = part;
+      misc->rank = rank;
+      bool ok = false;  // bounded wait for the other writers
+#pragma unroll 1
+      for (uint32_t i = 0; i < (1u << 22); ++i) {
+        if (ld_acquire(arrived) >= ns) { ok = true; break; }
+        if (misc->abort) break;
+        __nanosleep(32);
+      }
+      if (!ok && !misc->abort) flag_timeout(c, 100 + k, uint32_t(ns));
+    }
+    __syncthreads();
+    const int ns = misc->n_slots, np = misc->n_part, rank = misc->rank;
+    if (tid == 0) MLA_TRACE(3, 1u, 2);
+    if (!misc->abort) {
+      int qpos, head0;
+      group_coords(m.g, p.num_heads, qpos, head0);
+      const int heads_here = min(kGroupHeads, p.num_heads - head0);
+      const size_t row0 = (size_t(m.b) * p.q_len + qpos) * p.num_heads + head0;
+      // one round of independent loads: every LSE and every slot scale of the request
+#pragma unroll 1
+      for (int idx = tid; idx < ns * (kGroupHeads + 1); idx += kThreads) {
+        const int i = idx / (kGroupHeads + 1), h = idx - i * (kGroupHeads + 1);
+        const float v = __ldcg(slot_lse(ws, list_s[i]) + h);  // element 64 is the slot scale
+        if (h < kGroupHeads) lse_s[i * kTailLseStride + h] = v;
+        else scale_s[i] = v;
+      }
+      __syncthreads();
+      if (tid == 0) MLA_TRACE(3, 1u, 3);
+      if (tid < 8 * kGroupHeads) {  // eight lanes per head split the slots; butterflies give all of them the result
+        const int h = tid >> 3, j = tid & 7;
+        float* col = lse_s + h;
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int i = j; i < ns; i += 8) mx = fmaxf(mx, col[i * kTailLseStride]);
+#pragma unroll
+        for (int off = 4; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        float dsum = 0.f;
+#pragma unroll 1
+        for (int i = j; i < ns; i += 8) {
+          const float l = col[i * kTailLseStride];
+          const float e = (l == -INFINITY) ? 0.f : ptx::ex2(l - mx);
+          col[i * kTailLseStride] = e;
+          dsum += e;
+        }
+#pragma unroll
+        for (int off = 4; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
+        const float inv = dsum > 0.f ? __frcp_rn(dsum) : 0.f;
+#pragma unroll 1
+        for (int i = j; i < ns; i += 8) col[i * kTailLseStride] *= inv * scale_s[i];  // weights, times the slot's fp16 scale
+        if (j == 0 && rank == 0 && p.lse && h < heads_here) p.lse[row0 + h] = (dsum > 0.f) ? (__log2f(dsum) + mx) : -INFINITY;
+      }
+      __syncthreads();
+      if (tid == 0) MLA_TRACE(3, 1u, 4);
+      // This CTA's dims: pairs [256*rank/np, 256*(rank+1)/np).  A unit is (pair of dims, 8 heads, slot
+      // lane); the SL lanes of a unit are consecutive lanes of a warp, split the slots (at most four
+      // each, all their loads in flight together) and add their sums with a fixed shuffle tree
+      // (bit-reproducible).  Lane 0 of the unit writes 8 x 2 outputs.
+      const int u0 = (256 * rank) / np, u1 = (256 * (rank + 1)) / np;
+      const int d0 = 2 * u0, pairs = u1 - u0;
+      const int items = pairs * 8;
+      int SL = 1, lg = 0;
+      while (SL < 32 && 4 * SL < ns) { SL *= 2; ++lg; }
+      const int units = items << lg;
+#pragma unroll 1
+      for (int base = (tid & ~31); base < units; base += kThreads) {
+        const int unit = base + (tid & 31);
+        const bool live_unit = unit < units;
+        const int item = min(unit, units - 1) >> lg, sl = unit & (SL - 1);
+        const int o = item & 7, pr = item >> 3;
+        const char* src = reinterpret_cast<const char*>(slot_o(ws, 0) + size_t(d0 + 2 * pr) * kGroupHeads + 8 * o);
+        const float* wrow = lse_s + 8 * o;
+        float acc[2][8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[0][e] = acc[1][e] = 0.f;
+#pragma unroll 1
+        for (int i0 = sl; i0 < ns; i0 += 4 * SL) {  // four slots x two dims: eight independent 16-byte loads in flight
+          uint4 a[4][2];
+#pragma unroll
+          for (int qq = 0; qq < 4; ++qq) {
+            const bool ld = live_unit && i0 + qq * SL < ns;  // no load for a slot that does not exist
+            const char* sp = src + size_t(list_s[min(i0 + qq * SL, ns - 1)]) * kSlotBytes;
+            a[qq][0] = ld ? __ldcg(reinterpret_cast<const uint4*>(sp)) : make_uint4(0u, 0u, 0u, 0u);
+            a[qq][1] = ld ? __ldcg(reinterpret_cast<const uint4*>(sp + kGroupHeads * 2)) : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int qq = 0; qq < 4; ++qq) {
+            const int i = i0 + qq * SL;
+            const float* w = wrow + min(i, ns - 1) * kTailLseStride;  // data of a missing slot is zero
+            const float4 w0 = *reinterpret_cast<const float4*>(w), w1 = *reinterpret_cast<const float4*>(w + 4);
+            const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int dd = 0; dd < 2; ++dd) {
+              const uint32_t u[4] = {a[qq][dd].x, a[qq][dd].y, a[qq][dd].z, a[qq][dd].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u[e]));
+                acc[dd][2 * e] += wv[2 * e] * f.x;
+                acc[dd][2 * e + 1] += wv[2 * e + 1] * f.y;
+              }
+            }
+          }
+        }
+#pragma unroll 1
+        for (int off = SL >> 1; off > 0; off >>= 1) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            acc[0][e] += __shfl_down_sync(0xffffffffu, acc[0][e], off);
+            acc[1][e] += __shfl_down_sync(0xffffffffu, acc[1][e], off);
+          }
+        }
+        if (live_unit && sl == 0) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int h = 8 * o + e;
+            if (h < heads_here) {
+              const size_t idx = (row0 + h) * kLatent + d0 + 2 * pr;
+              if (p.out_dtype == MLA_FP4_OUT_BF16) {
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(acc[0][e], acc[1][e]);
+                *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(p.out) + idx) = *reinterpret_cast<uint32_t*>(&b2);
+              } else {
+                *reinterpret_cast<float2*>(reinterpret_cast<float*>(p.out) + idx) = make_float2(acc[0][e], acc[1][e]);
+              }
+            }
+          }
+        }
+      }
+      if (tid == 0) MLA_TRACE(3, 1u, 5);
+    }
+    __syncthreads();
+    if (tid == 0) {  // the last CTA through leaves the counters of this request at zero
+      const int old = atomicAdd(done, 1);
+      if (old == np - 1) {
+        *done = 0;
+        *arrived = 0;
+      }
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -853,6 +1118,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
     if (tid == 0) {
       c.misc->walker = w;
       c.misc->abort = 0;
+      c.misc->n_merge = 0;
       stage_segments(c);
     }
     __syncwarp();
@@ -891,6 +1157,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   RoleState st;
   st.it = 0;
   st.seg = 0;
+  st.part = 0;
   // Rounds: almost always exactly one; more only when a CTA's range spans more than kMaxSeg requests.
   for (;;) {
     if (warp < 8) {
@@ -947,6 +1214,11 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   if (warp == 0) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, 512);
+  }
+  if (p.fused_merge) {
+    tail_merge(p, c, tid);
+    zero_empty_requests(p, tid);
+    if (tid == 0) MLA_TRACE(3, 0u, 5);
   }
 }
 
@@ -1021,8 +1293,17 @@ cudaError_t launch_decode_sm100(const DecodeParams& p, int num_ctas, cudaStream_
       if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
   }
-  mla_fp4_decode_sm100_kernel<<<num_ctas, kThreads, kSmemAlloc, stream>>>(p, map_q_lat, map_q_rope, map_rope);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(num_ctas);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemAlloc;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;  // the CTAs wait for one another in the tail merge
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = p.fused_merge ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, mla_fp4_decode_sm100_kernel, p, map_q_lat, map_q_rope, map_rope);
 }
 
 }  // namespace mla

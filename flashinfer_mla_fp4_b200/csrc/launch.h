@@ -22,6 +22,7 @@ struct DecodeParams {
   float softmax_scale, output_scale;
   int32_t out_dtype;
   int32_t pdl;
+  int32_t fused_merge;  // the decode kernel merges the split-KV partials itself (cooperative launch)
 };
 
 struct CombineParams {

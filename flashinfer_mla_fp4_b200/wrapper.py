@@ -49,7 +49,7 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         self._kernel = _cabi.KERNEL_TCGEN05
         self._status: Optional[torch.Tensor] = None
         self._num_ctas = 0
-        self._phase_mask = 0  # profiling aid: 1 = decode kernel only, 2 = combine kernel only
+        self._phase_mask = 0  # profiling aid of the two-kernel mode: 1 = decode kernel only, 2 = combine kernel only
 
     # ------------------------------------------------------------------ plan
     def plan(
@@ -101,7 +101,15 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         self._num_ctas = torch.cuda.get_device_properties(self._device).multi_processor_count
         if self._status is None:
             self._status = torch.zeros(8, dtype=torch.int32, device=self._device)
+        self._init_workspace()
         self._planned = True
+
+    def _init_workspace(self) -> None:
+        """Zero the workspace's counter header (every completed step leaves it zero again)."""
+        if self._workspace_buffer.is_cuda and self._workspace_buffer.numel() >= _cabi.WORKSPACE_HEADER_BYTES:
+            with torch.cuda.device(self._device):
+                _cabi.workspace_init(self._workspace_buffer.data_ptr(), self._workspace_buffer.numel(),
+                                     torch.cuda.current_stream(self._device).cuda_stream)
 
     # ------------------------------------------------------------------ run
     def _validate_run_inputs(self, q, kv_cache, kv_cache_sf, out) -> None:
@@ -225,6 +233,7 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         st = self.device_status()
         if st[0] != 0:
             self._status.zero_()
+            self._init_workspace()  # a step that timed out may have left the merge counters non-zero
             raise RuntimeError(
                 f"mla_fp4 device error {st[0]} (barrier {st[1]}, CTA {st[2]}, thread {st[3]}, parity {st[4]})"
             )

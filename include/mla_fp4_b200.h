@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define MLA_FP4_ABI_VERSION 1
+#define MLA_FP4_ABI_VERSION 2
 
 /* status codes */
 #define MLA_FP4_OK 0
@@ -39,8 +39,16 @@ extern "C" {
 #define MLA_FP4_GROUP_HEADS 64           /* query heads handled by one CTA                     */
 
 /* kernel selection for mla_fp4_decode */
-#define MLA_FP4_KERNEL_TCGEN05 0         /* the product path: TMA + tcgen05/TMEM               */
+#define MLA_FP4_KERNEL_TCGEN05 0         /* the product path: TMA + tcgen05/TMEM, one kernel that
+                                            also merges the split-KV partials                  */
 #define MLA_FP4_KERNEL_FP32_CHECK 1      /* plain-FP32 CUDA-core kernel, a test cross-check    */
+#define MLA_FP4_KERNEL_TCGEN05_2PASS 2   /* the tcgen05 kernel followed by a separate combine
+                                            kernel (the reference's two-kernel structure)      */
+
+/* The workspace starts with this many bytes of counters that must be zero before the first
+   decode step on that workspace (mla_fp4_workspace_init) and that every completed step leaves
+   zero; the split-KV partial slots follow. */
+#define MLA_FP4_WORKSPACE_HEADER_BYTES 2048
 
 /* output element types (reference: out dtype bf16 default, wrappers/batch_mla_fp4.py:228) */
 #define MLA_FP4_OUT_BF16 0
@@ -68,7 +76,8 @@ typedef struct MlaFp4DecodeArgs {
      computes it (wrappers/batch_mla_fp4.py:433-437) but does not return it. */
   float* lse;
   /* caller-owned scratch for split-KV partials (the reference slices the wrapper's
-     int8 workspace buffer, wrappers/batch_mla_fp4.py:413-420). */
+     int8 workspace buffer, wrappers/batch_mla_fp4.py:413-420); 16-byte aligned, prepared once
+     with mla_fp4_workspace_init. */
   void* workspace;
   size_t workspace_bytes;
   /* int32[8] device status words, zeroed by the caller before first use; word 0 becomes
@@ -80,8 +89,10 @@ typedef struct MlaFp4DecodeArgs {
   int32_t out_dtype;   /* MLA_FP4_OUT_*    */
   int32_t kernel;      /* MLA_FP4_KERNEL_* */
   int32_t num_ctas;    /* CTAs of the persistent decode grid; 0 = one per SM of the current device */
-  int32_t enable_pdl;  /* programmatic dependent launch between decode and combine (0/1) */
-  int32_t phase_mask;  /* 0 = decode + combine; 1 = decode kernel only; 2 = combine kernel only (profiling) */
+  int32_t enable_pdl;  /* programmatic dependent launch: lets the next kernel on the stream start its
+                          prologue while the decode kernel drains (0/1) */
+  int32_t phase_mask;  /* two-kernel modes only: 0 = decode + combine; 1 = decode kernel only;
+                          2 = combine kernel only (profiling) */
   void* stream;        /* cudaStream_t */
 } MlaFp4DecodeArgs;
 
@@ -109,9 +120,16 @@ int mla_fp4_plan_partition(const int32_t* seq_lens_host, int32_t batch, int32_t 
                            int32_t* seg_tile_begin, int32_t* seg_tile_end, int32_t* seg_slot,
                            int32_t* num_segments);
 
-/* One decode step: launches the decode kernel and the split-KV combine kernel on args->stream.
-   Stands in for the compiled callable invoked at wrappers/batch_mla_fp4.py:441-457
-   (mla_decode_fp4.py:60-305: split_kv_kernel + reduction_kernel). */
+/* Zero the counter header of a workspace (an asynchronous memset on `stream`).  Call once after
+   allocating the workspace, and again after a step that reported MLA_FP4_ERR_DEVICE_TIMEOUT.
+   The reference's workspace needs no preparation (wrappers/batch_mla_fp4.py:413-420). */
+int mla_fp4_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
+/* One decode step on args->stream: one persistent kernel that computes the attention and merges
+   the split-KV partials (its CTAs wait for one another at the end, so it is launched
+   cooperatively: the grid must fit the device).  Stands in for the compiled callable invoked at
+   wrappers/batch_mla_fp4.py:441-457 (mla_decode_fp4.py:60-305: split_kv_kernel +
+   reduction_kernel). */
 int mla_fp4_decode(const MlaFp4DecodeArgs* args);
 
 /* Merge `parts` normalised partial outputs with base-2 LSEs (decode context parallel):
@@ -133,7 +151,7 @@ int mla_fp4_dequant_e2m1_to_e4m3(const void* packed, void* out, int64_t n_bytes,
 /* Largest decode grid the allocation-free variant below accepts, and the bytes of device memory
    its built-in scratch occupies on every GPU that loads the library (until the process exits). */
 #define MLA_FP4_STATIC_MAX_CTAS 148
-#define MLA_FP4_STATIC_SCRATCH_BYTES (2 * MLA_FP4_STATIC_MAX_CTAS * 65808)
+#define MLA_FP4_STATIC_SCRATCH_BYTES (MLA_FP4_WORKSPACE_HEADER_BYTES + 2 * MLA_FP4_STATIC_MAX_CTAS * 65808)
 
 /* No counterpart in the reference.  Same decode step as mla_fp4_decode, for callers that may not
    allocate device memory and have no workspace buffer to lend: plugins running inside an engine
@@ -148,7 +166,8 @@ int mla_fp4_dequant_e2m1_to_e4m3(const void* packed, void* out, int64_t n_bytes,
    - The first call on a device looks the scratch address up once (with that device current) and
      keeps it; make that first call before any stream capture begins.
    - All calls on a device share the one scratch array.  It keeps the previous call's partials, which
-     is harmless: a step only reads the slots it has just written, so nothing has to start at zero.
+     is harmless: a step only reads the slots it has just written.  Its counter header starts at
+     zero (static storage) and every completed step leaves it zero.
      Two calls whose kernels overlap on the GPU (different streams) would overwrite each other's
      partials: run them in order on one stream, or use mla_fp4_decode with separate workspaces. */
 int mla_fp4_decode_static(const MlaFp4DecodeArgs* args);

@@ -14,7 +14,7 @@ from oracle import mla_fp4_oracle as O
 
 pytestmark = pytest.mark.gpu
 
-KERNELS = {"tcgen05": 0, "fp32_check": 1}
+KERNELS = {"tcgen05": 0, "fp32_check": 1, "tcgen05_2pass": 2}
 
 
 def _dev():
@@ -90,7 +90,7 @@ def test_heads_and_page_sizes(heads, page_size, kernel):
     check_case(synth.build_case("hp", [700, 129, 64, 2500], heads, page_size, seed=heads + page_size, device=_dev()), kernel)
 
 
-@pytest.mark.parametrize("kernel", ["fp32_check", "tcgen05"])
+@pytest.mark.parametrize("kernel", ["fp32_check", "tcgen05", "tcgen05_2pass"])
 def test_ragged_batch_with_empty_requests(kernel):
     from flashinfer_mla_fp4_b200 import synth
 
@@ -101,7 +101,7 @@ def test_ragged_batch_with_empty_requests(kernel):
     check_case(case, kernel)
 
 
-@pytest.mark.parametrize("kernel", ["fp32_check", "tcgen05"])
+@pytest.mark.parametrize("kernel", ["fp32_check", "tcgen05", "tcgen05_2pass"])
 def test_q_len_two_and_output_scale_and_f32_out(kernel):
     from flashinfer_mla_fp4_b200 import synth
 

@@ -22,7 +22,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in the header but not exported"
     assert set(_cabi.EXPORTS) == declared
-    assert lib.mla_fp4_abi_version() == 1
+    assert lib.mla_fp4_abi_version() == _cabi.ABI_VERSION == 2
 
 
 def test_abi_rejects_bad_arguments_without_a_gpu():
@@ -32,7 +32,8 @@ def test_abi_rejects_bad_arguments_without_a_gpu():
     assert "null" in _cabi.last_error()
     n = ctypes.c_size_t(0)
     assert _cabi.lib.mla_fp4_workspace_bytes(8, 1, 64, 148, ctypes.byref(n)) == 0
-    assert n.value == 2 * 148 * (512 * 64 * 2 + 64 * 4 + 16)
+    assert n.value == 2048 + 2 * 148 * (512 * 64 * 2 + 64 * 4 + 16)  # counter header + two slots per CTA
+    assert _cabi.lib.mla_fp4_workspace_init(None, 4096, None) == _cabi.ERR_BAD_ARG
     assert _cabi.lib.mla_fp4_workspace_bytes(8, 0, 64, 148, ctypes.byref(n)) == _cabi.ERR_BAD_ARG
     with pytest.raises(ValueError):
         _cabi.check(_cabi.ERR_WORKSPACE_TOO_SMALL)

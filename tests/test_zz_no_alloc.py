@@ -51,6 +51,7 @@ def test_static_scratch_entry_point_matches_regular_entry_point():
              synth.build_case("na1", [3000, 4097, 12000], 128, 32, seed=42, device=dev)]
     status = torch.zeros(8, dtype=torch.int32, device=dev)
     ws = torch.empty(64 << 20, dtype=torch.int8, device=dev)
+    _cabi.workspace_init(ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)  # counter header
     for case in cases:  # two static calls in a row, each checked against the regular entry point
         shape = (case.batch, case.q_len, case.num_heads, 512)
         ref_out = torch.zeros(shape, dtype=torch.bfloat16, device=dev)
