@@ -42,6 +42,11 @@ L2_BYTES = 126 * 1024 * 1024
 PUBLISHED_US = {"northstar": 37.726, "uniform": 13.461}  # reference README, one B300, cold L2
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel, from the ncu capture summarised in
+# profiles/decode_sm100_northstar_ncu_full.md (85.39 MB read + 8.20 MB written); None where no capture exists.
+NCU_TRAFFIC_BYTES = {("northstar", "fused"): 93.6e6}
+
+
 def peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -360,7 +365,7 @@ def main() -> None:
             "tb_per_s": kv_bytes_all / (us * 1e-6) / 1e12,
             "tflops": flops_all / (us * 1e-6) / 1e12,
             "roofline": {"bound": "hbm" if t_hbm >= t_fp8 else "tensor", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": achieved / hbm_peak, "traffic": None, "peak_kind": peak_kind,
+                         "frac": achieved / hbm_peak, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.kernel)), "peak_kind": peak_kind,
                          "kernel": "mla_fp4_decode_sm100_kernel", "kernel_mode": args.kernel, "kernel_us": kernel_us, "algorithmic_bytes": case.step_bytes(),
                          "roofline_us": max(t_hbm, t_fp8), "step_frac_of_roofline": max(t_hbm, t_fp8) / us,
                          "fp8_peak_tflops_assumed": fp8_peak},
