@@ -25,6 +25,7 @@ KERNEL_TCGEN05 = 0
 KERNEL_FP32_CHECK = 1
 KERNEL_TCGEN05_2PASS = 2
 WORKSPACE_HEADER_BYTES = 2048
+IN_BF16, IN_F16, IN_F32 = 0, 1, 2
 OUT_BF16 = 0
 OUT_F32 = 1
 
@@ -67,6 +68,7 @@ EXPORTS = (
     "mla_fp4_decode",
     "mla_fp4_merge_partials",
     "mla_fp4_dequant_e2m1_to_e4m3",
+    "mla_fp4_cache_write",
     "mla_fp4_decode_static",
 )
 
@@ -97,6 +99,9 @@ def _load() -> C.CDLL:
     lib.mla_fp4_merge_partials.restype = C.c_int
     lib.mla_fp4_dequant_e2m1_to_e4m3.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
     lib.mla_fp4_dequant_e2m1_to_e4m3.restype = C.c_int
+    lib.mla_fp4_cache_write.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p,
+                                        C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
+    lib.mla_fp4_cache_write.restype = C.c_int
     v = lib.mla_fp4_abi_version()
     if v != ABI_VERSION:
         raise ImportError(f"{LIB_PATH} has ABI version {v}, expected {ABI_VERSION}: rebuild it")

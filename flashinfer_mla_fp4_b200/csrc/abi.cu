@@ -232,6 +232,26 @@ int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, i
   return MLA_FP4_OK;
 }
 
+int mla_fp4_cache_write(const void* latent, int64_t latent_stride, const void* rope, int64_t rope_stride,
+                        int32_t in_dtype, const float* token_scale, const int64_t* slot_mapping,
+                        int64_t num_tokens, void* kv_cache, float* kv_cache_sf, int64_t num_slots, void* stream) {
+  if (num_tokens < 0 || num_slots < 0) return fail(MLA_FP4_ERR_BAD_ARG, "num_tokens/num_slots out of range");
+  if (num_tokens == 0) return MLA_FP4_OK;
+  if (!latent || !rope || !kv_cache || !kv_cache_sf) return fail(MLA_FP4_ERR_BAD_ARG, "null pointer");
+  if (in_dtype != MLA_FP4_IN_BF16 && in_dtype != MLA_FP4_IN_F16 && in_dtype != MLA_FP4_IN_F32)
+    return fail(MLA_FP4_ERR_UNSUPPORTED, "in_dtype must be MLA_FP4_IN_BF16, MLA_FP4_IN_F16 or MLA_FP4_IN_F32");
+  const int64_t esz = in_dtype == MLA_FP4_IN_F32 ? 4 : 2;
+  if (latent_stride < mla::kLatent || rope_stride < mla::kRope) return fail(MLA_FP4_ERR_BAD_ARG, "row strides smaller than the rows");
+  if (reinterpret_cast<uintptr_t>(latent) % 16 || (latent_stride * esz) % 16)
+    return fail(MLA_FP4_ERR_BAD_ARG, "latent rows must be 16-byte aligned");
+  if (reinterpret_cast<uintptr_t>(rope) % (2 * esz) || rope_stride % 2) return fail(MLA_FP4_ERR_BAD_ARG, "rope rows must be aligned to two elements");
+  if (reinterpret_cast<uintptr_t>(kv_cache) % 32) return fail(MLA_FP4_ERR_BAD_ARG, "kv_cache must be 32-byte aligned");
+  cudaError_t e = mla::launch_cache_write(latent, latent_stride, rope, rope_stride, in_dtype, token_scale, slot_mapping, num_tokens,
+                                          kv_cache, kv_cache_sf, num_slots, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("cache write launch: ") + cudaGetErrorString(e));
+  return MLA_FP4_OK;
+}
+
 int mla_fp4_dequant_e2m1_to_e4m3(const void* packed, void* out, int64_t n_bytes, void* stream) {
   if (n_bytes < 0 || (n_bytes % 4)) return fail(MLA_FP4_ERR_BAD_ARG, "n_bytes must be a non-negative multiple of 4");
   if (n_bytes == 0) return MLA_FP4_OK;

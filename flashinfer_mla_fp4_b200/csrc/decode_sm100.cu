@@ -1016,7 +1016,7 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
       const int d0 = 2 * u0, pairs = u1 - u0;
       const int items = pairs * 8;
       int SL = 1, lg = 0;
-      while (SL < 32 && 4 * SL < ns) { SL *= 2; ++lg; }
+      while (SL < 32 && 4 * SL < ns && items * SL * 2 <= kThreads) { SL *= 2; ++lg; }  // one round of threads if possible
       const int units = items << lg;
 #pragma unroll 1
       for (int base = (tid & ~31); base < units; base += kThreads) {

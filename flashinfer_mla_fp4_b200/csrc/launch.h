@@ -37,6 +37,9 @@ cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);
 cudaError_t launch_merge_partials(const float* po, const float* pl, int parts, int64_t rows, int64_t stride_o,
                                   int64_t stride_l, void* out, int out_dtype, float* lse, cudaStream_t stream);
 cudaError_t launch_fp32_check(const DecodeParams& p, int num_ctas, cudaStream_t stream);
+cudaError_t launch_cache_write(const void* latent, int64_t latent_stride, const void* rope, int64_t rope_stride, int in_dtype,
+                               const float* scale_in, const int64_t* slot_mapping, int64_t num_tokens, void* cache,
+                               float* cache_sf, int64_t num_slots, cudaStream_t stream);
 cudaError_t launch_dequant(const void* in, void* out, int64_t n_bytes, cudaStream_t stream);
 // tcgen05 decode kernel (decode_sm100.cu). Returns cudaErrorNotSupported-like codes through `err`.
 cudaError_t launch_decode_sm100(const DecodeParams& p, int num_ctas, cudaStream_t stream, const char** err);

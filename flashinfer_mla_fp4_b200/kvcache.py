@@ -48,3 +48,112 @@ def quantize_tokens(
     packed = code[..., 0::2] | (code[..., 1::2] << 4)
     rope_u8 = rope.to(torch.float8_e4m3fn).view(torch.uint8)
     return torch.cat((packed, rope_u8), dim=-1).contiguous(), token_scale.contiguous()
+
+
+@torch.no_grad()
+def write_tokens(
+    latent: torch.Tensor,
+    rope: torch.Tensor,
+    slot_mapping: Optional[torch.Tensor],
+    kv_cache: torch.Tensor,
+    kv_cache_sf: torch.Tensor,
+    token_scale: Optional[torch.Tensor] = None,
+) -> None:
+    """Quantise tokens and scatter them into the paged cache with the CUDA writer kernel.
+
+    latent [T, 512] and rope [T, 64] (bf16, f16 or f32, CUDA, unit inner stride) are written to
+    slot ``slot_mapping[t] = page * page_size + offset`` of ``kv_cache`` ([pages, page_size, 320]
+    uint8, contiguous) and ``kv_cache_sf`` ([pages, page_size, 1] f32, contiguous); a negative slot
+    skips the token, ``slot_mapping=None`` writes token t to slot t.  ``token_scale`` ([T] f32)
+    replaces the default amax/6.  Produces the bytes ``quantize_tokens`` produces (the reference's
+    fixture builder, tests/test_cute_dsl_mla_fp4.py:56-93; cache writes are the caller's job there,
+    README.md:81-83).  Asynchronous on the current stream; there is no CPU path.
+    """
+    from . import _cabi
+
+    if not (latent.is_cuda and rope.is_cuda and kv_cache.is_cuda and kv_cache_sf.is_cuda):
+        raise ValueError("write_tokens needs CUDA tensors (use quantize_tokens to build a cache on the host)")
+    if latent.ndim != 2 or latent.shape[1] != LATENT_DIM or rope.ndim != 2 or rope.shape[1] != ROPE_DIM or rope.shape[0] != latent.shape[0]:
+        raise ValueError("latent must be [T, 512] and rope [T, 64]")
+    if latent.dtype != rope.dtype or latent.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+        raise ValueError("latent and rope must share a dtype among bfloat16, float16, float32")
+    if latent.stride(1) != 1 or rope.stride(1) != 1:
+        raise ValueError("latent and rope must have unit inner stride")
+    if kv_cache.dtype != torch.uint8 or kv_cache.shape[-1] != ROW_BYTES or not kv_cache.is_contiguous():
+        raise ValueError("kv_cache must be a contiguous uint8 tensor [..., 320]")
+    if kv_cache_sf.dtype != torch.float32 or not kv_cache_sf.is_contiguous():
+        raise ValueError("kv_cache_sf must be a contiguous float32 tensor")
+    num_slots = kv_cache.numel() // ROW_BYTES
+    if kv_cache_sf.numel() != num_slots:
+        raise ValueError("kv_cache_sf must hold one scale per cache row")
+    tokens = latent.shape[0]
+    if slot_mapping is not None:
+        if slot_mapping.dtype != torch.int64 or slot_mapping.numel() != tokens or not slot_mapping.is_contiguous():
+            raise ValueError("slot_mapping must be a contiguous int64 tensor [T]")
+    if token_scale is not None:
+        token_scale = token_scale.reshape(-1)
+        if token_scale.dtype != torch.float32 or token_scale.numel() != tokens or not token_scale.is_contiguous():
+            raise ValueError("token_scale must be a contiguous float32 tensor [T]")
+    dt = {torch.bfloat16: _cabi.IN_BF16, torch.float16: _cabi.IN_F16, torch.float32: _cabi.IN_F32}[latent.dtype]
+    with torch.cuda.device(latent.device):
+        _cabi.check(_cabi.lib.mla_fp4_cache_write(
+            latent.data_ptr(), latent.stride(0), rope.data_ptr(), rope.stride(0), dt,
+            token_scale.data_ptr() if token_scale is not None else None,
+            slot_mapping.data_ptr() if slot_mapping is not None else None,
+            tokens, kv_cache.data_ptr(), kv_cache_sf.data_ptr(), num_slots,
+            torch.cuda.current_stream(latent.device).cuda_stream))
+
+
+def _bench_writer(tokens: int, reps: int, profile_only: bool) -> None:
+    """Time write_tokens on `tokens` bf16 tokens (inputs and cache larger than L2) and print one JSON line."""
+    import json
+    import statistics
+    from pathlib import Path
+
+    dev = torch.device("cuda:0")
+    page_size = 64
+    pages = (tokens + page_size - 1) // page_size
+    g = torch.Generator(device=dev).manual_seed(1234)
+    latent = torch.randn(tokens, LATENT_DIM, generator=g, device=dev, dtype=torch.float32).bfloat16()
+    rope = torch.randn(tokens, ROPE_DIM, generator=g, device=dev, dtype=torch.float32).bfloat16()
+    slots = torch.randperm(pages * page_size, generator=g, device=dev)[:tokens].contiguous()
+    cache = torch.empty(pages, page_size, ROW_BYTES, dtype=torch.uint8, device=dev)
+    sf = torch.empty(pages, page_size, 1, dtype=torch.float32, device=dev)
+    for _ in range(3):
+        write_tokens(latent, rope, slots, cache, sf)
+    torch.cuda.synchronize()
+    if profile_only:
+        print(json.dumps({"profile": "cache_write", "tokens": tokens}))
+        return
+    times = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        write_tokens(latent, rope, slots, cache, sf)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e-3)
+    t = statistics.median(times)
+    bytes_per_token = HEAD_DIM_QK * 2 + BYTES_PER_TOKEN + 8  # bf16 inputs, cache row + scale, slot id
+    peak = 6650.0
+    kind = "fallback"
+    peaks_file = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
+    if peaks_file.exists():
+        peak, kind = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured"
+    achieved = tokens * bytes_per_token / t / 1e9
+    print(json.dumps({"metric": "fp4_cache_write_tokens_per_s", "value": tokens / t, "unit": "tokens/s", "tokens": tokens,
+                      "us": t * 1e6, "dtype": "bf16->e2m1/e4m3",
+                      "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                                   "peak_kind": kind, "algorithmic_bytes_per_token": bytes_per_token},
+                      "l2": f"cold by size: {tokens * bytes_per_token / 2**20:.0f} MiB touched per call"}))
+
+
+if __name__ == "__main__":
+    import argparse
+
+    ap = argparse.ArgumentParser(description="time the CUDA cache writer (one JSON line)")
+    ap.add_argument("--tokens", type=int, default=1 << 20)
+    ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--profile-only", action="store_true", help="three warm-up calls and exit (the command line for ncu)")
+    a = ap.parse_args()
+    _bench_writer(a.tokens, a.reps, a.profile_only)

@@ -50,6 +50,11 @@ extern "C" {
    zero; the split-KV partial slots follow. */
 #define MLA_FP4_WORKSPACE_HEADER_BYTES 2048
 
+/* input element types of mla_fp4_cache_write */
+#define MLA_FP4_IN_BF16 0
+#define MLA_FP4_IN_F16 1
+#define MLA_FP4_IN_F32 2
+
 /* output element types (reference: out dtype bf16 default, wrappers/batch_mla_fp4.py:228) */
 #define MLA_FP4_OUT_BF16 0
 #define MLA_FP4_OUT_F32 1
@@ -147,6 +152,23 @@ int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, i
    (out holds 2*n_bytes E4M3 bytes, low nibble first), using the same device routine as the
    decode kernel.  Pins the table of tests/test_cute_dsl_mla_fp4.py:80-84. */
 int mla_fp4_dequant_e2m1_to_e4m3(const void* packed, void* out, int64_t n_bytes, void* stream);
+
+/* Write `num_tokens` tokens into the paged cache (the producer of the format mla_fp4_decode reads):
+   per token amax -> scale = amax / 6 (1 for an all-zero token), x / scale rounded to the nearest E2M1
+   magnitude with a tie going to the smaller one, packed low nibble = even element with the sign in
+   bit 3, the 64 RoPE values cast to E4M3 (round to nearest even; |x| > 464 becomes NaN, as a torch
+   cast does), row and FP32 scale
+   stored at slot_mapping[t] = page * page_size + offset of kv_cache [num_slots, 320] / kv_cache_sf
+   [num_slots].  latent [num_tokens, 512] and rope [num_tokens, 64] have element type in_dtype
+   (MLA_FP4_IN_*), unit inner stride, row strides in elements (latent rows 16-byte aligned).
+   token_scale (f32 [num_tokens]) replaces the amax scale when not NULL; slot_mapping NULL means
+   slot t; a slot that is negative or >= num_slots is skipped (padding tokens).  Byte-identical to the
+   reference's fixture builder (tests/test_cute_dsl_mla_fp4.py:56-93); the reference itself leaves
+   cache writes to the caller (README.md:81-83). */
+int mla_fp4_cache_write(const void* latent, int64_t latent_stride, const void* rope, int64_t rope_stride,
+                        int32_t in_dtype, const float* token_scale, const int64_t* slot_mapping,
+                        int64_t num_tokens, void* kv_cache, float* kv_cache_sf, int64_t num_slots,
+                        void* stream);
 
 /* Largest decode grid the allocation-free variant below accepts, and the bytes of device memory
    its built-in scratch occupies on every GPU that loads the library (until the process exits). */

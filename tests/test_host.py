@@ -34,6 +34,8 @@ def test_abi_rejects_bad_arguments_without_a_gpu():
     assert _cabi.lib.mla_fp4_workspace_bytes(8, 1, 64, 148, ctypes.byref(n)) == 0
     assert n.value == 2048 + 2 * 148 * (512 * 64 * 2 + 64 * 4 + 16)  # counter header + two slots per CTA
     assert _cabi.lib.mla_fp4_workspace_init(None, 4096, None) == _cabi.ERR_BAD_ARG
+    assert _cabi.lib.mla_fp4_cache_write(None, 512, None, 64, 0, None, None, 4, None, None, 16, None) == _cabi.ERR_BAD_ARG
+    assert _cabi.lib.mla_fp4_cache_write(None, 512, None, 64, 0, None, None, 0, None, None, 16, None) == 0  # nothing to write
     assert _cabi.lib.mla_fp4_workspace_bytes(8, 0, 64, 148, ctypes.byref(n)) == _cabi.ERR_BAD_ARG
     with pytest.raises(ValueError):
         _cabi.check(_cabi.ERR_WORKSPACE_TOO_SMALL)
