@@ -29,13 +29,19 @@ template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; 
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-// 16 consecutive elements of a row -> f32 (rows are 16-byte aligned: checked by the launcher)
-template <typename T> __device__ __forceinline__ void load16(const T* p, float (&v)[16]) {
-  constexpr int kPer = 16 / sizeof(T);  // elements per 16-byte load
+// 16 consecutive elements of a row (rows are 16-byte aligned: checked by the launcher): the raw
+// 16-byte loads of the next token are issued before the current one is converted.
+template <typename T> struct Raw16 {
+  static constexpr int kPer = 16 / sizeof(T);  // elements per 16-byte load
+  uint4 r[16 / kPer];
+  T rope0, rope1;
+  int64_t slot;
+};
+template <typename T> __device__ __forceinline__ void convert16(const Raw16<T>& raw, float (&v)[16]) {
+  constexpr int kPer = Raw16<T>::kPer;
 #pragma unroll
   for (int q = 0; q < 16 / kPer; ++q) {
-    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p) + q);
-    const T* e = reinterpret_cast<const T*>(&raw);
+    const T* e = reinterpret_cast<const T*>(&raw.r[q]);
 #pragma unroll
     for (int i = 0; i < kPer; ++i) v[q * kPer + i] = to_f32<T>(e[i]);
   }
@@ -43,7 +49,7 @@ template <typename T> __device__ __forceinline__ void load16(const T* p, float (
 
 // E2M1 code of x / scale: magnitude = number of thresholds strictly below |n| (a tie stays on the
 // smaller magnitude), bit 3 = n < 0.
-__device__ __forceinline__ uint32_t e2m1_code(float x, float scale) {
+__device__ __noinline__ uint32_t e2m1_code(float x, float scale) {
   const float n = __fdiv_rn(x, scale);
   const float a = fabsf(n);
   uint32_t m = 0;
@@ -64,6 +70,32 @@ __device__ __forceinline__ uint32_t rope_e4m3(float x) {
   return __nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
 }
 
+// The same codes without the division, for all but a few values in a million.  q = x * (1/scale)
+// is within 3 units in the last place of the correctly rounded quotient n, and every rounding
+// threshold is a float whose low 21 mantissa bits are zero.  So unless bits(q) lies within 8 of a
+// multiple of 2^21, q and n fall between the same two thresholds and are not on one: round-to-
+// nearest-even and "a tie goes to the smaller magnitude" agree there, and the hardware conversion
+// cvt.rn.satfinite.e2m1x2.f32 of q gives the code (it saturates at 6 and keeps the sign of values
+// that round to magnitude zero, as the rule above does).  The fused add of +0 turns a product of
+// -0.0 into +0.0: a zero carries no sign bit.  The other values (including q = 0 from an underflow,
+// and infinity) are redone with the exact division afterwards.
+__device__ __forceinline__ bool needs_exact(float q, float x) {
+  return (((__float_as_uint(q) + 8u) & 0x1ffff0u) == 0u) && (__float_as_uint(x) << 1) != 0u;
+}
+// eight values -> eight packed codes (value 0 in the low nibble)
+__device__ __forceinline__ uint32_t e2m1x8(const float (&q)[8]) {
+  uint32_t out;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+      : "=r"(out)
+      : "f"(q[0]), "f"(q[1]), "f"(q[2]), "f"(q[3]), "f"(q[4]), "f"(q[5]), "f"(q[6]), "f"(q[7]));
+  return out;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kWriterWarps * 32)
 cache_write_kernel(const T* __restrict__ latent, int64_t latent_stride, const T* __restrict__ rope, int64_t rope_stride,
@@ -71,11 +103,27 @@ cache_write_kernel(const T* __restrict__ latent, int64_t latent_stride, const T*
                    uint8_t* __restrict__ cache, float* __restrict__ cache_sf, int64_t num_slots) {
   const int lane = threadIdx.x & 31;
   const int64_t warps = int64_t(gridDim.x) * kWriterWarps;
-  for (int64_t t = int64_t(blockIdx.x) * kWriterWarps + (threadIdx.x >> 5); t < num_tokens; t += warps) {
-    const int64_t slot = slot_mapping ? slot_mapping[t] : t;
+  auto fetch = [&](int64_t t, Raw16<T>& raw) {
+    raw.slot = slot_mapping ? __ldg(slot_mapping + t) : t;
+    const uint4* p = reinterpret_cast<const uint4*>(latent + t * latent_stride + 16 * lane);
+#pragma unroll
+    for (int q = 0; q < 16 / Raw16<T>::kPer; ++q) raw.r[q] = __ldg(p + q);
+    const T* rp = rope + t * rope_stride + 2 * lane;
+    raw.rope0 = rp[0];
+    raw.rope1 = rp[1];
+  };
+  int64_t t = int64_t(blockIdx.x) * kWriterWarps + (threadIdx.x >> 5);
+  Raw16<T> cur;
+  if (t < num_tokens) fetch(t, cur);
+  for (; t < num_tokens; t += warps) {
+    Raw16<T> nxt;
+    if (t + warps < num_tokens) fetch(t + warps, nxt);  // in flight while this token is quantised
+    const Raw16<T> raw = cur;
+    cur = nxt;
+    const int64_t slot = raw.slot;
     if (slot < 0 || slot >= num_slots) continue;  // padding token (negative) or out of the pool: nothing is written
     float v[16];
-    load16<T>(latent + t * latent_stride + 16 * lane, v);
+    convert16<T>(raw, v);
     float scale;
     if (scale_in) {
       scale = scale_in[t];
@@ -88,14 +136,31 @@ cache_write_kernel(const T* __restrict__ latent, int64_t latent_stride, const T*
       scale = __fdiv_rn(amax, 6.0f);
       if (!(scale > 0.f)) scale = 1.0f;
     }
-    uint32_t w[2] = {0u, 0u};
+    const float inv_scale = __frcp_rn(scale);
+    uint32_t w[2];
+    uint32_t redo = 0u;  // positions whose code must come from the exact division (a few per million)
 #pragma unroll
-    for (int i = 0; i < 16; ++i) w[i >> 3] |= e2m1_code(v[i], scale) << (4 * (i & 7));
+    for (int h = 0; h < 2; ++h) {
+      float q[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        q[i] = fmaf(v[8 * h + i], inv_scale, 0.0f);
+        redo |= needs_exact(q[i], v[8 * h + i]) ? (1u << (8 * h + i)) : 0u;
+      }
+      w[h] = e2m1x8(q);
+    }
+    while (redo) {
+      const int i = __ffs(redo) - 1;
+      redo &= redo - 1u;
+      const uint32_t code = e2m1_code(to_f32<T>(latent[t * latent_stride + 16 * lane + i]), scale);
+      const uint32_t sh = 4u * (uint32_t(i) & 7u);
+      uint32_t& word = (i >> 3) ? w[1] : w[0];
+      word = (word & ~(0xfu << sh)) | (code << sh);
+    }
     uint8_t* row = cache + slot * kRowBytes;
     *reinterpret_cast<uint2*>(row + 8 * lane) = make_uint2(w[0], w[1]);
     // RoPE: two values per lane
-    const T* rp = rope + t * rope_stride + 2 * lane;
-    const uint32_t r0 = rope_e4m3(to_f32<T>(rp[0])), r1 = rope_e4m3(to_f32<T>(rp[1]));
+    const uint32_t r0 = rope_e4m3(to_f32<T>(raw.rope0)), r1 = rope_e4m3(to_f32<T>(raw.rope1));
     *reinterpret_cast<uint16_t*>(row + kLatent / 2 + 2 * lane) = uint16_t(r0 | (r1 << 8));
     if (lane == 0) cache_sf[slot] = scale;
   }
