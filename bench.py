@@ -74,6 +74,16 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def wait_first_sample(self, timeout_s: float = 10.0) -> None:
+        """Block until nvidia-smi has printed its first line, so that later samples fall inside the timed region."""
+        if self.proc is None or self.proc.stdout is None:
+            return
+        import select
+
+        ready, _, _ = select.select([self.proc.stdout], [], [], timeout_s)
+        if ready:
+            self.first = self.proc.stdout.readline()
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -261,9 +271,10 @@ def main() -> None:
                     step(i)
     sampler = ClockSampler(local_rank)
     times = []
-    barrier()
     sampler.start()
-    for _ in range(max(1, args.repeats)):
+    sampler.wait_first_sample()
+
+    def timed_replay():
         barrier()
         with torch.cuda.stream(stream):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -276,6 +287,17 @@ def main() -> None:
             e1.record(stream)
         barrier()
         times.append(e0.elapsed_time(e1) * 1e3 / K)  # us per step
+
+    for _ in range(max(1, args.repeats)):
+        timed_replay()
+    # The K steps of one replay last a millisecond or two; nvidia-smi samples every 100 ms.  Keep taking timed
+    # replays (all of them count toward the median) until the device has been under load for about 0.7 s, the
+    # same number on every rank.
+    extra = torch.tensor([min(3000, int(0.7e6 / max(K * statistics.median(times), 1.0)))], dtype=torch.int64, device=device)
+    if world > 1:
+        dist.all_reduce(extra, op=dist.ReduceOp.MAX)
+    for _ in range(int(extra.item())):
+        timed_replay()
     clocks = sampler.stop()
     us_local = statistics.median(times)
 
@@ -359,7 +381,7 @@ def main() -> None:
             "config": {"workload": case.name, "batch_per_gpu": B, "heads": H, "q_len": ql, "kv_len_max": case.max_seq_len,
                        "kv_tokens_per_gpu": case.kv_tokens, "page_size": case.page_size, "parallelism": f"{args.mode}{world}",
                        "l2": f"cold: {copies} cache copies rotated ({copies * case.kv_bytes() / 2**20:.0f} MiB > L2)",
-                       "timing": f"CUDA graph of {K} steps, events on the launching stream, median of {len(times)} replays, max over ranks"
+                       "timing": f"CUDA graph of {K} steps, events on the launching stream, median of {len(times)} timed replays, max over ranks"
                                  if use_graph else f"{K} eager steps between events, max over ranks",
                        "published_baseline": "reference README, one B300 (not a B200)"},
             "tb_per_s": kv_bytes_all / (us * 1e-6) / 1e12,
