@@ -11,7 +11,7 @@ from pathlib import Path
 
 # MLA_FP4_B200_LIB overrides the library location (for instance a debug build)
 LIB_PATH = Path(os.environ.get("MLA_FP4_B200_LIB") or (Path(__file__).resolve().parent / "libmla_fp4_b200.so"))
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 OK = 0
 ERR_BAD_ARG = 1
@@ -28,6 +28,7 @@ WORKSPACE_HEADER_BYTES = 2048
 IN_BF16, IN_F16, IN_F32 = 0, 1, 2
 OUT_BF16 = 0
 OUT_F32 = 1
+OUT_E4M3 = 2
 
 TILE_TOKENS = 128
 GROUP_HEADS = 64

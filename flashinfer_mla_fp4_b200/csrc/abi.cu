@@ -109,8 +109,8 @@ int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
   if (!page_size_ok(a->page_size))
     return fail(MLA_FP4_ERR_UNSUPPORTED, "page_size must be one of 8, 16, 32, 64, 128");
   if (a->num_heads > 128) return fail(MLA_FP4_ERR_UNSUPPORTED, "num_heads must be <= 128");
-  if (a->out_dtype != MLA_FP4_OUT_BF16 && a->out_dtype != MLA_FP4_OUT_F32)
-    return fail(MLA_FP4_ERR_UNSUPPORTED, "out_dtype must be MLA_FP4_OUT_BF16 or MLA_FP4_OUT_F32");
+  if (a->out_dtype != MLA_FP4_OUT_BF16 && a->out_dtype != MLA_FP4_OUT_F32 && a->out_dtype != MLA_FP4_OUT_E4M3)
+    return fail(MLA_FP4_ERR_UNSUPPORTED, "out_dtype must be MLA_FP4_OUT_BF16, MLA_FP4_OUT_F32 or MLA_FP4_OUT_E4M3");
   if (reinterpret_cast<uintptr_t>(a->kv_cache) % 32) return fail(MLA_FP4_ERR_BAD_ARG, "kv_cache must be 32-byte aligned");
   if (reinterpret_cast<uintptr_t>(a->kv_cache_sf) % 16) return fail(MLA_FP4_ERR_BAD_ARG, "kv_cache_sf must be 16-byte aligned");
   if (reinterpret_cast<uintptr_t>(a->q) % 16 || a->q_stride_head % 16 || a->q_stride_qpos % 16 || a->q_stride_batch % 16)
@@ -220,7 +220,8 @@ int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, i
   if (parts <= 0 || rows < 0) return fail(MLA_FP4_ERR_BAD_ARG, "parts/rows out of range");
   if (rows == 0) return MLA_FP4_OK;
   if (!partial_out || !partial_lse || !out) return fail(MLA_FP4_ERR_BAD_ARG, "null pointer");
-  if (out_dtype != MLA_FP4_OUT_BF16 && out_dtype != MLA_FP4_OUT_F32) return fail(MLA_FP4_ERR_UNSUPPORTED, "bad out_dtype");
+  if (out_dtype != MLA_FP4_OUT_BF16 && out_dtype != MLA_FP4_OUT_F32 && out_dtype != MLA_FP4_OUT_E4M3)
+    return fail(MLA_FP4_ERR_UNSUPPORTED, "bad out_dtype");
   if (reinterpret_cast<uintptr_t>(partial_out) % 16) return fail(MLA_FP4_ERR_BAD_ARG, "partial_out must be 16-byte aligned");
   if (part_stride_out == 0) part_stride_out = rows * mla::kLatent;
   if (part_stride_lse == 0) part_stride_lse = rows;

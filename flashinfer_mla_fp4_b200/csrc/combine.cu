@@ -10,6 +10,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 namespace mla {
 
@@ -53,8 +54,10 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
     if (h_out < heads_here) {
       if (p.out_dtype == MLA_FP4_OUT_BF16) {
         *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + out_idx) = make_uint2(0u, 0u);
-      } else {
+      } else if (p.out_dtype == MLA_FP4_OUT_F32) {
         *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + out_idx) = make_float4(0.f, 0.f, 0.f, 0.f);
+      } else {
+        *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(p.out) + out_idx) = 0u;
       }
     }
     if (dchunk == 0 && p.lse && tid < heads_here) p.lse[row0 + tid] = -INFINITY;
@@ -154,8 +157,12 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
       uint2 pk;
       pk.x = *reinterpret_cast<uint32_t*>(&v0); pk.y = *reinterpret_cast<uint32_t*>(&v1);
       *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + out_idx) = pk;
-    } else {
+    } else if (p.out_dtype == MLA_FP4_OUT_F32) {
       *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + out_idx) = make_float4(t[0], t[1], t[2], t[3]);
+    } else {
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(t[0], t[1]), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(t[2], t[3]), __NV_SATFINITE, __NV_E4M3);
+      *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(p.out) + out_idx) = lo | (hi << 16);
     }
   }
 }

@@ -48,6 +48,8 @@ MLA_HD float slot_scale_for(float bound) { return exp2f(ceilf(log2f(fmaxf(bound,
 // A request can be split over at most this many CTAs (= the largest decode grid accepted).
 constexpr int kMaxCombineSlots = 148;
 
+MLA_HD int out_elem_bytes(int out_dtype) { return out_dtype == MLA_FP4_OUT_F32 ? 4 : (out_dtype == MLA_FP4_OUT_BF16 ? 2 : 1); }
+
 // ----------------------------------------------------------------------------------------------
 // Work partition.
 //

@@ -15,9 +15,9 @@
 // into 128-byte-swizzled shared memory, where the very same bytes serve as the K-major A operand
 // of QK^T and as the MN-major A operand of PV.  RoPE bytes, per-token scales and Q arrive by TMA.
 //
-// Warp roles (608 threads): 0-7 softmax / O rescale / epilogue (TMEM lane = token or dim; two warps
-// share a lane quarter and split the 64 heads), 8-15 latent load + dequant, 16 QK^T issue, 17 TMA issue,
-// 18 PV issue (issue warps run warp-uniform code, one elected lane per instruction).
+// Warp roles (640 threads): 0 QK^T issue, 1 TMA issue, 2 PV issue (issue warps run warp-uniform code, one
+// elected lane per instruction, and have the lowest warp ids), 3 spare, 4-11 softmax / O rescale / epilogue
+// (TMEM lane = token or dim; two warps share a lane quarter and split the 64 heads), 12-19 latent load + dequant.
 //
 // Requests that are split across CTAs are merged at the end of the same kernel (tail_merge): the
 // CTAs publish their partials through counters in the workspace header and each takes a share of
@@ -42,11 +42,13 @@ namespace mla {
 
 namespace {
 
-#ifdef MLA_FP4_TRACE
-constexpr int kThreads = 640;           // trace builds add an observer warp
-#else
-constexpr int kThreads = 608;           // 19 warps; at most five per scheduler, hence at most 96 registers per thread
-#endif
+// Warp roles.  The three issue warps have the lowest warp ids: the warp scheduler prefers older
+// warps, and an issue warp that has to queue behind four busy compute warps on its scheduler
+// delays the tensor pipe (measured with the issue warps last: PV issue 1.7 k clk alone, 4.5 k clk next to busy warps).
+constexpr int kWarpQK = 0, kWarpTMA = 1, kWarpPV = 2, kWarpSpare = 3;  // the spare warp only joins the CTA barriers
+constexpr int kWarpSoftmax0 = 4;       // 8 warps; warp & 3 is the TMEM lane quarter the warp may access
+constexpr int kWarpDequant0 = 12;      // 8 warps
+constexpr int kThreads = 640;          // 20 warps, five per scheduler, hence at most 96 registers per thread
 constexpr int kSoftmaxThreads = 256;   // 8 warps: warp w works on TMEM lanes 32*(w%4).. and heads 32*(w/4)..
 constexpr int kDequantThreads = 256;
 constexpr int kDequantWarps = kDequantThreads / 32;
@@ -193,7 +195,7 @@ __device__ __noinline__ void drain_wait(const Ctx& c, int idx, uint32_t parity) 
 #endif
 
 // ------------------------------------------------------------------------------------------
-// role: latent load + dequant (warps 4..11)
+// role: latent load + dequant (warps 12..19)
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint4 ldg_nc(const uint8_t* p) {
   uint4 v;
@@ -303,7 +305,7 @@ __device__ __forceinline__ void dequant_role(const DecodeParams& p, const Ctx& c
 }
 
 // ------------------------------------------------------------------------------------------
-// role: TMA issue (warp 17, one lane): Q per segment; RoPE bytes + scales per tile
+// role: TMA issue (warp 1, one lane): Q per segment; RoPE bytes + scales per tile
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_role(const DecodeParams& p, const Ctx& c, const CUtensorMap* map_q_lat,
                                          const CUtensorMap* map_q_rope, const CUtensorMap* map_rope, RoleState& st) {
@@ -359,7 +361,7 @@ __device__ __forceinline__ void tma_role(const DecodeParams& p, const Ctx& c, co
 }
 
 // ------------------------------------------------------------------------------------------
-// role: MMA issue (warps 16 and 18).  The whole warp runs this code with uniform control flow; only the
+// role: MMA issue (warps 0 and 2).  The whole warp runs this code with uniform control flow; only the
 // tcgen05 instructions sit under elect_one(), so their operands stay in uniform registers.
 // ------------------------------------------------------------------------------------------
 // Descriptors of every operand, built once: the per-instruction work is one 32-bit add.
@@ -435,7 +437,7 @@ __device__ __forceinline__ MmaDescs make_descs(const Ctx& c) {
   return d;
 }
 
-// role: QK^T issue (warp 16)
+// role: QK^T issue (warp 0)
 __device__ __forceinline__ void qk_role(const Ctx& c, uint32_t tmem, RoleState& st) {
   const MmaDescs d = make_descs(c);
   const int nseg = c.misc->nseg;
@@ -465,7 +467,7 @@ __device__ __forceinline__ void qk_role(const Ctx& c, uint32_t tmem, RoleState& 
   }
 }
 
-// role: PV issue (warp 18)
+// role: PV issue (warp 2)
 __device__ __forceinline__ void pv_role(const Ctx& c, uint32_t tmem, RoleState& st) {
   const MmaDescs d = make_descs(c);
   const int nseg = c.misc->nseg;
@@ -489,7 +491,7 @@ __device__ __forceinline__ void pv_role(const Ctx& c, uint32_t tmem, RoleState& 
 }
 
 // ------------------------------------------------------------------------------------------
-// role: softmax / rescale / epilogue (warps 0..3, thread = TMEM lane)
+// role: softmax / rescale / epilogue (warps 4..11, thread = TMEM lane)
 // ------------------------------------------------------------------------------------------
 // ---- packed FP32 pairs (sm_100 f32x2 arithmetic)
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
@@ -698,11 +700,16 @@ __device__ __noinline__ void write_output(const DecodeParams& p, const Ctx& c, u
 #pragma unroll
       for (int i = 0; i < 16; ++i)
         if (h0 + i < heads_here) dst[size_t(i) * kLatent] = __float2bfloat16_rn(v[i]);
-    } else {
+    } else if (p.out_dtype == MLA_FP4_OUT_F32) {
       float* dst = reinterpret_cast<float*>(p.out) + (row0 + h0) * kLatent + dim;
 #pragma unroll
       for (int i = 0; i < 16; ++i)
         if (h0 + i < heads_here) dst[size_t(i) * kLatent] = v[i];
+    } else {
+      uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + (row0 + h0) * kLatent + dim;
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if (h0 + i < heads_here) dst[size_t(i) * kLatent] = __nv_cvt_float_to_fp8(v[i], __NV_SATFINITE, __NV_E4M3);
     }
   }
   const float lse = lds_f32(c.smem + kOffLse + 4 * (tid & 63));
@@ -892,7 +899,7 @@ __device__ __forceinline__ int ld_acquire(const int32_t* p) {
 // instructions (rolled loops, no 64-bit division, approximate exp2/log2), not for peak throughput.
 __device__ __noinline__ void zero_empty_requests(const DecodeParams& p, int tid) {
   const int total = p.groups * p.batch;
-  const uint32_t esz = p.out_dtype == MLA_FP4_OUT_BF16 ? 2u : 4u;
+  const uint32_t esz = uint32_t(out_elem_bytes(p.out_dtype));
 #pragma unroll 1
   for (int v = blockIdx.x; v < total; v += gridDim.x) {
     const int g = v / p.batch, b = v - g * p.batch;
@@ -1074,8 +1081,11 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
               if (p.out_dtype == MLA_FP4_OUT_BF16) {
                 __nv_bfloat162 b2 = __floats2bfloat162_rn(acc[0][e], acc[1][e]);
                 *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(p.out) + idx) = *reinterpret_cast<uint32_t*>(&b2);
-              } else {
+              } else if (p.out_dtype == MLA_FP4_OUT_F32) {
                 *reinterpret_cast<float2*>(reinterpret_cast<float*>(p.out) + idx) = make_float2(acc[0][e], acc[1][e]);
+              } else {
+                *reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(p.out) + idx) =
+                    __nv_cvt_float2_to_fp8x2(make_float2(acc[0][e], acc[1][e]), __NV_SATFINITE, __NV_E4M3);
               }
             }
           }
@@ -1124,7 +1134,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
     __syncwarp();
     ptx::tmem_alloc(c.smem + kOffMisc + offsetof(Misc, tmem_base), 512);
     ptx::tmem_relinquish();
-  } else if (warp == 1 && (tid & 31) == 0) {
+  } else if (warp == kWarpTMA && (tid & 31) == 0) {
     for (int s = 0; s < kStages; ++s) {
       for (int j = 0; j < kBlocks; ++j) {
         ptx::mbar_init(bar_addr(c, bar_kv_full(s, j)), kDequantWarps);
@@ -1140,7 +1150,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
     ptx::mbar_init(bar_addr(c, kBarOFree), kSoftmaxThreads);
     ptx::mbar_init(bar_addr(c, kBarDrain), 2);
     ptx::fence_barrier_init();
-  } else if (warp == 17 && (tid & 31) == 0) {
+  } else if (warp == kWarpPV && (tid & 31) == 0) {
     ptx::prefetch_tensormap(&map_q_lat);
     ptx::prefetch_tensormap(&map_q_rope);
     ptx::prefetch_tensormap(&map_rope);
@@ -1160,16 +1170,16 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   st.part = 0;
   // Rounds: almost always exactly one; more only when a CTA's range spans more than kMaxSeg requests.
   for (;;) {
-    if (warp < 8) {
-      softmax_role(p, c, tmem, tid, st);
-    } else if (warp < 16) {
-      dequant_role(p, c, tid - kSoftmaxThreads, st);
-    } else if (warp == 16) {
+    if (warp >= kWarpDequant0) {
+      dequant_role(p, c, tid - 32 * kWarpDequant0, st);
+    } else if (warp >= kWarpSoftmax0) {
+      softmax_role(p, c, tmem, tid - 32 * kWarpSoftmax0, st);
+    } else if (warp == kWarpQK) {
       qk_role(c, tmem, st);
-    } else if (warp == 18) {
+    } else if (warp == kWarpPV) {
       pv_role(c, tmem, st);
 #ifdef MLA_FP4_TRACE
-    } else if (warp == 19) {  // observers: lane 0 QK^T completion, lane 1 PV completion (block 0 and whole tile)
+    } else if (warp == kWarpSpare) {  // observers: lane 0 QK^T completion, lane 1 PV completion (block 0 and whole tile)
       if (blockIdx.x == 0 && (tid & 31) < 2) {
         const int nseg = c.misc->nseg;
         uint32_t it = 0;
@@ -1189,7 +1199,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
       }
       __syncwarp();
 #endif
-    } else {
+    } else if (warp == kWarpTMA) {
       if ((tid & 31) == 0) tma_role(p, c, &map_q_lat, &map_q_rope, &map_rope, st);
       __syncwarp();
     }
@@ -1201,7 +1211,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   }
 
   // drain: everything issued has completed before TMEM is released
-  if (warp == 16 || warp == 18) {  // a commit covers the MMAs of the thread that executes it
+  if (warp == kWarpQK || warp == kWarpPV) {  // a commit covers the MMAs of the thread that executes it
     if (ptx::elect_one()) {
       ptx::umma_commit(bar_addr(c, kBarDrain));
       drain_wait(c, kBarDrain, 0);

@@ -21,7 +21,8 @@ __device__ __forceinline__ float e4m3_to_float(uint8_t v) {
 
 __device__ __forceinline__ void store_out(void* out, int out_dtype, size_t idx, float v) {
   if (out_dtype == MLA_FP4_OUT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
-  else reinterpret_cast<float*>(out)[idx] = v;
+  else if (out_dtype == MLA_FP4_OUT_F32) reinterpret_cast<float*>(out)[idx] = v;
+  else reinterpret_cast<uint8_t*>(out)[idx] = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -114,7 +114,7 @@ class ContextParallelDecoder:
         base = self._gathered.data_ptr()
         _cabi.check(_cabi.lib.mla_fp4_merge_partials(
             C.c_void_p(base), C.c_void_p(base + 4 * rows * LATENT_DIM), self._world, rows, stride, stride,
-            C.c_void_p(out.data_ptr()), _cabi.OUT_BF16 if out.dtype == torch.bfloat16 else _cabi.OUT_F32,
+            C.c_void_p(out.data_ptr()), {torch.bfloat16: _cabi.OUT_BF16, torch.float32: _cabi.OUT_F32, torch.float8_e4m3fn: _cabi.OUT_E4M3}[out.dtype],
             C.c_void_p(lse_out.data_ptr()) if lse_out is not None else None,
             C.c_void_p(torch.cuda.current_stream(q.device).cuda_stream)))
         return (out, lse_out) if return_lse else out

@@ -10,7 +10,7 @@ current stream.  There is no CPU or library fallback.
 Additions over the reference (all opt-in, defaults keep the reference behaviour):
 ``run(..., return_lse=True)`` returns the base-2 log-sum-exp the reference computes but drops;
 ``q_len`` > 1 is accepted (every query position attends to all ``seq_len`` tokens);
-``out_dtype=torch.float32`` is accepted.
+``out_dtype`` may be ``torch.bfloat16`` (default), ``torch.float8_e4m3fn`` (both as in the reference) or ``torch.float32``.
 """
 from __future__ import annotations
 
@@ -22,7 +22,7 @@ import torch
 from . import _cabi
 from .kvcache import LATENT_DIM, ROPE_DIM, ROW_BYTES
 
-_OUT_DTYPES = {torch.bfloat16: _cabi.OUT_BF16, torch.float32: _cabi.OUT_F32}
+_OUT_DTYPES = {torch.bfloat16: _cabi.OUT_BF16, torch.float32: _cabi.OUT_F32, torch.float8_e4m3fn: _cabi.OUT_E4M3}
 
 
 def _require_sm100(device: torch.device) -> None:
@@ -87,7 +87,7 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         if not (1 <= num_heads <= 128):
             raise ValueError(f"Unsupported num_heads={num_heads}: must be in [1, 128]")
         if o_dtype not in _OUT_DTYPES:
-            raise ValueError(f"Unsupported out_dtype={o_dtype}: must be torch.bfloat16 or torch.float32")
+            raise ValueError(f"Unsupported out_dtype={o_dtype}: must be torch.bfloat16, torch.float8_e4m3fn or torch.float32")
         _require_sm100(self._device)
 
         self._kv_lora_rank = kv_lora_rank

@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define MLA_FP4_ABI_VERSION 2
+#define MLA_FP4_ABI_VERSION 3
 
 /* status codes */
 #define MLA_FP4_OK 0
@@ -58,6 +58,7 @@ extern "C" {
 /* output element types (reference: out dtype bf16 default, wrappers/batch_mla_fp4.py:228) */
 #define MLA_FP4_OUT_BF16 0
 #define MLA_FP4_OUT_F32 1
+#define MLA_FP4_OUT_E4M3 2           /* round to nearest even, saturating at +-448 (reference: out in {bf16, e4m3}) */
 
 typedef struct MlaFp4DecodeArgs {
   /* query, E4M3 bytes, logical shape [batch, q_len, num_heads, 576], unit last stride;

@@ -198,3 +198,22 @@ def test_merge_partials_matches_oracle():
     live = torch.isfinite(ref_lse)
     torch.testing.assert_close(lse.cpu()[live], ref_lse[live], atol=1e-5, rtol=1e-5)
     assert (lse.cpu()[~live] == float("-inf")).all()
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_2pass", "fp32_check"])
+def test_e4m3_output(kernel):
+    """out_dtype = E4M3 (the reference's second output type): the oracle's FP32 output rounded to E4M3,
+    within the kernel's tolerance plus half an E4M3 step; split requests, direct requests and an empty one."""
+    from flashinfer_mla_fp4_b200 import synth
+
+    case = synth.build_case("e4m3out", [3000, 129, 0, 64, 9000], 64, 64, seed=77, device=_dev())
+    out, lse = run_case(case, kernel, out_dtype=torch.float8_e4m3fn, output_scale=8.0)
+    assert out.dtype == torch.float8_e4m3fn
+    ref, _ = O.mla_decode(case.q.cpu(), case.kv_cache.cpu(), case.kv_cache_sf.cpu(), case.block_tables.cpu(),
+                          case.seq_lens.cpu(), case.softmax_scale, 8.0)
+    got = out.float().cpu()
+    rms = ref.pow(2).mean(dim=-1, keepdim=True).sqrt()
+    tol = ref.abs() * 2.0 ** -4 + 2e-2 * rms + 2.0 ** -10  # half a step of a 3-bit mantissa + the parity bar + half a subnormal step
+    assert torch.isfinite(got).all()
+    assert (got - ref).abs().le(tol).all(), float(((got - ref).abs() - tol).max())
+    assert (got[2] == 0).all()  # the empty request
