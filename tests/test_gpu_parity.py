@@ -217,3 +217,42 @@ def test_e4m3_output(kernel):
     assert torch.isfinite(got).all()
     assert (got - ref).abs().le(tol).all(), float(((got - ref).abs() - tol).max())
     assert (got[2] == 0).all()  # the empty request
+
+
+def test_full_size_properties_north_star():
+    """BASELINE's full size (B=8, H=64, KV=32768; too large for the CPU oracle inside a test): the tensor-core
+    kernel against the exact-FP32 GPU kernel over the same partition (itself pinned to the oracle above), and
+    two properties that hold at any size: the result does not depend on where the pages live in the pool
+    (bit-identical after a physical page permutation) nor, beyond rounding, on how many CTAs share the work."""
+    from flashinfer_mla_fp4_b200 import BatchMLADecodeCuteDSLFP4Wrapper, synth
+
+    dev = _dev()
+    case = synth.config_case("northstar", device=dev)
+    out, lse = run_case(case, "tcgen05")
+    chk, chk_lse = run_case(case, "fp32_check", out_dtype=torch.float32)
+    O.assert_parity(out.float().cpu(), chk.cpu(), "northstar: tcgen05 vs exact FP32 kernel")
+    torch.testing.assert_close(lse, chk_lse, atol=2e-3, rtol=1e-4)
+
+    # physical page permutation: same logical sequence, different pool placement
+    pages = case.kv_cache.shape[0]
+    perm = torch.randperm(pages, generator=torch.Generator().manual_seed(5)).to(dev)
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(pages, device=dev)
+    cache2 = case.kv_cache[perm].contiguous()      # new page j holds old page perm[j]
+    sf2 = case.kv_cache_sf[perm].contiguous()
+    bt2 = inv[case.block_tables.long()].to(torch.int32)
+    ws = torch.empty(64 << 20, dtype=torch.int8, device=dev)
+    w = BatchMLADecodeCuteDSLFP4Wrapper(ws)
+    w.plan(num_heads=case.num_heads, page_size=case.page_size)
+    out2 = w.run(case.q, cache2, bt2, case.seq_lens, case.max_seq_len, case.softmax_scale, kv_cache_sf=sf2)
+    torch.cuda.synchronize()
+    w.check_device_status()
+    assert torch.equal(out2, out)
+
+    # a different grid: other split points, same answer within the parity bar
+    w._num_ctas = 100
+    out3 = w.run(case.q, case.kv_cache, case.block_tables, case.seq_lens, case.max_seq_len, case.softmax_scale,
+                 kv_cache_sf=case.kv_cache_sf)
+    torch.cuda.synchronize()
+    w.check_device_status()
+    O.assert_parity(out3.float().cpu(), chk.cpu(), "northstar on 100 CTAs vs exact FP32 kernel")
