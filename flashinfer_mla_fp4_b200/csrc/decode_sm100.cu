@@ -182,12 +182,12 @@ __device__ __noinline__ void drain_wait(const Ctx& c, int idx, uint32_t parity) 
   }
 }
 
-// Optional timeline trace (debug builds only, -DMLA_FP4_TRACE): clock64 stamps of CTA 0 for the
+// Optional timeline trace (debug builds only, -DMLA_FP4_TRACE): clock64 stamps of the last CTA for the
 // first 16 tiles, written after the 8 status words (the status buffer must then be larger).
 #ifdef MLA_FP4_TRACE
 #define MLA_TRACE(role, tile, ev)                                                                      \
   do {                                                                                                 \
-    if (blockIdx.x == 0 && (tile) < 16u && c.status)                                                   \
+    if (blockIdx.x == gridDim.x - 1 && (tile) < 16u && c.status)                                                   \
       reinterpret_cast<long long*>(c.status + 8)[((role) * 16 + (tile)) * 8 + (ev)] = clock64();       \
   } while (0)
 #else
@@ -1180,7 +1180,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
       pv_role(c, tmem, st);
 #ifdef MLA_FP4_TRACE
     } else if (warp == kWarpSpare) {  // observers: lane 0 QK^T completion, lane 1 PV completion (block 0 and whole tile)
-      if (blockIdx.x == 0 && (tid & 31) < 2) {
+      if (blockIdx.x == gridDim.x - 1 && (tid & 31) < 2) {
         const int nseg = c.misc->nseg;
         uint32_t it = 0;
         for (int si = 0; si < nseg; ++si)
