@@ -15,8 +15,8 @@
 // into 128-byte-swizzled shared memory, where the very same bytes serve as the K-major A operand
 // of QK^T and as the MN-major A operand of PV.  RoPE bytes, per-token scales and Q arrive by TMA.
 //
-// Warp roles (640 threads): 0 QK^T issue, 1 TMA issue, 2 PV issue (issue warps run warp-uniform code, one
-// elected lane per instruction, and have the lowest warp ids), 3 spare, 4-11 softmax / O rescale / epilogue
+// Warp roles (640 threads): 0 QK^T issue, 1 TMA issue, 2 and 3 PV issue, two 128-dim blocks each (issue
+// warps run warp-uniform code, one elected lane per instruction), 4-11 softmax / O rescale / epilogue
 // (TMEM lane = token or dim; two warps share a lane quarter and split the 64 heads), 12-19 latent load + dequant.
 //
 // Requests that are split across CTAs are merged at the end of the same kernel (tail_merge): the
@@ -45,7 +45,7 @@ namespace {
 // Warp roles.  The three issue warps have the lowest warp ids: the warp scheduler prefers older
 // warps, and an issue warp that has to queue behind four busy compute warps on its scheduler
 // delays the tensor pipe (measured with the issue warps last: PV issue 1.7 k clk alone, 4.5 k clk next to busy warps).
-constexpr int kWarpQK = 0, kWarpTMA = 1, kWarpPV = 2, kWarpSpare = 3;  // the spare warp only joins the CTA barriers
+constexpr int kWarpQK = 0, kWarpTMA = 1, kWarpPV = 2, kWarpPV2 = 3;
 constexpr int kWarpSoftmax0 = 4;       // 8 warps; warp & 3 is the TMEM lane quarter the warp may access
 constexpr int kWarpDequant0 = 12;      // 8 warps
 constexpr int kThreads = 640;          // 20 warps, five per scheduler, hence at most 96 registers per thread
@@ -271,30 +271,29 @@ __device__ __forceinline__ void dequant_role(const DecodeParams& p, const Ctx& c
     }
     if (more) row_sources(p, sg[nsi], nt, r0, src);
     if (dtid == 0) MLA_TRACE(1, it, 0);
+    // Software pipeline over the four blocks: the conversion of block j+1 (registers only) is issued
+    // between the stores of block j and the proxy fence that has to wait for them.
+    E4m3x32 e0 = dequant32(regs[0][0]);
+    E4m3x32 e1 = dequant32(regs[0][1]);
 #pragma unroll
     for (int j = 0; j < kBlocks; ++j) {
-      // convert first (registers only), then wait for the block to be free, then store
-      if (dtid == 0 && j == 1) MLA_TRACE(4, it, 4);
-      const E4m3x32 e0 = dequant32(regs[j][0]);
-      const E4m3x32 e1 = dequant32(regs[j][1]);
-#ifdef MLA_FP4_TRACE
-      if (dtid == 0 && j == 1 && (e0.a[0] ^ e1.b[3]) != 0x12345678u) MLA_TRACE(4, it, 5);
-#endif
       if (k >= 1) wait_warp(c, bar_kv_empty(s, j), (k - 1) & 1);
       if (dtid == 0) MLA_TRACE(1, it, 1 + j);
       const uint32_t base = c.smem + kOffKV + (s * kBlocks + j) * kBlockBytes;
       store32(e0, base + off_a, base + off_b);
       store32(e1, base + off_a + 64u * 128u, base + off_b + 64u * 128u);
-      if (dtid == 0 && j == 1) MLA_TRACE(4, it, 6);
-      ptx::fence_proxy_async_smem();
-      __syncwarp();
-      if (dtid == 0 && j == 1) MLA_TRACE(4, it, 7);
-      if (lane == 0) ptx::mbar_arrive(bar_addr(c, bar_kv_full(s, j)));
-      if (lane == 0) MLA_TRACE(4 + (dtid >> 5), it, j);
-      if (more) {
+      if (more) {  // this block's registers are free: fetch the same block of the next tile
 #pragma unroll
         for (int u = 0; u < 2; ++u) regs[j][u] = src[u] ? ldg_nc(src[u] + 64 * j + 16 * ch) : zero;
       }
+      if (j + 1 < kBlocks) {
+        e0 = dequant32(regs[j + 1][0]);
+        e1 = dequant32(regs[j + 1][1]);
+      }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(bar_addr(c, bar_kv_full(s, j)));
+      if (lane == 0) MLA_TRACE(4 + (dtid >> 5), it, j);
     }
     if (dtid == 0) MLA_TRACE(1, it, 5);
     si = nsi;
@@ -364,57 +363,72 @@ __device__ __forceinline__ void tma_role(const DecodeParams& p, const Ctx& c, co
 // role: MMA issue (warps 0 and 2).  The whole warp runs this code with uniform control flow; only the
 // tcgen05 instructions sit under elect_one(), so their operands stay in uniform registers.
 // ------------------------------------------------------------------------------------------
-// Descriptors of every operand, built once: the per-instruction work is one 32-bit add.
+// A shared-memory descriptor as two words.  Only the 14-bit address field (bytes >> 4) in the low word
+// changes from one instruction to the next and it cannot carry out (shared memory is smaller than
+// 2^18 bytes), so stepping a descriptor is ONE 32-bit add; with 64-bit descriptors the compiler has to
+// propagate a carry it cannot rule out.  The issue warps share their schedulers with four busy
+// compute warps each, so every instruction they do not execute shortens the tensor pipe's waits.
+struct Desc {
+  uint32_t lo, hi;
+  __device__ __forceinline__ uint64_t at(uint32_t off16) const { return (uint64_t(hi) << 32) | uint64_t(lo + off16); }
+};
+__device__ __forceinline__ Desc make_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout) {
+  const uint64_t d = ptx::smem_desc(addr, lbo, sbo, layout);
+  return Desc{uint32_t(d), uint32_t(d >> 32)};
+}
+// Descriptors of every operand, built once.
 struct MmaDescs {
-  uint64_t kv_k;    // K tile block, K-major, 128B swizzle          (+ (stage*4+block)*1024 + kstep*2)
-  uint64_t kv_mn;   // same bytes as V^T, MN-major                  (+ (stage*4+block)*1024 + kstep*256)
-  uint64_t q_lat;   // Q latent block, K-major, 128B swizzle        (+ block*512 + kstep*2)
-  uint64_t rope;    // K rope, K-major, 64B swizzle                 (+ stage*512 + kstep*2)
-  uint64_t q_rope;  // Q rope                                       (+ kstep*2)
-  uint64_t p;       // P^T hi, MN-major, 64B swizzle                (+ stage*1024 + lo*512 + kstep*128)
+  Desc kv_k;    // K tile block, K-major, 128B swizzle          (+ (stage*4+block)*1024 + kstep*2)
+  Desc kv_mn;   // same bytes as V^T, MN-major                  (+ (stage*4+block)*1024 + kstep*256)
+  Desc q_lat;   // Q latent block, K-major, 128B swizzle        (+ block*512 + kstep*2)
+  Desc rope;    // K rope, K-major, 64B swizzle                 (+ stage*512 + kstep*2)
+  Desc q_rope;  // Q rope                                       (+ kstep*2)
+  Desc p;       // P^T hi, MN-major, 64B swizzle                (+ stage*1024 + lo*512 + kstep*128)
 };
 
-// QK^T of one 128-dim block of tile `it` (4 MMAs); after the last block also the RoPE part and the
-// commit that hands S to the softmax warps.  The caller has seen the operands' barriers complete.
+// QK^T of one 128-dim block of tile `it` (4 MMAs); with the first block also the RoPE part, after the
+// last block the commit that hands S to the softmax warps.  The caller has seen the operands' barriers complete.
 __device__ __forceinline__ void issue_qk_block(const Ctx& c, const MmaDescs& d, uint32_t it, uint32_t j, uint32_t tmem) {
   const uint32_t s = it & 1;
   const uint32_t d_lat = tmem + kColSLat + 64u * s;
-  const uint64_t ad = d.kv_k + ((s * kBlocks + j) * (kBlockBytes >> 4));
-  const uint64_t bd = d.q_lat + j * ((kGroupHeads * 128) >> 4);
+  const uint32_t a_off = (s * kBlocks + j) * (kBlockBytes >> 4);
+  const uint32_t b_off = j * ((kGroupHeads * 128) >> 4);
   ptx::tc_fence_after();
   if (ptx::elect_one()) {
-#pragma unroll
-    for (uint32_t ks = 0; ks < 4; ++ks) ptx::umma_f8(d_lat, ad + 2 * ks, bd + 2 * ks, kIdescQK, (j | ks) ? 1u : 0u);
-    if (j == kBlocks - 1) {
+    if (j == 0) {  // the RoPE part first: its operands arrive by TMA long before the last latent block
       const uint32_t d_rope = tmem + kColSRope + 64u * s;
-      const uint64_t ar = d.rope + s * ((kTile * 64) >> 4);
+      const uint32_t r_off = s * ((kTile * 64) >> 4);
 #pragma unroll
-      for (uint32_t ks = 0; ks < 2; ++ks) ptx::umma_f8(d_rope, ar + 2 * ks, d.q_rope + 2 * ks, kIdescQK, ks);
-      ptx::umma_commit(bar_addr(c, bar_s_full(s)));
+      for (uint32_t ks = 0; ks < 2; ++ks) ptx::umma_f8(d_rope, d.rope.at(r_off + 2 * ks), d.q_rope.at(2 * ks), kIdescQK, ks);
     }
+#pragma unroll
+    for (uint32_t ks = 0; ks < 4; ++ks)
+      ptx::umma_f8(d_lat, d.kv_k.at(a_off + 2 * ks), d.q_lat.at(b_off + 2 * ks), kIdescQK, (j | ks) ? 1u : 0u);
+    if (j == kBlocks - 1) ptx::umma_commit(bar_addr(c, bar_s_full(s)));
   }
   __syncwarp();
 }
 
-// PV of tile `it`: 4 blocks x 4 token steps x (hi, lo); every block commits the barrier that frees it.
-__device__ __forceinline__ void issue_pv(const Ctx& c, const MmaDescs& d, uint32_t it, uint32_t tmem, bool first_of_segment) {
+// PV of tile `it`, blocks [j_begin, j_end): per block 4 token steps x (hi, lo); every block commits the barrier that frees it.
+__device__ __forceinline__ void issue_pv(const Ctx& c, const MmaDescs& d, uint32_t it, uint32_t tmem, bool first_of_segment,
+                                         uint32_t j_begin, uint32_t j_end) {
   const uint32_t s = it & 1;
   ptx::tc_fence_after();
-  const uint64_t p_hi = d.p + s * ((2 * kTile * 64) >> 4);
-  const uint64_t p_lo = p_hi + ((kTile * 64) >> 4);
+  const uint32_t p_hi = s * ((2 * kTile * 64) >> 4);
+  const uint32_t p_lo = p_hi + ((kTile * 64) >> 4);
   const uint32_t acc0 = first_of_segment ? 0u : 1u;
-#pragma unroll 1
-  for (uint32_t j = 0; j < kBlocks; ++j) {
+#pragma unroll
+  for (uint32_t j = j_begin; j < j_end; ++j) {
     // A = V^T block: MN-major, 128-byte swizzle; 32 tokens per step = 4 groups of 8 rows (4096 B)
-    const uint64_t ad = d.kv_mn + ((s * kBlocks + j) * (kBlockBytes >> 4));
+    const uint32_t a_off = (s * kBlocks + j) * (kBlockBytes >> 4);
     const uint32_t dd = tmem + kColO + 64u * j;
     if (ptx::elect_one()) {
 #pragma unroll
       for (uint32_t ks = 0; ks < 4; ++ks) {
         // B = P^T: MN-major (64 heads contiguous), 64-byte swizzle; 32 tokens per step = 2048 B.
         // The hi and the lo term share A: it is fetched once and kept in the collector for the second.
-        ptx::umma_f8_a_fill(dd, ad + 256 * ks, p_hi + 128 * ks, kIdescPV, ks ? 1u : acc0);
-        ptx::umma_f8_a_lastuse(dd, ad + 256 * ks, p_lo + 128 * ks, kIdescPV, 1u);
+        ptx::umma_f8_a_fill(dd, d.kv_mn.at(a_off + 256 * ks), d.p.at(p_hi + 128 * ks), kIdescPV, ks ? 1u : acc0);
+        ptx::umma_f8_a_lastuse(dd, d.kv_mn.at(a_off + 256 * ks), d.p.at(p_lo + 128 * ks), kIdescPV, 1u);
       }
       ptx::umma_commit(bar_addr(c, bar_kv_empty(s, j)));
     }
@@ -428,12 +442,12 @@ __device__ __forceinline__ void issue_pv(const Ctx& c, const MmaDescs& d, uint32
 // data hazard between them is already covered by a barrier.
 __device__ __forceinline__ MmaDescs make_descs(const Ctx& c) {
   MmaDescs d;
-  d.kv_k = ptx::smem_desc(c.smem + kOffKV, 16, 1024, 2);
-  d.kv_mn = ptx::smem_desc(c.smem + kOffKV, kBlockBytes, 1024, 2);
-  d.q_lat = ptx::smem_desc(c.smem + kOffQLat, 16, 1024, 2);
-  d.rope = ptx::smem_desc(c.smem + kOffRope, 16, 512, 4);
-  d.q_rope = ptx::smem_desc(c.smem + kOffQRope, 16, 512, 4);
-  d.p = ptx::smem_desc(c.smem + kOffP, 512, 512, 4);
+  d.kv_k = make_desc(c.smem + kOffKV, 16, 1024, 2);
+  d.kv_mn = make_desc(c.smem + kOffKV, kBlockBytes, 1024, 2);
+  d.q_lat = make_desc(c.smem + kOffQLat, 16, 1024, 2);
+  d.rope = make_desc(c.smem + kOffRope, 16, 512, 4);
+  d.q_rope = make_desc(c.smem + kOffQRope, 16, 512, 4);
+  d.p = make_desc(c.smem + kOffP, 512, 512, 4);
   return d;
 }
 
@@ -453,9 +467,9 @@ __device__ __forceinline__ void qk_role(const Ctx& c, uint32_t tmem, RoleState& 
       if (k >= 1) ok = wait_warp(c, bar_s_empty(s), (k - 1) & 1);
       ok = ok && wait_warp(c, bar_aux_full(s), k & 1);
       MLA_TRACE(2, it, 0);
-#pragma unroll 1
-      for (uint32_t j = 0; j < kBlocks && ok; ++j) {
-        ok = wait_warp(c, bar_kv_full(s, j), k & 1);
+#pragma unroll
+      for (uint32_t j = 0; j < kBlocks; ++j) {
+        ok = ok && wait_warp(c, bar_kv_full(s, j), k & 1);
         if (ok) issue_qk_block(c, d, it, j, tmem);
       }
       MLA_TRACE(2, it, 2);
@@ -467,8 +481,9 @@ __device__ __forceinline__ void qk_role(const Ctx& c, uint32_t tmem, RoleState& 
   }
 }
 
-// role: PV issue (warp 2)
-__device__ __forceinline__ void pv_role(const Ctx& c, uint32_t tmem, RoleState& st) {
+// role: PV issue (warps 2 and 3: two of the four 128-dim blocks each, so that the 32 MMAs of a tile are
+// issued through two warp schedulers; an issue warp shares its scheduler with four compute warps)
+__device__ __forceinline__ void pv_role(const Ctx& c, uint32_t tmem, RoleState& st, uint32_t part) {
   const MmaDescs d = make_descs(c);
   const int nseg = c.misc->nseg;
   const Segment* sg = segs(c);
@@ -482,9 +497,10 @@ __device__ __forceinline__ void pv_role(const Ctx& c, uint32_t tmem, RoleState& 
       const uint32_t it = st.it + t, s = it & 1, k = it >> 1;
       ok = wait_warp(c, bar_p_full(s), k & 1);
       if (!ok) break;
-      MLA_TRACE(2, it, 4);
-      issue_pv(c, d, it, tmem, t == 0);
-      MLA_TRACE(2, it, 5);
+      if (part == 0) MLA_TRACE(2, it, 4);
+      if (part == 0) issue_pv(c, d, it, tmem, t == 0, 0, kBlocks / 2);
+      else issue_pv(c, d, it, tmem, t == 0, kBlocks / 2, kBlocks);
+      if (part == 1) MLA_TRACE(2, it, 5);
     }
     st.it += n;
   }
@@ -764,7 +780,10 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       t.p_lo = t.p_hi + kTile * 64;
 
       // the P buffer of this stage is free once PV of tile it-2 has completed
-      if (k >= 1) wait(c, bar_kv_empty(s, 3), (k - 1) & 1);
+      if (k >= 1) {  // both PV issue warps' last blocks
+        wait(c, bar_kv_empty(s, 1), (k - 1) & 1);
+        wait(c, bar_kv_empty(s, 3), (k - 1) & 1);
+      }
       wait(c, bar_s_full(s), k & 1);
       if (tid == 0) MLA_TRACE(0, it, 1);
       ptx::tc_fence_after();
@@ -790,6 +809,7 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
         }
         if (!first) {  // O^T holds earlier tiles: rescale once their PV has completed
           const uint32_t pit = it - 1;
+          wait(c, bar_kv_empty(pit & 1, 1), (pit >> 1) & 1);
           wait(c, bar_kv_empty(pit & 1, 3), (pit >> 1) & 1);
           ptx::tc_fence_after();
           rescale_output(c, tmem_lane, uint32_t(half));
@@ -821,6 +841,7 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       }
       ptx::bar_sync(1, kSoftmaxThreads);
       // wait for the PV of the last tile
+      wait(c, bar_kv_empty(lit & 1, 1), (lit >> 1) & 1);
       wait(c, bar_kv_empty(lit & 1, 3), (lit >> 1) & 1);
       ptx::tc_fence_after();
       float sc_all = 0.f;
@@ -1148,7 +1169,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
     ptx::mbar_init(bar_addr(c, kBarQFull), 1);
     ptx::mbar_init(bar_addr(c, kBarQEmpty), 1);
     ptx::mbar_init(bar_addr(c, kBarOFree), kSoftmaxThreads);
-    ptx::mbar_init(bar_addr(c, kBarDrain), 2);
+    ptx::mbar_init(bar_addr(c, kBarDrain), 3);
     ptx::fence_barrier_init();
   } else if (warp == kWarpPV && (tid & 31) == 0) {
     ptx::prefetch_tensormap(&map_q_lat);
@@ -1176,29 +1197,8 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
       softmax_role(p, c, tmem, tid - 32 * kWarpSoftmax0, st);
     } else if (warp == kWarpQK) {
       qk_role(c, tmem, st);
-    } else if (warp == kWarpPV) {
-      pv_role(c, tmem, st);
-#ifdef MLA_FP4_TRACE
-    } else if (warp == kWarpSpare) {  // observers: lane 0 QK^T completion, lane 1 PV completion (block 0 and whole tile)
-      if (blockIdx.x == gridDim.x - 1 && (tid & 31) < 2) {
-        const int nseg = c.misc->nseg;
-        uint32_t it = 0;
-        for (int si = 0; si < nseg; ++si)
-          for (int tt = segs(c)[si].tile_begin; tt < segs(c)[si].tile_end; ++tt, ++it) {
-            const uint32_t s = it & 1, k = it >> 1;
-            if ((tid & 31) == 0) {
-              while (!ptx::mbar_try_wait(bar_addr(c, bar_s_full(s)), k & 1) && !c.misc->abort) {}
-              MLA_TRACE(3, it, 2);
-            } else {
-              while (!ptx::mbar_try_wait(bar_addr(c, bar_kv_empty(s, 0)), k & 1) && !c.misc->abort) {}
-              MLA_TRACE(3, it, 4);
-              while (!ptx::mbar_try_wait(bar_addr(c, bar_kv_empty(s, 3)), k & 1) && !c.misc->abort) {}
-              MLA_TRACE(3, it, 3);
-            }
-          }
-      }
-      __syncwarp();
-#endif
+    } else if (warp == kWarpPV || warp == kWarpPV2) {
+      pv_role(c, tmem, st, uint32_t(warp - kWarpPV));
     } else if (warp == kWarpTMA) {
       if ((tid & 31) == 0) tma_role(p, c, &map_q_lat, &map_q_rope, &map_rope, st);
       __syncwarp();
@@ -1211,7 +1211,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   }
 
   // drain: everything issued has completed before TMEM is released
-  if (warp == kWarpQK || warp == kWarpPV) {  // a commit covers the MMAs of the thread that executes it
+  if (warp == kWarpQK || warp == kWarpPV || warp == kWarpPV2) {  // a commit covers the MMAs of the thread that executes it
     if (ptx::elect_one()) {
       ptx::umma_commit(bar_addr(c, kBarDrain));
       drain_wait(c, kBarDrain, 0);
