@@ -4,26 +4,31 @@
 // For a tile of request b and a group of 64 query heads the CTA computes, with tokens on the
 // MMA M axis ("swapped" orientation, so 64 heads do not waste half of a 128-row MMA):
 //
-//   S_lat^T [128 tok, 64 head] = K_lat (E4M3, 128x512)  . Q_lat^T      16 x tcgen05.mma K=32
-//   S_rope^T[128 tok, 64 head] = K_rope(E4M3, 128x64)   . Q_rope^T      2 x tcgen05.mma
+//   S_lat^T [128 tok, 64 head] = K_lat (E2M1, 128x512)  . Q_lat^T(E4M3)  16 x tcgen05.mma K=32
+//   S_rope^T[128 tok, 64 head] = K_rope(E4M3, 128x64)   . Q_rope^T        2 x tcgen05.mma
 //   x = (scale_t * S_lat + S_rope) * softmax_scale*log2(e)              per token row, registers
 //   P' = exp2(x - m_head) * scale_t, split into E4M3 hi + E4M3 lo       (two terms ~ 8 mantissa bits)
-//   O^T[512 dim, 64 head] += V^T (E4M3, MN-major view of the same K_lat tile) . (P'_hi + P'_lo)
+//   O^T[512 dim, 64 head] += V^T (E2M1, MN-major view of the same K_lat tile) . (P'_hi + P'_lo)
 //
-// The packed E2M1 latent is read from global memory straight into the registers of eight
-// dequant warps (one tile ahead), expanded to E4M3 with a byte-permute table and written once
-// into 128-byte-swizzled shared memory, where the very same bytes serve as the K-major A operand
-// of QK^T and as the MN-major A operand of PV.  RoPE bytes, per-token scales and Q arrive by TMA.
+// The packed E2M1 latent goes from global memory to shared memory by TMA with the 4-bit tensor-map
+// type that writes every 16 codes as 8 bytes of data + 8 bytes of padding: the form in which
+// tcgen05.mma.kind::f8f6f4 reads 4-bit operands.  A 128-dim block of a tile is then [128 tokens][128 B]
+// with the 128-byte swizzle, and the very same bytes serve as the K-major A operand of QK^T and as the
+// MN-major A operand of PV: there is no conversion pass and no copy of the tile in any other format.
+// (Earlier versions expanded the codes to E4M3 with eight warps; those warps competed with the softmax
+// warps for issue slots and with the MMAs for shared-memory bandwidth, and were the busiest role.)
+// RoPE bytes, per-token scales and Q arrive by TMA as well; pages two tiles ahead are prefetched into L2.
 //
-// Warp roles (640 threads): 0 QK^T issue, 1 TMA issue, 2 and 3 PV issue, two 128-dim blocks each (issue
-// warps run warp-uniform code, one elected lane per instruction), 4-11 softmax / O rescale / epilogue
-// (TMEM lane = token or dim; two warps share a lane quarter and split the 64 heads), 12-19 latent load + dequant.
+// Warp roles (384 threads): 0 QK^T issue, 1 TMA issue (lane i owns page i of the tile), 2 and 3 PV issue,
+// two 128-dim blocks each (issue warps run warp-uniform code, one elected lane per instruction),
+// 4-11 softmax / O rescale / epilogue (TMEM lane = token or dim; two warps share a lane quarter and
+// split the 64 heads).
 //
 // Requests that are split across CTAs are merged at the end of the same kernel (tail_merge): the
 // CTAs publish their partials through counters in the workspace header and each takes a share of
 // the output dims.  The two-kernel mode leaves the merge to the combine kernel instead.
 //
-// The per-role loops are kept small on purpose: the four instruction streams share one
+// The per-role loops are kept small on purpose: the instruction streams share one
 // instruction cache, and an MMA-issue or softmax loop that misses it starves the tensor pipe.
 //
 // Every wait is bounded: when a wait expires the CTA records MLA_FP4_ERR_DEVICE_TIMEOUT in the
@@ -34,7 +39,6 @@
 #include <cuda_fp8.h>
 
 #include "common.cuh"
-#include "dequant.cuh"
 #include "launch.h"
 #include "ptx_sm100.cuh"
 
@@ -42,16 +46,11 @@ namespace mla {
 
 namespace {
 
-// Warp roles.  The three issue warps have the lowest warp ids: the warp scheduler prefers older
-// warps, and an issue warp that has to queue behind four busy compute warps on its scheduler
-// delays the tensor pipe (measured with the issue warps last: PV issue 1.7 k clk alone, 4.5 k clk next to busy warps).
+// Warp roles.  One issue warp per warp scheduler (warp id mod 4), each next to two softmax warps.
 constexpr int kWarpQK = 0, kWarpTMA = 1, kWarpPV = 2, kWarpPV2 = 3;
 constexpr int kWarpSoftmax0 = 4;       // 8 warps; warp & 3 is the TMEM lane quarter the warp may access
-constexpr int kWarpDequant0 = 12;      // 8 warps
-constexpr int kThreads = 640;          // 20 warps, five per scheduler, hence at most 96 registers per thread
+constexpr int kThreads = 384;          // 12 warps, three per scheduler
 constexpr int kSoftmaxThreads = 256;   // 8 warps: warp w works on TMEM lanes 32*(w%4).. and heads 32*(w/4)..
-constexpr int kDequantThreads = 256;
-constexpr int kDequantWarps = kDequantThreads / 32;
 constexpr int kStages = 2;
 constexpr int kBlocks = 4;                 // 128-dim blocks of the latent
 constexpr int kBlockBytes = kTile * 128;   // 16 KiB: [128 tokens][128 B], 128B swizzle
@@ -97,8 +96,10 @@ constexpr uint32_t kColSLat = 0;     // + 64 * stage
 constexpr uint32_t kColSRope = 128;  // + 64 * stage
 constexpr uint32_t kColO = 256;      // + 64 * block
 
-constexpr uint32_t kIdescQK = ptx::idesc_e4m3(128, kGroupHeads, false, false);
-constexpr uint32_t kIdescPV = ptx::idesc_e4m3(128, kGroupHeads, true, true);
+constexpr uint32_t kFmtE2M1 = 5u << 7;  // A operand format field of kind::f8f6f4 (E4M3 = 0)
+constexpr uint32_t kIdescQKRope = ptx::idesc_e4m3(128, kGroupHeads, false, false);       // E4M3 x E4M3
+constexpr uint32_t kIdescQK = ptx::idesc_e4m3(128, kGroupHeads, false, false) | kFmtE2M1;  // E2M1 (K tile) x E4M3 (Q)
+constexpr uint32_t kIdescPV = ptx::idesc_e4m3(128, kGroupHeads, true, true) | kFmtE2M1;    // E2M1 (V^T, MN-major) x E4M3 (P)
 
 // A split request this CTA wrote a partial for (at most two: its first and its last segment).
 struct MergeReq {
@@ -126,6 +127,9 @@ struct Ctx {
   uint8_t* smem_ptr;  // generic pointer to the same
   Misc* misc;
   int32_t* status;
+#ifdef MLA_FP4_TRACE
+  int trace_cta;  // the CTA whose timeline is recorded (status word 7; the last CTA when negative)
+#endif
 };
 
 // running position of a role across rounds
@@ -187,7 +191,7 @@ __device__ __noinline__ void drain_wait(const Ctx& c, int idx, uint32_t parity) 
 #ifdef MLA_FP4_TRACE
 #define MLA_TRACE(role, tile, ev)                                                                      \
   do {                                                                                                 \
-    if (blockIdx.x == gridDim.x - 1 && (tile) < 16u && c.status)                                                   \
+    if (int(blockIdx.x) == c.trace_cta && (tile) < 16u && c.status)                                                   \
       reinterpret_cast<long long*>(c.status + 8)[((role) * 16 + (tile)) * 8 + (ev)] = clock64();       \
   } while (0)
 #else
@@ -195,129 +199,25 @@ __device__ __noinline__ void drain_wait(const Ctx& c, int idx, uint32_t parity) 
 #endif
 
 // ------------------------------------------------------------------------------------------
-// role: latent load + dequant (warps 12..19)
+// role: TMA issue (warp 1): Q per segment; per tile the packed latent (four blocks), RoPE bytes and scales
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint4 ldg_nc(const uint8_t* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-
-// 16 packed bytes (32 codes) -> 32 E4M3 bytes (two 16-byte chunks).  Everything in this loop is
-// inlined on purpose: a call makes the compiler wait, at the call, for every global load still in
-// flight (their destination registers must survive the call), which exposes the memory latency.
-struct E4m3x32 {
-  uint32_t a[4], b[4];
-};
-__device__ __forceinline__ E4m3x32 dequant32(uint4 v) {
-  E4m3x32 r;
-  e2m1x8_to_e4m3x8(v.x, r.a[0], r.a[1]);
-  e2m1x8_to_e4m3x8(v.y, r.a[2], r.a[3]);
-  e2m1x8_to_e4m3x8(v.z, r.b[0], r.b[1]);
-  e2m1x8_to_e4m3x8(v.w, r.b[2], r.b[3]);
-  return r;
-}
-__device__ __forceinline__ void store32(const E4m3x32& r, uint32_t dst_a, uint32_t dst_b) {
-  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst_a), "r"(r.a[0]), "r"(r.a[1]), "r"(r.a[2]), "r"(r.a[3]) : "memory");
-  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst_b), "r"(r.b[0]), "r"(r.b[1]), "r"(r.b[2]), "r"(r.b[3]) : "memory");
-}
-
-// Row pointers of this thread's two tokens (r0 and r0 + 64) of tile t of a segment; nullptr beyond seq_len.
-__device__ __forceinline__ void row_sources(const DecodeParams& p, const Segment& sg, int t, int r0, const uint8_t* (&ptr)[2]) {
-  const uint8_t* cache = reinterpret_cast<const uint8_t*>(p.kv_cache);
-  const int32_t* bt = p.block_tables + size_t(sg.b) * p.block_table_stride;
-#pragma unroll
-  for (int u = 0; u < 2; ++u) {
-    const int tok = t * kTile + r0 + 64 * u;
-    ptr[u] = nullptr;
-    if (tok < sg.seq_len) ptr[u] = cache + (size_t(__ldg(bt + tok / p.page_size)) * p.page_size + tok % p.page_size) * kRowBytes;
-  }
-}
-
-__device__ __forceinline__ void dequant_role(const DecodeParams& p, const Ctx& c, int dtid, RoleState& st) {
-  const int nseg = c.misc->nseg;
-  if (nseg == 0) return;
-  const Segment* sg = segs(c);
-  const int r0 = dtid >> 2;    // 0..63; this thread's rows are r0 and r0 + 64
-  const int ch = dtid & 3;     // 16-byte packed chunk inside the 64-byte slice of a block
-  const int lane = dtid & 31;
-  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-
-  int si = 0, t = sg[0].tile_begin;
-  const uint8_t* src[2];
-  row_sources(p, sg[0], t, r0, src);
-  uint4 regs[kBlocks][2];
-#pragma unroll
-  for (int j = 0; j < kBlocks; ++j)
-#pragma unroll
-    for (int u = 0; u < 2; ++u) regs[j][u] = src[u] ? ldg_nc(src[u] + 64 * j + 16 * ch) : zero;
-  // swizzled destinations inside a block: row*128 + ((2*ch + e) ^ (row & 7)) * 16; (r0 + 64) & 7 == r0 & 7
-  const uint32_t sw0 = uint32_t(r0 & 7);
-  const uint32_t off_a = uint32_t(r0) * 128u + ((uint32_t(2 * ch) ^ sw0) << 4);
-  const uint32_t off_b = uint32_t(r0) * 128u + ((uint32_t(2 * ch + 1) ^ sw0) << 4);
-
-  bool more = true;
-  while (more) {
-    const uint32_t it = st.it;
-    const uint32_t s = it & 1, k = it >> 1;
-    // position of the next tile (prefetched while this one is converted)
-    int nsi = si, nt = t + 1;
-    if (nt == sg[si].tile_end) {
-      ++nsi;
-      more = nsi < nseg;
-      if (more) nt = sg[nsi].tile_begin;
-    }
-    if (more) row_sources(p, sg[nsi], nt, r0, src);
-    if (dtid == 0) MLA_TRACE(1, it, 0);
-    // Software pipeline over the four blocks: the conversion of block j+1 (registers only) is issued
-    // between the stores of block j and the proxy fence that has to wait for them.
-    E4m3x32 e0 = dequant32(regs[0][0]);
-    E4m3x32 e1 = dequant32(regs[0][1]);
-#pragma unroll
-    for (int j = 0; j < kBlocks; ++j) {
-      if (k >= 1) wait_warp(c, bar_kv_empty(s, j), (k - 1) & 1);
-      if (dtid == 0) MLA_TRACE(1, it, 1 + j);
-      const uint32_t base = c.smem + kOffKV + (s * kBlocks + j) * kBlockBytes;
-      store32(e0, base + off_a, base + off_b);
-      store32(e1, base + off_a + 64u * 128u, base + off_b + 64u * 128u);
-      if (more) {  // this block's registers are free: fetch the same block of the next tile
-#pragma unroll
-        for (int u = 0; u < 2; ++u) regs[j][u] = src[u] ? ldg_nc(src[u] + 64 * j + 16 * ch) : zero;
-      }
-      if (j + 1 < kBlocks) {
-        e0 = dequant32(regs[j + 1][0]);
-        e1 = dequant32(regs[j + 1][1]);
-      }
-      ptx::fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(bar_addr(c, bar_kv_full(s, j)));
-      if (lane == 0) MLA_TRACE(4 + (dtid >> 5), it, j);
-    }
-    if (dtid == 0) MLA_TRACE(1, it, 5);
-    si = nsi;
-    t = nt;
-    ++st.it;
-  }
-  st.seg += nseg;
-}
-
-// ------------------------------------------------------------------------------------------
-// role: TMA issue (warp 1, one lane): Q per segment; RoPE bytes + scales per tile
-// ------------------------------------------------------------------------------------------
+// The whole warp runs this role: lane i owns page i of the current tile (at most 16 pages of 8 tokens),
+// keeps its page id in a register and issues that page's copies; lane 0 does the waits and arms the barriers.
 __device__ __forceinline__ void tma_role(const DecodeParams& p, const Ctx& c, const CUtensorMap* map_q_lat,
-                                         const CUtensorMap* map_q_rope, const CUtensorMap* map_rope, RoleState& st) {
+                                         const CUtensorMap* map_q_rope, const CUtensorMap* map_rope,
+                                         const CUtensorMap* map_lat, RoleState& st) {
   const int nseg = c.misc->nseg;
   const Segment* sg = segs(c);
+  const int lane = threadIdx.x & 31;
   const int ppt = kTile / p.page_size;  // pages per tile
   const uint32_t page_rope_bytes = uint32_t(p.page_size) * 64u;
   const uint32_t page_scale_bytes = uint32_t(p.page_size) * 4u;
+  const uint32_t page_block_bytes = uint32_t(p.page_size) * 128u;  // one 128-dim block of a page as it lies in shared memory
 #pragma unroll 1
   for (int si = 0; si < nseg; ++si, ++st.seg) {
     const Segment g = sg[si];
-    if (st.seg >= 1) wait(c, kBarQEmpty, (st.seg - 1) & 1);
-    if (!c.misc->abort) {
+    if (st.seg >= 1) wait_warp(c, kBarQEmpty, (st.seg - 1) & 1);
+    if (lane == 0 && !c.misc->abort) {
       int qpos, head0;
       group_coords(g.g, p.num_heads, qpos, head0);
       const uint32_t bar = bar_addr(c, kBarQFull);
@@ -328,35 +228,73 @@ __device__ __forceinline__ void tma_role(const DecodeParams& p, const Ctx& c, co
       ptx::tma_load_4d(c.smem + kOffQRope, map_q_rope, bar, kLatent, head0, qpos, g.b);
     }
     const int pages_total = (g.seq_len + p.page_size - 1) / p.page_size;
+    const int32_t* bt_req = p.block_tables + size_t(g.b) * p.block_table_stride;
+    // This lane's page id for the current tile and the two after it, loaded a tile ahead of their use
+    // (never beyond the request's pages).
+    auto page_of = [&](int tile) {
+      const int lp = tile * ppt + lane;
+      return (tile < g.tile_end && lane < ppt && lp < pages_total) ? __ldg(bt_req + lp) : -1;
+    };
+    int pg = page_of(g.tile_begin), pg1 = page_of(g.tile_begin + 1), pg2 = page_of(g.tile_begin + 2);
 #pragma unroll 1
     for (int t = g.tile_begin; t < g.tile_end; ++t, ++st.it) {
       const uint32_t s = st.it & 1, k = st.it >> 1;
-      // The RoPE tile of this stage was last read by QK of tile it-2 and the scales by the softmax
-      // of tile it-2; both are over once the softmax threads have released S of that tile.  (Waiting
-      // for PV of tile it-2 instead would put the copy's latency on the critical path.)
-      if (k >= 1) wait(c, bar_s_empty(s), (k - 1) & 1);
-      if (c.misc->abort) continue;
-      const int lp0 = t * ppt;
-      const int np = min(ppt, pages_total - lp0);
-      const uint32_t bar = bar_addr(c, bar_aux_full(s));
-      ptx::mbar_arrive_expect_tx(bar, uint32_t(np) * (page_rope_bytes + page_scale_bytes));
-      const int32_t* bt = p.block_tables + size_t(g.b) * p.block_table_stride + lp0;
-#pragma unroll 1
-      for (int i = 0; i < np; ++i) {
-        const int pg = __ldg(bt + i);
-        ptx::tma_load_3d(c.smem + kOffRope + s * kTile * 64 + uint32_t(i) * page_rope_bytes, map_rope, bar, kLatent / 2, 0, pg);
-        ptx::bulk_load(c.smem + kOffScale + s * kTile * 4 + uint32_t(i) * page_scale_bytes,
-                       p.kv_cache_sf + size_t(pg) * p.page_size, page_scale_bytes, bar);
+      if (lane == 0) MLA_TRACE(1, st.it, 0);
+      const int np = min(ppt, pages_total - t * ppt);
+      const bool mine = pg >= 0;
+      const int pg3 = page_of(t + 3);  // in flight while this tile is issued
+      // Two tiles ahead there is no free shared-memory stage yet, but L2 can take the rows already: the
+      // copy issued later (when PV frees the stage) then finds them there instead of waiting for HBM.
+      if (pg2 >= 0) {  // a page is one contiguous range of the cache, and one of the scale tensor
+        ptx::bulk_prefetch_l2(reinterpret_cast<const uint8_t*>(p.kv_cache) + size_t(pg2) * p.page_size * kRowBytes,
+                              uint32_t(p.page_size) * kRowBytes);
+        ptx::bulk_prefetch_l2(p.kv_cache_sf + size_t(pg2) * p.page_size, page_scale_bytes);
       }
+      // The RoPE tile of this stage was last read by QK of tile it-2 and the scales by the softmax
+      // of tile it-2; both are over once the softmax threads have released S of that tile.
+      if (k >= 1) wait_warp(c, bar_s_empty(s), (k - 1) & 1);
+      if (!c.misc->abort) {
+        const uint32_t bar = bar_addr(c, bar_aux_full(s));
+        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, uint32_t(np) * (page_rope_bytes + page_scale_bytes));
+        __syncwarp();
+        if (mine) {
+          ptx::tma_load_3d(c.smem + kOffRope + s * kTile * 64 + uint32_t(lane) * page_rope_bytes, map_rope, bar, kLatent / 2, 0, pg);
+          ptx::bulk_load(c.smem + kOffScale + s * kTile * 4 + uint32_t(lane) * page_scale_bytes,
+                         p.kv_cache_sf + size_t(pg) * p.page_size, page_scale_bytes, bar);
+        }
+      }
+      // The packed E2M1 latent: the tensor map's 4-bit type makes the copy write every 16 values as
+      // 8 bytes of data + 8 bytes of padding, the form the MMA reads 4-bit operands in, so a block is
+      // [128 tokens][128 B] with the same 128-byte swizzle as an 8-bit tile and needs no conversion pass.
+      // Block j of this stage is free once PV of tile it-2 has finished with it.
+#pragma unroll 1
+      for (int j = 0; j < kBlocks; ++j) {
+        if (k >= 1) wait_warp(c, bar_kv_empty(s, j), (k - 1) & 1);
+        if (c.misc->abort) break;
+        if (lane == 0) MLA_TRACE(1, st.it, 1 + j);
+        const uint32_t bar = bar_addr(c, bar_kv_full(s, j));
+        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, uint32_t(np) * (page_block_bytes / 2));  // the transaction count is in packed bytes
+        __syncwarp();
+        if (mine)
+          ptx::tma_load_3d(c.smem + kOffKV + (s * kBlocks + j) * kBlockBytes + uint32_t(lane) * page_block_bytes, map_lat, bar,
+                           128 * j, 0, pg);
+      }
+      pg = pg1;
+      pg1 = pg2;
+      pg2 = pg3;
     }
   }
-  if (c.misc->abort) {  // let copies that were issued but never consumed land before exit
+  if (c.misc->abort && lane == 0) {  // let copies that were issued but never consumed land before exit
     for (uint32_t s = 0; s < kStages; ++s) {
       const uint32_t used = (st.it + 1 - s) >> 1;  // tiles issued on stage s
-      if (used >= 1) drain_wait(c, bar_aux_full(s), (used - 1) & 1);
+      if (used >= 1) {
+        drain_wait(c, bar_aux_full(s), (used - 1) & 1);
+        for (int j = 0; j < kBlocks; ++j) drain_wait(c, bar_kv_full(s, j), (used - 1) & 1);
+      }
     }
     if (st.seg >= 1) drain_wait(c, kBarQFull, (st.seg - 1) & 1);
   }
+  __syncwarp();
 }
 
 // ------------------------------------------------------------------------------------------
@@ -366,7 +304,7 @@ __device__ __forceinline__ void tma_role(const DecodeParams& p, const Ctx& c, co
 // A shared-memory descriptor as two words.  Only the 14-bit address field (bytes >> 4) in the low word
 // changes from one instruction to the next and it cannot carry out (shared memory is smaller than
 // 2^18 bytes), so stepping a descriptor is ONE 32-bit add; with 64-bit descriptors the compiler has to
-// propagate a carry it cannot rule out.  The issue warps share their schedulers with four busy
+// propagate a carry it cannot rule out.  The issue warps share their schedulers with two busy
 // compute warps each, so every instruction they do not execute shortens the tensor pipe's waits.
 struct Desc {
   uint32_t lo, hi;
@@ -399,7 +337,7 @@ __device__ __forceinline__ void issue_qk_block(const Ctx& c, const MmaDescs& d, 
       const uint32_t d_rope = tmem + kColSRope + 64u * s;
       const uint32_t r_off = s * ((kTile * 64) >> 4);
 #pragma unroll
-      for (uint32_t ks = 0; ks < 2; ++ks) ptx::umma_f8(d_rope, d.rope.at(r_off + 2 * ks), d.q_rope.at(2 * ks), kIdescQK, ks);
+      for (uint32_t ks = 0; ks < 2; ++ks) ptx::umma_f8(d_rope, d.rope.at(r_off + 2 * ks), d.q_rope.at(2 * ks), kIdescQKRope, ks);
     }
 #pragma unroll
     for (uint32_t ks = 0; ks < 4; ++ks)
@@ -482,7 +420,7 @@ __device__ __forceinline__ void qk_role(const Ctx& c, uint32_t tmem, RoleState& 
 }
 
 // role: PV issue (warps 2 and 3: two of the four 128-dim blocks each, so that the 32 MMAs of a tile are
-// issued through two warp schedulers; an issue warp shares its scheduler with four compute warps)
+// issued through two warp schedulers; an issue warp shares its scheduler with two compute warps)
 __device__ __forceinline__ void pv_role(const Ctx& c, uint32_t tmem, RoleState& st, uint32_t part) {
   const MmaDescs d = make_descs(c);
   const int nseg = c.misc->nseg;
@@ -1011,27 +949,27 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
       }
       __syncthreads();
       if (tid == 0) MLA_TRACE(3, 1u, 3);
-      if (tid < 8 * kGroupHeads) {  // eight lanes per head split the slots; butterflies give all of them the result
-        const int h = tid >> 3, j = tid & 7;
+      if (tid < 4 * kGroupHeads) {  // four lanes per head split the slots; butterflies give all of them the result
+        const int h = tid >> 2, j = tid & 3;
         float* col = lse_s + h;
         float mx = -INFINITY;
 #pragma unroll 1
-        for (int i = j; i < ns; i += 8) mx = fmaxf(mx, col[i * kTailLseStride]);
+        for (int i = j; i < ns; i += 4) mx = fmaxf(mx, col[i * kTailLseStride]);
 #pragma unroll
-        for (int off = 4; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        for (int off = 2; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
         float dsum = 0.f;
 #pragma unroll 1
-        for (int i = j; i < ns; i += 8) {
+        for (int i = j; i < ns; i += 4) {
           const float l = col[i * kTailLseStride];
           const float e = (l == -INFINITY) ? 0.f : ptx::ex2(l - mx);
           col[i * kTailLseStride] = e;
           dsum += e;
         }
 #pragma unroll
-        for (int off = 4; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
+        for (int off = 2; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
         const float inv = dsum > 0.f ? __frcp_rn(dsum) : 0.f;
 #pragma unroll 1
-        for (int i = j; i < ns; i += 8) col[i * kTailLseStride] *= inv * scale_s[i];  // weights, times the slot's fp16 scale
+        for (int i = j; i < ns; i += 4) col[i * kTailLseStride] *= inv * scale_s[i];  // weights, times the slot's fp16 scale
         if (j == 0 && rank == 0 && p.lse && h < heads_here) p.lse[row0 + h] = (dsum > 0.f) ? (__log2f(dsum) + mx) : -INFINITY;
       }
       __syncthreads();
@@ -1128,9 +1066,10 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
 // ------------------------------------------------------------------------------------------
 // kernel
 // ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(640, 1)  // register budget of five warps per scheduler (kThreads are launched)
+__global__ void __launch_bounds__(kThreads, 1)
 mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map_q_lat,
-                            const __grid_constant__ CUtensorMap map_q_rope, const __grid_constant__ CUtensorMap map_rope) {
+                            const __grid_constant__ CUtensorMap map_q_rope, const __grid_constant__ CUtensorMap map_rope,
+                            const __grid_constant__ CUtensorMap map_lat) {
   extern __shared__ uint8_t smem_raw[];
   Ctx c;
   {
@@ -1141,6 +1080,9 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   }
   c.misc = reinterpret_cast<Misc*>(c.smem_ptr + kOffMisc);
   c.status = p.status;
+#ifdef MLA_FP4_TRACE
+  c.trace_cta = (p.status && p.status[7] >= 0 && p.status[7] < int(gridDim.x) && p.status[7] != 0) ? p.status[7] : int(gridDim.x) - 1;
+#endif
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
 
@@ -1158,7 +1100,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   } else if (warp == kWarpTMA && (tid & 31) == 0) {
     for (int s = 0; s < kStages; ++s) {
       for (int j = 0; j < kBlocks; ++j) {
-        ptx::mbar_init(bar_addr(c, bar_kv_full(s, j)), kDequantWarps);
+        ptx::mbar_init(bar_addr(c, bar_kv_full(s, j)), 1);
         ptx::mbar_init(bar_addr(c, bar_kv_empty(s, j)), 1);
       }
       ptx::mbar_init(bar_addr(c, bar_aux_full(s)), 1);
@@ -1175,6 +1117,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
     ptx::prefetch_tensormap(&map_q_lat);
     ptx::prefetch_tensormap(&map_q_rope);
     ptx::prefetch_tensormap(&map_rope);
+    ptx::prefetch_tensormap(&map_lat);
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -1191,17 +1134,14 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   st.part = 0;
   // Rounds: almost always exactly one; more only when a CTA's range spans more than kMaxSeg requests.
   for (;;) {
-    if (warp >= kWarpDequant0) {
-      dequant_role(p, c, tid - 32 * kWarpDequant0, st);
-    } else if (warp >= kWarpSoftmax0) {
+    if (warp >= kWarpSoftmax0) {
       softmax_role(p, c, tmem, tid - 32 * kWarpSoftmax0, st);
     } else if (warp == kWarpQK) {
       qk_role(c, tmem, st);
     } else if (warp == kWarpPV || warp == kWarpPV2) {
       pv_role(c, tmem, st, uint32_t(warp - kWarpPV));
     } else if (warp == kWarpTMA) {
-      if ((tid & 31) == 0) tma_role(p, c, &map_q_lat, &map_q_rope, &map_rope, st);
-      __syncwarp();
+      tma_role(p, c, &map_q_lat, &map_q_rope, &map_rope, &map_lat, st);
     }
     const int more = c.misc->more;
     __syncthreads();  // every role is done with the staged segments
@@ -1292,6 +1232,22 @@ cudaError_t launch_decode_sm100(const DecodeParams& p, int num_ctas, cudaStream_
       return cudaErrorInvalidValue;
     }
   }
+  CUtensorMap map_lat;
+  {
+    // the cache as 4-bit elements: 640 per row (the 512 latent codes, then the RoPE bytes seen as nibbles and
+    // never fetched through this map), page_size rows per page; a box is one 128-dim block of one page
+    EncodeTiledFn fn = get_encode_fn();
+    cuuint64_t gd[3] = {cuuint64_t(2 * kRowBytes), cuuint64_t(p.page_size), cuuint64_t(p.num_pages)};
+    cuuint64_t gs[2] = {cuuint64_t(kRowBytes), cuuint64_t(kRowBytes) * cuuint64_t(p.page_size)};
+    cuuint32_t bx[3] = {128, cuuint32_t(p.page_size), 1};
+    cuuint32_t es[3] = {1, 1, 1};
+    if (!fn || fn(&map_lat, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, const_cast<void*>(p.kv_cache), gd, gs, bx, es,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+      *err = "cuTensorMapEncodeTiled failed for the packed latent (kv_cache must be 32-byte aligned)";
+      return cudaErrorInvalidValue;
+    }
+  }
   {
     static bool attr_done[64] = {};
     int dev = 0;
@@ -1313,7 +1269,7 @@ cudaError_t launch_decode_sm100(const DecodeParams& p, int num_ctas, cudaStream_
   attr[0].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = p.fused_merge ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, mla_fp4_decode_sm100_kernel, p, map_q_lat, map_q_rope, map_rope);
+  return cudaLaunchKernelEx(&cfg, mla_fp4_decode_sm100_kernel, p, map_q_lat, map_q_rope, map_rope, map_lat);
 }
 
 }  // namespace mla
