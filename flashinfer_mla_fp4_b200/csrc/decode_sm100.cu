@@ -245,10 +245,18 @@ __device__ __forceinline__ void tma_role(const DecodeParams& p, const Ctx& c, co
       const int pg3 = page_of(t + 3);  // in flight while this tile is issued
       // Two tiles ahead there is no free shared-memory stage yet, but L2 can take the rows already: the
       // copy issued later (when PV frees the stage) then finds them there instead of waiting for HBM.
-      if (pg2 >= 0) {  // a page is one contiguous range of the cache, and one of the scale tensor
-        ptx::bulk_prefetch_l2(reinterpret_cast<const uint8_t*>(p.kv_cache) + size_t(pg2) * p.page_size * kRowBytes,
-                              uint32_t(p.page_size) * kRowBytes);
-        ptx::bulk_prefetch_l2(p.kv_cache_sf + size_t(pg2) * p.page_size, page_scale_bytes);
+      // The 32 lanes share the lines of each page of that tile (a page is one contiguous range).
+      {
+        const uint32_t page_bytes = uint32_t(p.page_size) * kRowBytes;
+#pragma unroll 1
+        for (int i = 0; i < ppt; ++i) {
+          const int pgi = __shfl_sync(0xffffffffu, pg2, i);
+          if (pgi < 0) break;
+          const uint8_t* base = reinterpret_cast<const uint8_t*>(p.kv_cache) + size_t(pgi) * page_bytes;
+#pragma unroll 1
+          for (uint32_t off = uint32_t(lane) * 128u; off < page_bytes; off += 32u * 128u)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off) : "memory");
+        }
       }
       // The RoPE tile of this stage was last read by QK of tile it-2 and the scales by the softmax
       // of tile it-2; both are over once the softmax threads have released S of that tile.
@@ -408,6 +416,7 @@ __device__ __forceinline__ void qk_role(const Ctx& c, uint32_t tmem, RoleState& 
 #pragma unroll
       for (uint32_t j = 0; j < kBlocks; ++j) {
         ok = ok && wait_warp(c, bar_kv_full(s, j), k & 1);
+        MLA_TRACE(2, it, j == 0 ? 7 : (j == 1 ? 1 : (j == 2 ? 6 : 3)));  // block j has landed
         if (ok) issue_qk_block(c, d, it, j, tmem);
       }
       MLA_TRACE(2, it, 2);
@@ -939,6 +948,35 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
       group_coords(m.g, p.num_heads, qpos, head0);
       const int heads_here = min(kGroupHeads, p.num_heads - head0);
       const size_t row0 = (size_t(m.b) * p.q_len + qpos) * p.num_heads + head0;
+      // This CTA's dims: pairs [256*rank/np, 256*(rank+1)/np).  A unit is (pair of dims, 8 heads, slot
+      // lane); the SL lanes of a unit are consecutive lanes of a warp, split the slots (four per batch,
+      // all their loads in flight together) and add their sums with a fixed shuffle tree
+      // (bit-reproducible).  Lane 0 of the unit writes 8 x 2 outputs.
+      const int u0 = (256 * rank) / np, u1 = (256 * (rank + 1)) / np;
+      const int d0 = 2 * u0, pairs = u1 - u0;
+      const int items = pairs * 8;
+      int SL = 1, lg = 0;
+      while (SL < 32 && 4 * SL < ns && items * SL * 2 <= kThreads) { SL *= 2; ++lg; }  // one round of threads if possible
+      const int units = items << lg;
+      const char* slot0 = reinterpret_cast<const char*>(slot_o(ws, 0));
+      auto load_batch = [&](const char* src, bool live_unit, int i0, uint4 (&a)[4][2]) {
+#pragma unroll
+        for (int qq = 0; qq < 4; ++qq) {
+          const bool ld = live_unit && i0 + qq * SL < ns;  // no load for a slot that does not exist
+          const char* sp = src + size_t(list_s[min(i0 + qq * SL, ns - 1)]) * kSlotBytes;
+          a[qq][0] = ld ? __ldcg(reinterpret_cast<const uint4*>(sp)) : make_uint4(0u, 0u, 0u, 0u);
+          a[qq][1] = ld ? __ldcg(reinterpret_cast<const uint4*>(sp + kGroupHeads * 2)) : make_uint4(0u, 0u, 0u, 0u);
+        }
+      };
+      // The first batch of partial rows does not depend on the weights: its loads go out together with the
+      // LSE loads, one round of latency instead of two.
+      uint4 a[4][2];
+      const int base0 = tid & ~31;
+      if (base0 < units) {
+        const int unit = tid;
+        const int item = min(unit, units - 1) >> lg, sl = unit & (SL - 1);
+        load_batch(slot0 + (size_t(d0 + 2 * (item >> 3)) * kGroupHeads + 8 * (item & 7)) * 2, unit < units, sl, a);
+      }
       // one round of independent loads: every LSE and every slot scale of the request
 #pragma unroll 1
       for (int idx = tid; idx < ns * (kGroupHeads + 1); idx += kThreads) {
@@ -974,37 +1012,20 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
       }
       __syncthreads();
       if (tid == 0) MLA_TRACE(3, 1u, 4);
-      // This CTA's dims: pairs [256*rank/np, 256*(rank+1)/np).  A unit is (pair of dims, 8 heads, slot
-      // lane); the SL lanes of a unit are consecutive lanes of a warp, split the slots (at most four
-      // each, all their loads in flight together) and add their sums with a fixed shuffle tree
-      // (bit-reproducible).  Lane 0 of the unit writes 8 x 2 outputs.
-      const int u0 = (256 * rank) / np, u1 = (256 * (rank + 1)) / np;
-      const int d0 = 2 * u0, pairs = u1 - u0;
-      const int items = pairs * 8;
-      int SL = 1, lg = 0;
-      while (SL < 32 && 4 * SL < ns && items * SL * 2 <= kThreads) { SL *= 2; ++lg; }  // one round of threads if possible
-      const int units = items << lg;
 #pragma unroll 1
       for (int base = (tid & ~31); base < units; base += kThreads) {
         const int unit = base + (tid & 31);
         const bool live_unit = unit < units;
         const int item = min(unit, units - 1) >> lg, sl = unit & (SL - 1);
         const int o = item & 7, pr = item >> 3;
-        const char* src = reinterpret_cast<const char*>(slot_o(ws, 0) + size_t(d0 + 2 * pr) * kGroupHeads + 8 * o);
+        const char* src = slot0 + (size_t(d0 + 2 * pr) * kGroupHeads + 8 * o) * 2;
         const float* wrow = lse_s + 8 * o;
         float acc[2][8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[0][e] = acc[1][e] = 0.f;
 #pragma unroll 1
         for (int i0 = sl; i0 < ns; i0 += 4 * SL) {  // four slots x two dims: eight independent 16-byte loads in flight
-          uint4 a[4][2];
-#pragma unroll
-          for (int qq = 0; qq < 4; ++qq) {
-            const bool ld = live_unit && i0 + qq * SL < ns;  // no load for a slot that does not exist
-            const char* sp = src + size_t(list_s[min(i0 + qq * SL, ns - 1)]) * kSlotBytes;
-            a[qq][0] = ld ? __ldcg(reinterpret_cast<const uint4*>(sp)) : make_uint4(0u, 0u, 0u, 0u);
-            a[qq][1] = ld ? __ldcg(reinterpret_cast<const uint4*>(sp + kGroupHeads * 2)) : make_uint4(0u, 0u, 0u, 0u);
-          }
+          if (!(base == base0 && i0 == sl)) load_batch(src, live_unit, i0, a);  // the first batch is already here
 #pragma unroll
           for (int qq = 0; qq < 4; ++qq) {
             const int i = i0 + qq * SL;
