@@ -1145,6 +1145,11 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   ptx::tc_fence_after();
   const uint32_t tmem = c.misc->tmem_base;
   if (tid == 0) MLA_TRACE(3, 0u, 0);
+#ifdef MLA_FP4_TRACE
+  auto gtimer = [] { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
+  unsigned long long* cta_times = p.status ? reinterpret_cast<unsigned long long*>(p.status + 8) + 12 * 16 * 8 + 3 * blockIdx.x : nullptr;
+  if (tid == 0 && cta_times) cta_times[0] = gtimer();
+#endif
   // Let a dependent kernel (the split-KV combine) start its launch and prologue early; it still waits
   // for this whole grid before it reads the partial slots.
   if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -1182,6 +1187,9 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   ptx::tc_fence_before();
   __syncthreads();
   if (tid == 0) MLA_TRACE(3, 0u, 1);
+#ifdef MLA_FP4_TRACE
+  if (tid == 0 && cta_times) cta_times[1] = gtimer();
+#endif
   if (warp == 0) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, 512);
@@ -1190,6 +1198,9 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
     tail_merge(p, c, tid);
     zero_empty_requests(p, tid);
     if (tid == 0) MLA_TRACE(3, 0u, 5);
+#ifdef MLA_FP4_TRACE
+    if (tid == 0 && cta_times) cta_times[2] = gtimer();
+#endif
   }
 }
 
