@@ -22,6 +22,7 @@ import torch
 import torch.distributed as dist
 
 from . import _cabi
+from .api_log import api_logged
 from .kvcache import LATENT_DIM
 
 
@@ -94,6 +95,7 @@ class ContextParallelDecoder:
             self._buf = torch.empty(n, dtype=torch.float32, device=device)
             self._gathered = torch.empty(self._world * n, dtype=torch.float32, device=device)
 
+    @api_logged
     def run(self, q, kv_cache, block_tables, seq_lens, max_seq_len, softmax_scale, output_scale: float = 1.0,
             out: Optional[torch.Tensor] = None, kv_cache_sf: Optional[torch.Tensor] = None, return_lse: bool = False):
         B, ql, H, _ = q.shape

@@ -13,6 +13,8 @@ from typing import Optional, Tuple
 
 import torch
 
+from .api_log import api_logged
+
 LATENT_DIM = 512
 ROPE_DIM = 64
 HEAD_DIM_QK = LATENT_DIM + ROPE_DIM  # 576
@@ -50,6 +52,7 @@ def quantize_tokens(
     return torch.cat((packed, rope_u8), dim=-1).contiguous(), token_scale.contiguous()
 
 
+@api_logged
 @torch.no_grad()
 def write_tokens(
     latent: torch.Tensor,

@@ -20,6 +20,7 @@ from typing import Optional, Tuple, Union
 import torch
 
 from . import _cabi
+from .api_log import api_logged
 from .kvcache import LATENT_DIM, ROPE_DIM, ROW_BYTES
 
 _OUT_DTYPES = {torch.bfloat16: _cabi.OUT_BF16, torch.float32: _cabi.OUT_F32, torch.float8_e4m3fn: _cabi.OUT_E4M3}
@@ -52,6 +53,7 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         self._phase_mask = 0  # profiling aid of the two-kernel mode: 1 = decode kernel only, 2 = combine kernel only
 
     # ------------------------------------------------------------------ plan
+    @api_logged
     def plan(
         self,
         kv_lora_rank: int = 512,
@@ -129,6 +131,7 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         if out is not None and out.dtype != self._o_dtype:
             raise ValueError(f"out.dtype={out.dtype} does not match planned {self._o_dtype}")
 
+    @api_logged
     def run(
         self,
         q: torch.Tensor,
