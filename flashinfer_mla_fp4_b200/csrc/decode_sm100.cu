@@ -857,6 +857,18 @@ constexpr uint32_t kTailList = kTailLse + kMaxCombineSlots * kTailLseStride * 4;
 constexpr uint32_t kTailScale = kTailList + kMaxCombineSlots * 4;      // [148] f32 slot scales
 static_assert(kTailScale + kMaxCombineSlots * 4 <= kOffKV + kStages * kBlocks * kBlockBytes, "tail scratch fits the idle KV ring");
 
+// Loads that happen only under a predicate and leave the destination untouched otherwise (the caller
+// never reads a destination whose load was off): no zero fill, no branch.
+__device__ __forceinline__ void ldcg_v4_if(uint4& d, const void* ptr, bool on) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t@p ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];\n\t}"
+               : "=r"(d.x), "=r"(d.y), "=r"(d.z), "=r"(d.w)
+               : "l"(ptr), "r"(uint32_t(on))
+               : "memory");
+}
+__device__ __forceinline__ void ldcg_f32_if(float& d, const float* ptr, bool on) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %2, 0;\n\t@p ld.global.cg.f32 %0, [%1];\n\t}" : "=f"(d) : "l"(ptr), "r"(uint32_t(on)) : "memory");
+}
+
 __device__ __forceinline__ int ld_acquire(const int32_t* p) {
   int v;
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -901,44 +913,64 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
     if (m.slot & 1) continue;
     int32_t* arrived = ws_arrived(ws) + m.counter;
     int32_t* done = ws_done(ws) + m.counter;
-    if (tid == 0) {
-      // Writers of the request: CTA m.counter, then every following CTA whose range starts before
-      // the request ends.  lo(i) = floor(Tt*i/n) is advanced without division: lo(i+1) = lo(i) + q
-      // + carry of the remainders.  The first writer uses slot 2i+1 unless its range starts with
-      // the request; the others start inside the request and use slot 2i; empty ranges write nothing.
+    // Writers of the request: CTA m.counter, then every following CTA whose range starts before the
+    // request ends and is not empty.  The first writer uses slot 2i+1 unless its range starts with the
+    // request; the others start inside the request, use slot 2i and take part in the merge.  Thread i
+    // looks at CTA i (one thread walking the CTAs cost 6000 clocks of dependent 64-bit arithmetic);
+    // ballots and per-warp counts give every writer its place in the list, in CTA order.
+    static_assert(kMaxCombineSlots <= kThreads, "one thread per CTA of the grid");
+    {
       const int64_t Tt = misc->walker.Tt;
-      const int64_t q = Tt / n, r = Tt - q * n;
       const int64_t end = m.start + m.tiles;
-      int64_t lo = cta_lo(Tt, n, m.counter), rem = (r * m.counter) % n;
-      int cnt = 0, part = 0, rank = 0;
-#pragma unroll 1
-      for (int i = m.counter; i < n && lo < end; ++i) {
-        int64_t nlo = lo + q;
-        rem += r;
-        if (rem >= n) { rem -= n; ++nlo; }
-        if (nlo > lo) {  // a non-empty range
-          const bool first_seg = lo >= m.start;
-          if (cnt < kMaxCombineSlots) list_s[cnt] = slot_of(i, first_seg);
-          ++cnt;
-          if (first_seg) {  // this writer takes part in the merge
-            if (i == int(blockIdx.x)) rank = part;
-            ++part;
-          }
+      bool writer = false, merger = false;
+      if (tid < n && tid >= m.counter) {
+        int64_t lo, nlo;
+        if (Tt * n < (int64_t(1) << 32)) {  // the usual case: 32-bit division
+          lo = int64_t(uint32_t(Tt) * uint32_t(tid) / uint32_t(n));
+          nlo = int64_t(uint32_t(Tt) * uint32_t(tid + 1) / uint32_t(n));
+        } else {
+          lo = cta_lo(Tt, n, tid);
+          nlo = cta_lo(Tt, n, tid + 1);
         }
-        lo = nlo;
+        writer = lo < end && nlo > lo;
+        merger = writer && lo >= m.start;
       }
-      const int ns = min(cnt, kMaxCombineSlots);
-      misc->n_slots = ns;
-      misc->n_part = part;
-      misc->rank = rank;
-      bool ok = false;  // bounded wait for the other writers
+      const uint32_t bw = __ballot_sync(0xffffffffu, writer), bm = __ballot_sync(0xffffffffu, merger);
+      int* wcount = reinterpret_cast<int*>(scale_s);  // [12][2]; the slot scales are written two barriers later
+      const int warp = tid >> 5;
+      if ((tid & 31) == 0) {
+        wcount[2 * warp] = __popc(bw);
+        wcount[2 * warp + 1] = __popc(bm);
+      }
+      __syncthreads();
+      int before_w = 0, before_m = 0, cnt = 0, part = 0;
+#pragma unroll
+      for (int w = 0; w < kThreads / 32; ++w) {
+        const int cw = wcount[2 * w], cm = wcount[2 * w + 1];
+        if (w < warp) { before_w += cw; before_m += cm; }
+        cnt += cw;
+        part += cm;
+      }
+      const uint32_t below = (1u << (tid & 31)) - 1u;
+      if (writer) {
+        const int pos = before_w + __popc(bw & below);
+        if (pos < kMaxCombineSlots) list_s[pos] = slot_of(tid, merger);
+      }
+      if (tid == int(blockIdx.x)) misc->rank = merger ? before_m + __popc(bm & below) : 0;
+      if (tid == 0) {
+        const int ns = min(cnt, kMaxCombineSlots);
+        MLA_TRACE(3, 1u, 1);
+        misc->n_slots = ns;
+        misc->n_part = part;
+        bool ok = false;  // bounded wait for the other writers
 #pragma unroll 1
-      for (uint32_t i = 0; i < (1u << 22); ++i) {
-        if (ld_acquire(arrived) >= ns) { ok = true; break; }
-        if (misc->abort) break;
-        __nanosleep(32);
+        for (uint32_t i = 0; i < (1u << 22); ++i) {
+          if (ld_acquire(arrived) >= ns) { ok = true; break; }
+          if (misc->abort) break;
+          __nanosleep(32);
+        }
+        if (!ok && !misc->abort) flag_timeout(c, 100 + k, uint32_t(ns));
       }
-      if (!ok && !misc->abort) flag_timeout(c, 100 + k, uint32_t(ns));
     }
     __syncthreads();
     const int ns = misc->n_slots, np = misc->n_part, rank = misc->rank;
@@ -949,54 +981,79 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
       const int heads_here = min(kGroupHeads, p.num_heads - head0);
       const size_t row0 = (size_t(m.b) * p.q_len + qpos) * p.num_heads + head0;
       // This CTA's dims: pairs [256*rank/np, 256*(rank+1)/np).  A unit is (pair of dims, 8 heads, slot
-      // lane); the SL lanes of a unit are consecutive lanes of a warp, split the slots (four per batch,
+      // lane); the SL lanes of a unit are consecutive lanes of a warp, split the slots (eight per batch,
       // all their loads in flight together) and add their sums with a fixed shuffle tree
       // (bit-reproducible).  Lane 0 of the unit writes 8 x 2 outputs.
-      const int u0 = (256 * rank) / np, u1 = (256 * (rank + 1)) / np;
+      // (integer quotients through float: the operands are small and never within 1/300 of a boundary)
+      const float rnp = 1.0f / float(np);
+      const int u0 = int((float(256 * rank) + 0.5f) * rnp), u1 = int((float(256 * (rank + 1)) + 0.5f) * rnp);
       const int d0 = 2 * u0, pairs = u1 - u0;
-      const int items = pairs * 8;
+      const int og = (heads_here + 7) >> 3;  // 8-head groups that hold heads of this launch
+      const float rog = 1.0f / float(og);
+      const int items = pairs * og;
+      constexpr int kBatch = 8;  // slots whose rows a unit lane has in flight together
       int SL = 1, lg = 0;
-      while (SL < 32 && 4 * SL < ns && items * SL * 2 <= kThreads) { SL *= 2; ++lg; }  // one round of threads if possible
+      while (SL < 32 && kBatch * SL < ns && items * SL * 2 <= kThreads) { SL *= 2; ++lg; }  // one round of threads if possible
       const int units = items << lg;
       const char* slot0 = reinterpret_cast<const char*>(slot_o(ws, 0));
-      auto load_batch = [&](const char* src, bool live_unit, int i0, uint4 (&a)[4][2]) {
+      auto load_batch = [&](const char* src, bool live_unit, int i0, uint4 (&a)[kBatch][2]) {
 #pragma unroll
-        for (int qq = 0; qq < 4; ++qq) {
-          const bool ld = live_unit && i0 + qq * SL < ns;  // no load for a slot that does not exist
-          const char* sp = src + size_t(list_s[min(i0 + qq * SL, ns - 1)]) * kSlotBytes;
-          a[qq][0] = ld ? __ldcg(reinterpret_cast<const uint4*>(sp)) : make_uint4(0u, 0u, 0u, 0u);
-          a[qq][1] = ld ? __ldcg(reinterpret_cast<const uint4*>(sp + kGroupHeads * 2)) : make_uint4(0u, 0u, 0u, 0u);
+        for (int qq = 0; qq < kBatch; ++qq) {
+          const bool ld = live_unit && i0 + qq * SL < ns;  // no load for a slot that does not exist (its list entry is stale)
+          const char* sp = src + size_t(list_s[i0 + qq * SL]) * kSlotBytes;
+          ldcg_v4_if(a[qq][0], sp, ld);
+          ldcg_v4_if(a[qq][1], sp + kGroupHeads * 2, ld);
         }
       };
-      // The first batch of partial rows does not depend on the weights: its loads go out together with the
-      // LSE loads, one round of latency instead of two.
-      uint4 a[4][2];
+      // LSEs and slot scales: four lanes per head split the slots; a lane has eight slots' loads in flight
+      // together (one round of latency for up to 32 slots).  They go out first: the weights are computed
+      // while the partial rows, requested right behind them, are still on their way.
+      const bool wlane = tid < 4 * kGroupHeads;
+      const int wh = tid >> 2, wj = tid & 3;
+      float v[8], sc[8];
+      auto load_lse = [&](int i0) {
+#pragma unroll
+        for (int qq = 0; qq < 8; ++qq) {
+          const int i = i0 + 4 * qq;
+          const float* src = slot_lse(ws, list_s[i]);
+          ldcg_f32_if(v[qq], src + wh, i < ns);
+          ldcg_f32_if(sc[qq], src + kGroupHeads, i < ns);  // element 64 is the slot scale
+        }
+      };
+      if (wlane) load_lse(wj);
+      // The first batch of partial rows does not depend on the weights: its loads go out in the same round.
+      uint4 a[kBatch][2];
       const int base0 = tid & ~31;
       if (base0 < units) {
         const int unit = tid;
         const int item = min(unit, units - 1) >> lg, sl = unit & (SL - 1);
-        load_batch(slot0 + (size_t(d0 + 2 * (item >> 3)) * kGroupHeads + 8 * (item & 7)) * 2, unit < units, sl, a);
+        const int pr = int((float(item) + 0.5f) * rog), o = item - pr * og;
+        load_batch(slot0 + (size_t(d0 + 2 * pr) * kGroupHeads + 8 * o) * 2, unit < units, sl, a);
       }
-      // one round of independent loads: every LSE and every slot scale of the request
-#pragma unroll 1
-      for (int idx = tid; idx < ns * (kGroupHeads + 1); idx += kThreads) {
-        const int i = idx / (kGroupHeads + 1), h = idx - i * (kGroupHeads + 1);
-        const float v = __ldcg(slot_lse(ws, list_s[i]) + h);  // element 64 is the slot scale
-        if (h < kGroupHeads) lse_s[i * kTailLseStride + h] = v;
-        else scale_s[i] = v;
-      }
-      __syncthreads();
+      // A weight lane keeps the running maximum and leaves the values in shared memory for its own second
+      // pass; butterflies give all four lanes of a head the results.
       if (tid == 0) MLA_TRACE(3, 1u, 3);
-      if (tid < 4 * kGroupHeads) {  // four lanes per head split the slots; butterflies give all of them the result
-        const int h = tid >> 2, j = tid & 3;
+      if (wlane) {
+        const int h = wh, j = wj;
         float* col = lse_s + h;
         float mx = -INFINITY;
 #pragma unroll 1
-        for (int i = j; i < ns; i += 4) mx = fmaxf(mx, col[i * kTailLseStride]);
+        for (int i0 = j; i0 < ns; i0 += 32) {
+          if (i0 != j) load_lse(i0);
+#pragma unroll
+          for (int qq = 0; qq < 8; ++qq) {
+            const int i = i0 + 4 * qq;
+            if (i < ns) {
+              col[i * kTailLseStride] = v[qq];
+              scale_s[i] = sc[qq];  // every head's lane writes the same value; a lane reads back only what it wrote
+              mx = fmaxf(mx, v[qq]);
+            }
+          }
+        }
 #pragma unroll
         for (int off = 2; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
         float dsum = 0.f;
-#pragma unroll 1
+#pragma unroll 4
         for (int i = j; i < ns; i += 4) {
           const float l = col[i * kTailLseStride];
           const float e = (l == -INFINITY) ? 0.f : ptx::ex2(l - mx);
@@ -1006,7 +1063,7 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
 #pragma unroll
         for (int off = 2; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
         const float inv = dsum > 0.f ? __frcp_rn(dsum) : 0.f;
-#pragma unroll 1
+#pragma unroll 4
         for (int i = j; i < ns; i += 4) col[i * kTailLseStride] *= inv * scale_s[i];  // weights, times the slot's fp16 scale
         if (j == 0 && rank == 0 && p.lse && h < heads_here) p.lse[row0 + h] = (dsum > 0.f) ? (__log2f(dsum) + mx) : -INFINITY;
       }
@@ -1017,19 +1074,20 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
         const int unit = base + (tid & 31);
         const bool live_unit = unit < units;
         const int item = min(unit, units - 1) >> lg, sl = unit & (SL - 1);
-        const int o = item & 7, pr = item >> 3;
+        const int pr = int((float(item) + 0.5f) * rog), o = item - pr * og;
         const char* src = slot0 + (size_t(d0 + 2 * pr) * kGroupHeads + 8 * o) * 2;
         const float* wrow = lse_s + 8 * o;
         float acc[2][8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[0][e] = acc[1][e] = 0.f;
 #pragma unroll 1
-        for (int i0 = sl; i0 < ns; i0 += 4 * SL) {  // four slots x two dims: eight independent 16-byte loads in flight
+        for (int i0 = sl; i0 < ns; i0 += kBatch * SL) {  // eight slots x two dims: sixteen independent 16-byte loads in flight
           if (!(base == base0 && i0 == sl)) load_batch(src, live_unit, i0, a);  // the first batch is already here
 #pragma unroll
-          for (int qq = 0; qq < 4; ++qq) {
+          for (int qq = 0; qq < kBatch; ++qq) {
             const int i = i0 + qq * SL;
-            const float* w = wrow + min(i, ns - 1) * kTailLseStride;  // data of a missing slot is zero
+            if (i >= ns) break;  // the remaining slots of the batch do not exist
+            const float* w = wrow + i * kTailLseStride;
             const float4 w0 = *reinterpret_cast<const float4*>(w), w1 = *reinterpret_cast<const float4*>(w + 4);
             const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
