@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout and the installed flashinfer wheel:
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <path of the reference checkout>
 
 Two fixtures are written (small .npz files, committed):
 
@@ -40,7 +40,7 @@ def load_reference_builder(ref_root: Path):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     args = ap.parse_args()
     builder = load_reference_builder(Path(args.reference))
 
