@@ -636,42 +636,46 @@ __device__ __noinline__ void write_output(const DecodeParams& p, const Ctx& c, u
   const size_t row0 = (size_t(b) * p.q_len + qpos) * p.num_heads + head0;
   const bool direct = slot < 0;
   __half* so = reinterpret_cast<__half*>(slot_o(p.workspace, direct ? 0 : slot));
-  const float inv_slot_scale = 1.f / slot_scale_v;
-  const uint32_t linv = c.smem + kOffLinv;
+  // output_scale / l of this thread's 32 heads (times 1 / slot scale for a partial), read once
+  const float post = direct ? 1.f : 1.f / slot_scale_v;
+  float li[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) li[i] = lds_f32(c.smem + kOffLinv + 4 * (32 * half + i)) * post;
 #pragma unroll 1
-  for (int jc = 0; jc < kBlocks * 2; ++jc) {
-    uint32_t o[16];
-    const int h0 = 32 * half + 16 * (jc & 1);
-    ptx::tmem_ld16(tmem_lane + kColO + 64u * (jc >> 1) + uint32_t(h0), o);
+  for (int jb = 0; jb < kBlocks; ++jb) {
+    uint32_t o[2][16];  // both 16-head halves of the block in flight before one wait
+    ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(jb) + uint32_t(32 * half), o[0]);
+    ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(jb) + uint32_t(32 * half + 16), o[1]);
     ptx::tmem_wait_ld();
-    const int dim = 128 * (jc >> 1) + row;
-    float v[16];
+    const int dim = 128 * jb + row;
+    const int h0 = 32 * half;
+    float v[32];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(o[i]) * lds_f32(linv + 4 * (h0 + i));
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i >> 4][i & 15]) * li[i];
     if (!direct) {
-      uint32_t pk[8];
+      uint32_t pk[16];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        __half2 h2 = __floats2half2_rn(v[2 * q] * inv_slot_scale, v[2 * q + 1] * inv_slot_scale);
+      for (int q = 0; q < 16; ++q) {
+        __half2 h2 = __floats2half2_rn(v[2 * q], v[2 * q + 1]);
         pk[q] = *reinterpret_cast<uint32_t*>(&h2);
       }
       uint4* dst = reinterpret_cast<uint4*>(so + size_t(dim) * kGroupHeads + h0);
-      dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-      dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) dst[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
     } else if (p.out_dtype == MLA_FP4_OUT_BF16) {
       __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (row0 + h0) * kLatent + dim;
 #pragma unroll
-      for (int i = 0; i < 16; ++i)
+      for (int i = 0; i < 32; ++i)
         if (h0 + i < heads_here) dst[size_t(i) * kLatent] = __float2bfloat16_rn(v[i]);
     } else if (p.out_dtype == MLA_FP4_OUT_F32) {
       float* dst = reinterpret_cast<float*>(p.out) + (row0 + h0) * kLatent + dim;
 #pragma unroll
-      for (int i = 0; i < 16; ++i)
+      for (int i = 0; i < 32; ++i)
         if (h0 + i < heads_here) dst[size_t(i) * kLatent] = v[i];
     } else {
       uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + (row0 + h0) * kLatent + dim;
 #pragma unroll
-      for (int i = 0; i < 16; ++i)
+      for (int i = 0; i < 32; ++i)
         if (h0 + i < heads_here) dst[size_t(i) * kLatent] = __nv_cvt_float_to_fp8(v[i], __NV_SATFINITE, __NV_E4M3);
     }
   }
@@ -699,6 +703,7 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
   t.cs2 = pack2(cscale, cscale);
   t.psw = (uint32_t(row) >> 1) & 3u;
   t.half = uint32_t(half);
+  int pending0 = 0, pending1 = 0, n_pending = 0;  // counters of the partials written in this call, published together at its end
 
 #pragma unroll 1
   for (int si = 0; si < nseg; ++si, ++st.seg) {
@@ -798,15 +803,27 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       if (!c.misc->abort) write_output(p, c, tmem_lane, row, half, tid, g.b, g.g, g.slot, slot_scale_v);
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar_addr(c, kBarOFree));
-      if (g.slot >= 0) {
-        if (p.fused_merge) {  // publish the partial: the tail merge of the request's CTAs waits for this count
-          __threadfence();
-          ptx::bar_sync(1, kSoftmaxThreads);
-          if (tid == 0) atomicAdd(ws_arrived(p.workspace) + c.misc->merge[st.part].counter, 1);
+      if (g.slot >= 0) {  // a partial: published (below) once this CTA has written all its partials of the round
+        if (p.fused_merge && n_pending < 2) {
+          const int counter = c.misc->merge[st.part].counter;
+          if (n_pending == 0) pending0 = counter;
+          else pending1 = counter;
+          ++n_pending;
         }
         ++st.part;
       }
       if (tid == 0) MLA_TRACE(0, lit, 6);
+    }
+  }
+  // Publish the partials: the tail merge of their requests' CTAs waits for these counts.  One fence for
+  // all of them, after the last segment: a fence in the middle would hold up the next segment's first tile,
+  // and nobody can use a partial before this CTA, itself a writer of the later request, is done anyway.
+  if (n_pending > 0) {
+    __threadfence();
+    ptx::bar_sync(1, kSoftmaxThreads);
+    if (tid == 0) {
+      atomicAdd(ws_arrived(p.workspace) + pending0, 1);
+      if (n_pending > 1) atomicAdd(ws_arrived(p.workspace) + pending1, 1);
     }
   }
 }
