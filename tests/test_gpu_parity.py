@@ -90,6 +90,36 @@ def test_heads_and_page_sizes(heads, page_size, kernel):
     check_case(synth.build_case("hp", [700, 129, 64, 2500], heads, page_size, seed=heads + page_size, device=_dev()), kernel)
 
 
+@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_2pass"])
+def test_many_short_requests_on_few_ctas(kernel):
+    """More segments per CTA than one staging round holds (48): 300 requests of 1-3 tiles on 4 CTAs, with
+    empty requests in between and requests cut at every CTA boundary (their partials are published at the
+    end of the role and merged in the tail)."""
+    from flashinfer_mla_fp4_b200 import BatchMLADecodeCuteDSLFP4Wrapper, synth
+
+    g = torch.Generator().manual_seed(77)
+    lens = torch.randint(1, 330, (300,), generator=g).tolist()
+    for i in range(0, 300, 37):
+        lens[i] = 0
+    case = synth.build_case("many_short", [max(n, 1) for n in lens], 16, 16, seed=78, device=_dev())
+    case.seq_lens = torch.tensor(lens, dtype=torch.int32, device=case.q.device)
+    case.seq_lens_host = lens
+    w = BatchMLADecodeCuteDSLFP4Wrapper(torch.empty(64 << 20, dtype=torch.int8, device=case.q.device))
+    w.plan(num_heads=case.num_heads, page_size=case.page_size)
+    w._kernel = KERNELS[kernel]
+    w._num_ctas = 4
+    out, lse = w.run(case.q, case.kv_cache, case.block_tables, case.seq_lens, case.max_seq_len, case.softmax_scale,
+                     kv_cache_sf=case.kv_cache_sf, return_lse=True)
+    torch.cuda.synchronize()
+    w.check_device_status()
+    ref, ref_lse = O.mla_decode(case.q, case.kv_cache, case.kv_cache_sf, case.block_tables, case.seq_lens, case.softmax_scale)
+    O.assert_parity(out, ref, f"many_short/{kernel}")
+    live = torch.isfinite(ref_lse)
+    torch.testing.assert_close(lse.cpu()[live], ref_lse[live], atol=2e-3, rtol=1e-4)
+    assert (lse.cpu()[~live] == float("-inf")).all()
+    assert not out[~live.view(300, -1)[:, 0]].float().any()
+
+
 @pytest.mark.parametrize("kernel", ["fp32_check", "tcgen05", "tcgen05_2pass"])
 def test_ragged_batch_with_empty_requests(kernel):
     from flashinfer_mla_fp4_b200 import synth
