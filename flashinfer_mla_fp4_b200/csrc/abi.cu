@@ -57,7 +57,7 @@ int mla_fp4_plan_partition(const int32_t* seq_lens_host, int32_t batch, int32_t 
     return fail(MLA_FP4_ERR_BAD_ARG, "batch/q_len/num_heads/num_ctas out of range");
   const int groups = mla::num_groups(q_len, num_heads);
   int64_t T = 0;
-  for (int b = 0; b < batch; ++b) T += mla::tiles_of(seq_lens_host[b]);
+  for (int b = 0; b < batch; ++b) T += mla::vtiles_of(seq_lens_host[b]);
   const int64_t Tt = T * groups;
   int count = 0;
   for (int i = 0; i < num_ctas; ++i) {
@@ -70,7 +70,7 @@ int mla_fp4_plan_partition(const int32_t* seq_lens_host, int32_t batch, int32_t 
       w.g = int(w.f / T);
       int64_t r = w.f % T, run = 0;
       for (int b = 0; b < batch; ++b) {
-        int tb = mla::tiles_of(seq_lens_host[b]);
+        int tb = mla::vtiles_of(seq_lens_host[b]);
         if (r < run + tb) { w.b = b; w.t = int(r - run); break; }
         run += tb;
       }

@@ -34,14 +34,14 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
   if (tid < 32) {  // seq_lens is an input of the step, not a product of the decode kernel
     int64_t T = warp_total_tiles(p.seq_lens, p.batch);
     int64_t run = 0;
-    for (int i = tid; i < b; i += 32) run += tiles_of(p.seq_lens[i]);
+    for (int i = tid; i < b; i += 32) run += vtiles_of(p.seq_lens[i]);
     for (int o = 16; o > 0; o >>= 1) run += __shfl_xor_sync(0xffffffffu, run, o);
     if (tid == 0) { s_T = T; s_start = run; }
   }
   __syncthreads();
   const int64_t T = s_T;
   const int64_t Tt = T * p.groups;
-  const int tiles = tiles_of(p.seq_lens[b]);
+  const int tiles = vtiles_of(p.seq_lens[b]);  // of the flat space: phantom tiles included
   int qpos, head0;
   group_coords(g, p.num_heads, qpos, head0);
   const int heads_here = min(kGroupHeads, p.num_heads - head0);
@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
     return;
   }
   const int64_t start = int64_t(g) * T + s_start;
-  const Span sp = span_of(Tt, p.num_ctas, start, tiles);
+  const Span sp = span_of(Tt, p.num_ctas, start + kPhantom, tiles - kPhantom);  // CTAs that hold its real tiles
   if (!sp.split) return;  // the decode kernel wrote the final output itself
 
   // slots of this request, computed once (the partition arithmetic is 64-bit division heavy)
@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
     int n = 0;
     for (int base = sp.cta_first; base <= sp.cta_last; base += 32) {
       const int i = base + tid;
-      const bool live = i <= sp.cta_last && !cta_is_empty(Tt, p.num_ctas, i);
+      const bool live = i <= sp.cta_last && cta_writes(Tt, p.num_ctas, i, start, tiles);
       const unsigned m = __ballot_sync(0xffffffffu, live);
       if (live) {
         const int pos = n + __popc(m & ((1u << tid) - 1u));

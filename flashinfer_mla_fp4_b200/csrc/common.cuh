@@ -66,6 +66,13 @@ MLA_HD int out_elem_bytes(int out_dtype) { return out_dtype == MLA_FP4_OUT_F32 ?
 
 MLA_HD int tiles_of(int seq_len) { return seq_len > 0 ? (seq_len + kTile - 1) / kTile : 0; }
 
+// The flat space that is cut into CTA ranges counts kPhantom extra tiles in front of every non-empty
+// request: moving on to another request costs a CTA about as much as a tile (the epilogue of the old
+// one, a fresh query, a cold pipeline), so a CTA whose range holds the start of a request gets that
+// many tiles less.  A piece of a range that holds nothing but phantom tiles is no segment.
+constexpr int kPhantom = 1;
+MLA_HD int vtiles_of(int seq_len) { return seq_len > 0 ? tiles_of(seq_len) + kPhantom : 0; }
+
 MLA_HD int num_groups(int q_len, int num_heads) {
   return q_len * ((num_heads + kGroupHeads - 1) / kGroupHeads);
 }
@@ -77,8 +84,13 @@ MLA_HD int cta_of_tile(int64_t Tt, int n, int64_t f) {
   return int(((f + 1) * n + Tt - 1) / Tt) - 1;
 }
 
-// A CTA whose flat range is empty (more CTAs than tiles) has no segment and writes no slot.
-MLA_HD bool cta_is_empty(int64_t Tt, int n, int i) { return cta_lo(Tt, n, i) == cta_lo(Tt, n, i + 1); }
+// Does CTA i write a partial of the split request whose flat range (phantom tiles first) is
+// [start, start + vtiles)?  Its range must hold at least one of the request's real tiles.
+MLA_HD bool cta_writes(int64_t Tt, int n, int i, int64_t start, int vtiles) {
+  const int64_t lo = cta_lo(Tt, n, i), hi = cta_lo(Tt, n, i + 1);
+  const int64_t a = lo > start + kPhantom ? lo : start + kPhantom, b = hi < start + vtiles ? hi : start + vtiles;
+  return a < b;
+}
 
 MLA_HD int slot_of(int cta, bool first_segment_of_cta) { return 2 * cta + (first_segment_of_cta ? 0 : 1); }
 
@@ -122,7 +134,7 @@ struct Walker {
     while (f < hi) {
       if (g >= groups) return false;
       int sl = seq_lens[b];
-      int tb = tiles_of(sl);
+      int tb = vtiles_of(sl);  // t, end, room and f count phantom tiles; the segment holds real ones
       if (t >= tb) {
         t = 0;
         if (++b == batch) { b = 0; ++g; }
@@ -130,10 +142,13 @@ struct Walker {
       }
       int64_t room = hi - f;
       int end = (tb - t) <= room ? tb : t + int(room);
-      s.b = b; s.g = g; s.tile_begin = t; s.tile_end = end; s.seq_len = sl;
-      s.slot = (t == 0 && end == tb) ? -1 : slot_of(cta, first);
+      const bool whole = t <= kPhantom && end == tb;  // all real tiles of the request
+      const int real_begin = (t > kPhantom ? t : kPhantom) - kPhantom, real_end = end - kPhantom;
       f += end - t;
       t = end;
+      if (real_end <= real_begin) continue;  // nothing but phantom tiles
+      s.b = b; s.g = g; s.tile_begin = real_begin; s.tile_end = real_end; s.seq_len = sl;
+      s.slot = whole ? -1 : slot_of(cta, first);
       first = false;
       return true;
     }
@@ -153,7 +168,7 @@ MLA_HD void group_coords(int g, int num_heads, int& qpos, int& head0) {
 __device__ __forceinline__ int64_t warp_total_tiles(const int32_t* seq_lens, int batch) {
   int lane = threadIdx.x & 31;
   int64_t acc = 0;
-  for (int i = lane; i < batch; i += 32) acc += tiles_of(seq_lens[i]);
+  for (int i = lane; i < batch; i += 32) acc += vtiles_of(seq_lens[i]);
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   return acc;
 }
@@ -165,7 +180,7 @@ __device__ __forceinline__ void warp_locate(const int32_t* seq_lens, int batch, 
   b_out = batch; t_out = 0;
   for (int base = 0; base < batch; base += 32) {
     int i = base + lane;
-    int64_t v = i < batch ? tiles_of(seq_lens[i]) : 0;
+    int64_t v = i < batch ? vtiles_of(seq_lens[i]) : 0;
     int64_t inc = v;
     for (int o = 1; o < 32; o <<= 1) {
       int64_t u = __shfl_up_sync(0xffffffffu, inc, o);

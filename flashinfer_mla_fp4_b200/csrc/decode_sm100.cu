@@ -842,8 +842,8 @@ __device__ __noinline__ void stage_segments(const Ctx& c) {
       MergeReq& m = c.misc->merge[c.misc->n_merge++];
       m.b = s.b;
       m.g = s.g;
-      m.tiles = tiles_of(s.seq_len);
-      m.start = w.f - int64_t(s.tile_end);  // w.f is the flat index just past this segment
+      m.tiles = vtiles_of(s.seq_len);       // of the flat space: phantom tiles included
+      m.start = w.f - int64_t(w.t);         // w.f and w.t are the flat and the in-request position just past this segment
       m.counter = cta_of_tile(w.Tt, int(gridDim.x), m.start);
       m.slot = s.slot;
     }
@@ -949,7 +949,7 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
           lo = cta_lo(Tt, n, tid);
           nlo = cta_lo(Tt, n, tid + 1);
         }
-        writer = lo < end && nlo > lo;
+        writer = lo < end && nlo > lo && nlo > m.start + kPhantom;  // holds at least one real tile of the request
         merger = writer && lo >= m.start;
       }
       const uint32_t bw = __ballot_sync(0xffffffffu, writer), bm = __ballot_sync(0xffffffffu, merger);

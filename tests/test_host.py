@@ -72,9 +72,15 @@ def test_partition_is_a_partition(seq_lens, q_len, heads, ctas):
         assert (s.slot == -1) == whole
     total = groups * sum(planner.tiles_of(n) for n in seq_lens)
     assert len(covered) == total
-    # balance: CTA loads differ by at most one tile
-    loads = [sum(s.tile_end - s.tile_begin for s in per_cta.get(i, [])) for i in range(ctas)]
-    assert max(loads) - min(loads) <= 1
+    # balance: the flat space that is cut evenly counts one extra (phantom) tile in front of every non-empty
+    # request, so a CTA's tiles plus the request starts it holds stay within one of the even share
+    flat = groups * sum(planner.tiles_of(n) + 1 for n in seq_lens if n > 0)
+    for i in range(ctas):
+        ss = per_cta.get(i, [])
+        real = sum(s.tile_end - s.tile_begin for s in ss)
+        starts = sum(1 for s in ss if s.tile_begin == 0)  # the phantom of one of them may lie in the CTA before
+        assert real <= -(-flat // ctas), (i, real, flat, ctas)
+        assert flat // ctas - 1 <= real + starts <= -(-flat // ctas) + 1, (i, real, starts, flat, ctas)
     # partial slots: unique, at most two per CTA, only at the ends of a CTA's walk
     slots = [s.slot for s in segs if s.slot >= 0]
     assert len(slots) == len(set(slots))
