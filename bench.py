@@ -44,7 +44,7 @@ PUBLISHED_US = {"northstar": 37.726, "uniform": 13.461}  # reference README, one
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel, from the ncu capture summarised in
 # profiles/decode_sm100_northstar_ncu_full.md (87.26 MB read + 15.18 MB written); None where no capture exists.
-NCU_TRAFFIC_BYTES = {("northstar", "fused"): 100.3e6}
+NCU_TRAFFIC_BYTES = {("northstar", "fused"): 100.8e6}
 
 
 def peaks():

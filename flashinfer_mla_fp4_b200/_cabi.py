@@ -32,6 +32,7 @@ OUT_E4M3 = 2
 
 TILE_TOKENS = 128
 GROUP_HEADS = 64
+PHANTOM_TILES = 2  # MLA_FP4_PHANTOM_TILES: tiles the work partition charges for a request's start
 
 
 class DecodeArgs(C.Structure):

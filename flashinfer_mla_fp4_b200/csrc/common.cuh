@@ -67,10 +67,10 @@ MLA_HD int out_elem_bytes(int out_dtype) { return out_dtype == MLA_FP4_OUT_F32 ?
 MLA_HD int tiles_of(int seq_len) { return seq_len > 0 ? (seq_len + kTile - 1) / kTile : 0; }
 
 // The flat space that is cut into CTA ranges counts kPhantom extra tiles in front of every non-empty
-// request: moving on to another request costs a CTA about as much as a tile (the epilogue of the old
-// one, a fresh query, a cold pipeline), so a CTA whose range holds the start of a request gets that
-// many tiles less.  A piece of a range that holds nothing but phantom tiles is no segment.
-constexpr int kPhantom = 1;
+// request: moving on to another request costs a CTA about as much as two tiles (the epilogue of the
+// old one, a fresh query, a cold pipeline), so a CTA whose range holds the start of a request gets
+// that many tiles less.  A piece of a range that holds nothing but phantom tiles is no segment.
+constexpr int kPhantom = MLA_FP4_PHANTOM_TILES;  // measured: 2 and 3 are equally good, 1 and 4 worse
 MLA_HD int vtiles_of(int seq_len) { return seq_len > 0 ? tiles_of(seq_len) + kPhantom : 0; }
 
 MLA_HD int num_groups(int q_len, int num_heads) {

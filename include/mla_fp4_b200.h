@@ -37,6 +37,9 @@ extern "C" {
 #define MLA_FP4_ROW_BYTES 320
 #define MLA_FP4_TILE_TOKENS 128          /* KV tokens per work tile                            */
 #define MLA_FP4_GROUP_HEADS 64           /* query heads handled by one CTA                     */
+#ifndef MLA_FP4_PHANTOM_TILES
+#define MLA_FP4_PHANTOM_TILES 2          /* tiles the work partition charges for a request's start */
+#endif
 
 /* kernel selection for mla_fp4_decode */
 #define MLA_FP4_KERNEL_TCGEN05 0         /* the product path: TMA + tcgen05/TMEM, one kernel that

@@ -72,15 +72,18 @@ def test_partition_is_a_partition(seq_lens, q_len, heads, ctas):
         assert (s.slot == -1) == whole
     total = groups * sum(planner.tiles_of(n) for n in seq_lens)
     assert len(covered) == total
-    # balance: the flat space that is cut evenly counts one extra (phantom) tile in front of every non-empty
-    # request, so a CTA's tiles plus the request starts it holds stay within one of the even share
-    flat = groups * sum(planner.tiles_of(n) + 1 for n in seq_lens if n > 0)
+    # balance: the flat space that is cut evenly counts P extra (phantom) tiles in front of every non-empty
+    # request, so a CTA's tiles plus P per request start it holds stay close to the even share
+    from flashinfer_mla_fp4_b200 import _cabi
+
+    P = _cabi.PHANTOM_TILES
+    flat = groups * sum(planner.tiles_of(n) + P for n in seq_lens if n > 0)
     for i in range(ctas):
         ss = per_cta.get(i, [])
         real = sum(s.tile_end - s.tile_begin for s in ss)
         starts = sum(1 for s in ss if s.tile_begin == 0)  # the phantom of one of them may lie in the CTA before
         assert real <= -(-flat // ctas), (i, real, flat, ctas)
-        assert flat // ctas - 1 <= real + starts <= -(-flat // ctas) + 1, (i, real, starts, flat, ctas)
+        assert flat // ctas - P <= real + P * starts <= -(-flat // ctas) + P, (i, real, starts, flat, ctas)
     # partial slots: unique, at most two per CTA, only at the ends of a CTA's walk
     slots = [s.slot for s in segs if s.slot >= 0]
     assert len(slots) == len(set(slots))
@@ -177,3 +180,14 @@ def test_wrapper_run_validation(monkeypatch):
     small.__dict__.update({k: v for k, v in w.__dict__.items() if k != "_workspace_buffer"})
     with pytest.raises(ValueError, match="are required"):
         small.run(**ok)
+
+
+def test_partition_charges_phantom_tiles_for_a_request_start():
+    """One request of 10 tiles on 10 + P CTAs: the first P CTAs get the phantom tiles and no segment."""
+    from flashinfer_mla_fp4_b200 import _cabi, planner
+
+    P = _cabi.PHANTOM_TILES
+    segs = planner.plan_partition([1280], 1, 64, 10 + P)
+    assert [s.cta for s in segs] == list(range(P, 10 + P))
+    assert [(s.tile_begin, s.tile_end) for s in segs] == [(t, t + 1) for t in range(10)]
+    assert segs[0].slot == 2 * P and all(s.slot == 2 * s.cta for s in segs)
