@@ -6,7 +6,8 @@ wrappers/batch_mla_fp4.py:189, :320), which logs calls under ``FLASHINFER_LOGLEV
 
 * ``MLA_FP4_LOGLEVEL``  0 off (default), 1 function names, 3 + every argument's metadata (tensors:
   shape, dtype, device, strides, data pointer; scalars: value), 5 + tensor statistics (min, max,
-  mean, NaN and Inf counts; this level synchronises and is skipped while a stream is capturing);
+  mean, NaN and Inf counts; this level synchronises, is skipped while a stream is capturing and for
+  tensors of more than 16 M elements);
 * ``MLA_FP4_LOGDEST``   ``stdout`` (default), ``stderr`` or a file path (``%i`` becomes the process id);
 * ``MLA_FP4_NVTX``      ``1`` wraps every call in an NVTX range named after the function.
 
@@ -23,6 +24,9 @@ import time
 from typing import Any, Callable, Optional, TextIO
 
 import torch
+
+
+_STATS_MAX_ELEMENTS = 1 << 24  # level 5 converts a tensor to FP32 for its statistics: not for a whole cache pool
 
 
 class _State:
@@ -64,7 +68,9 @@ def _describe(v: Any, stats: bool) -> str:
     if isinstance(v, torch.Tensor):
         s = (f"Tensor(shape={tuple(v.shape)}, dtype={v.dtype}, device={v.device}, stride={tuple(v.stride())}, "
              f"ptr=0x{v.data_ptr():x}, contiguous={v.is_contiguous()}")
-        if stats and v.numel() > 0:
+        if stats and v.numel() > _STATS_MAX_ELEMENTS:
+            s += f", statistics skipped ({v.numel()} elements)"
+        elif stats and v.numel() > 0:
             f = v.float() if v.dtype != torch.uint8 else v.to(torch.float32)
             finite = f[torch.isfinite(f)]
             s += (f", min={finite.min().item() if finite.numel() else float('nan'):.6g}"
