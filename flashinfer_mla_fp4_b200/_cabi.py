@@ -11,7 +11,7 @@ from pathlib import Path
 
 # MLA_FP4_B200_LIB overrides the library location (for instance a debug build)
 LIB_PATH = Path(os.environ.get("MLA_FP4_B200_LIB") or (Path(__file__).resolve().parent / "libmla_fp4_b200.so"))
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 OK = 0
 ERR_BAD_ARG = 1
@@ -58,6 +58,8 @@ class DecodeArgs(C.Structure):
         ("enable_pdl", C.c_int32),
         ("phase_mask", C.c_int32),
         ("stream", C.c_void_p),
+        ("max_pages_per_request", C.c_int32),
+        ("wait_polls", C.c_int32),
     ]
 
 
@@ -72,6 +74,7 @@ EXPORTS = (
     "mla_fp4_dequant_e2m1_to_e4m3",
     "mla_fp4_cache_write",
     "mla_fp4_decode_static",
+    "mla_fp4_static_reset",
 )
 
 
@@ -96,6 +99,8 @@ def _load() -> C.CDLL:
     lib.mla_fp4_decode.restype = C.c_int
     lib.mla_fp4_decode_static.argtypes = [C.POINTER(DecodeArgs)]
     lib.mla_fp4_decode_static.restype = C.c_int
+    lib.mla_fp4_static_reset.argtypes = [C.c_void_p]
+    lib.mla_fp4_static_reset.restype = C.c_int
     lib.mla_fp4_merge_partials.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
                                            C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]
     lib.mla_fp4_merge_partials.restype = C.c_int
@@ -128,7 +133,7 @@ def check(rc: int) -> None:
 
 
 def workspace_init(ptr: int, nbytes: int, stream: int) -> None:
-    """Zero the counter header of a workspace (asynchronous, on `stream`)."""
+    """Zero the header of a workspace (asynchronous, on `stream`)."""
     check(lib.mla_fp4_workspace_init(ptr, nbytes, stream))
 
 

@@ -1,4 +1,6 @@
 // extern "C" boundary of libmla_fp4_b200.so: argument validation, host planner, launches.
+#include <atomic>
+#include <climits>
 #include <cstdio>
 #include <cstring>
 #include <string>
@@ -28,6 +30,14 @@ int sm_count(int* out) {
 
 bool page_size_ok(int ps) { return ps >= 8 && ps <= 128 && (128 % ps) == 0; }
 
+// Zero the header (generation, finished count) and the tails of all slots (their flags): one asynchronous memset.
+int clear_workspace(void* ws, size_t bytes, cudaStream_t stream) {
+  if (bytes < mla::kWsFixedBytes) return fail(MLA_FP4_ERR_WORKSPACE_TOO_SMALL, "workspace is smaller than its header and slot tails");
+  cudaError_t e = cudaMemsetAsync(ws, 0, mla::kWsFixedBytes, stream);
+  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
+  return MLA_FP4_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -43,8 +53,8 @@ int mla_fp4_workspace_bytes(int32_t batch, int32_t q_len, int32_t num_heads, int
     int rc = sm_count(&num_ctas);
     if (rc) return rc;
   }
-  // the counter header, then two partial slots per CTA (its first and its last segment), whatever the batch is
-  *bytes_out = mla::kWsHeaderBytes + size_t(2) * size_t(num_ctas) * mla::kSlotBytes;
+  // the header and the slot tails, then two partial-O slots per CTA (its first and its last segment), whatever the batch is
+  *bytes_out = mla::workspace_bytes_for(num_ctas);
   return MLA_FP4_OK;
 }
 
@@ -62,7 +72,7 @@ int mla_fp4_plan_partition(const int32_t* seq_lens_host, int32_t batch, int32_t 
   int count = 0;
   for (int i = 0; i < num_ctas; ++i) {
     mla::Walker w;
-    w.seq_lens = seq_lens_host; w.batch = batch; w.groups = groups; w.cta = i; w.first = true;
+    w.seq_lens = seq_lens_host; w.cap = INT_MAX; w.batch = batch; w.groups = groups; w.cta = i; w.first = true;
     w.f = mla::cta_lo(Tt, num_ctas, i);
     w.hi = mla::cta_lo(Tt, num_ctas, i + 1);
     w.b = 0; w.g = groups; w.t = 0;
@@ -94,10 +104,7 @@ int mla_fp4_plan_partition(const int32_t* seq_lens_host, int32_t batch, int32_t 
 
 int mla_fp4_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
   if (!workspace) return fail(MLA_FP4_ERR_BAD_ARG, "workspace is null");
-  if (workspace_bytes < mla::kWsHeaderBytes) return fail(MLA_FP4_ERR_WORKSPACE_TOO_SMALL, "workspace is smaller than its header");
-  cudaError_t e = cudaMemsetAsync(workspace, 0, mla::kWsHeaderBytes, reinterpret_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
-  return MLA_FP4_OK;
+  return clear_workspace(workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
@@ -124,7 +131,7 @@ int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
     if (rc) return rc;
   }
   if (num_ctas > mla::kMaxCombineSlots) return fail(MLA_FP4_ERR_UNSUPPORTED, "num_ctas must be <= 148");
-  size_t need = mla::kWsHeaderBytes + size_t(2) * size_t(num_ctas) * mla::kSlotBytes;
+  size_t need = mla::workspace_bytes_for(num_ctas);
   if (!a->workspace || a->workspace_bytes < need) {
     char buf[160];
     snprintf(buf, sizeof buf, "workspace has %zu bytes, but %zu are required", a->workspace ? a->workspace_bytes : size_t(0), need);
@@ -142,6 +149,13 @@ int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
   p.num_pages = a->num_pages;
   p.softmax_scale = a->softmax_scale; p.output_scale = a->output_scale;
   p.out_dtype = a->out_dtype; p.pdl = a->enable_pdl ? 1 : 0;
+  if (a->max_pages_per_request < 0 || a->wait_polls < 0) return fail(MLA_FP4_ERR_BAD_ARG, "max_pages_per_request/wait_polls must not be negative");
+  p.seq_cap = INT_MAX;
+  if (a->max_pages_per_request > 0) {
+    const int64_t cap = int64_t(a->max_pages_per_request) * a->page_size;
+    p.seq_cap = cap < INT_MAX ? int32_t(cap) : INT_MAX;
+  }
+  p.wait_polls = a->wait_polls > 0 ? uint32_t(a->wait_polls) : (1u << 22);
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
 
   cudaError_t e = cudaSuccess;
@@ -167,6 +181,7 @@ int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
   c.seq_lens = a->seq_lens; c.workspace = a->workspace; c.out = a->out; c.lse = a->lse;
   c.batch = a->batch; c.q_len = a->q_len; c.num_heads = a->num_heads; c.groups = p.groups;
   c.num_ctas = num_ctas; c.out_dtype = a->out_dtype; c.pdl = (p.pdl && do_decode) ? 1 : 0;
+  c.seq_cap = p.seq_cap;
   e = mla::launch_combine(c, stream);
   if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("combine launch: ") + cudaGetErrorString(e));
   return MLA_FP4_OK;
@@ -177,9 +192,38 @@ int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
 // Scratch of the allocation-free entry point: the counter header (zero-initialised static storage)
 // and the split-KV partial slots of the largest accepted grid.  On the host this name is only a handle; the device address is looked up per device.
 static __device__ __align__(256) unsigned char g_static_scratch[MLA_FP4_STATIC_SCRATCH_BYTES];
-static_assert(MLA_FP4_STATIC_SCRATCH_BYTES == mla::kWsHeaderBytes + 2 * MLA_FP4_STATIC_MAX_CTAS * mla::kSlotBytes, "static scratch size");
+static_assert(MLA_FP4_STATIC_SCRATCH_BYTES == mla::workspace_bytes_for(MLA_FP4_STATIC_MAX_CTAS), "static scratch size");
+
+namespace {
+// Set-up of the built-in scratch, once per device, with that device current: the device address of the
+// array (the array's name is only a handle on the host).  Two threads racing here both look it up
+// and store the same value.
+int static_scratch_address(int dev, void** out) {
+  static std::atomic<void*> scratch_addr[64];
+  void* ptr = scratch_addr[dev].load(std::memory_order_acquire);
+  if (!ptr) {
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || !ptr)
+      return fail(MLA_FP4_ERR_CUDA, std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(e));
+    scratch_addr[dev].store(ptr, std::memory_order_release);
+  }
+  *out = ptr;
+  return MLA_FP4_OK;
+}
+}  // namespace
 
 extern "C" {
+
+int mla_fp4_static_reset(void* stream) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(MLA_FP4_ERR_UNSUPPORTED, "device ordinal out of range for the static scratch table");
+  void* scratch = nullptr;
+  int rc = static_scratch_address(dev, &scratch);
+  if (rc) return rc;
+  return clear_workspace(scratch, size_t(MLA_FP4_STATIC_SCRATCH_BYTES), reinterpret_cast<cudaStream_t>(stream));
+}
 
 int mla_fp4_decode_static(const MlaFp4DecodeArgs* a) {
   if (!a) return fail(MLA_FP4_ERR_BAD_ARG, "args is null");
@@ -198,17 +242,11 @@ int mla_fp4_decode_static(const MlaFp4DecodeArgs* a) {
              MLA_FP4_STATIC_MAX_CTAS, int(MLA_FP4_STATIC_SCRATCH_BYTES), num_ctas);
     return fail(MLA_FP4_ERR_UNSUPPORTED, buf);
   }
-  // set-up, once per device, with that device current: the device address of the scratch array
-  static void* scratch_addr[64] = {};
-  if (!scratch_addr[dev]) {
-    void* ptr = nullptr;
-    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
-    if (e != cudaSuccess || !ptr)
-      return fail(MLA_FP4_ERR_CUDA, std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(e));
-    scratch_addr[dev] = ptr;
-  }
+  void* scratch = nullptr;
+  int rc = static_scratch_address(dev, &scratch);
+  if (rc) return rc;
   MlaFp4DecodeArgs b = *a;
-  b.workspace = scratch_addr[dev];
+  b.workspace = scratch;
   b.workspace_bytes = size_t(MLA_FP4_STATIC_SCRATCH_BYTES);
   b.num_ctas = num_ctas;
   return mla_fp4_decode(&b);

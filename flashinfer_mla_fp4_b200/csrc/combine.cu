@@ -3,7 +3,7 @@
 //
 // grid = (512 / 16 dim chunks, groups * batch), block = 256.  A CTA owns 16 output dims of the
 // 64 heads of one (request, head group).  It re-derives which CTAs touched the request from the
-// same partition arithmetic the decode kernel used, reads their slots ([dim][head] fp16 + 64
+// same partition arithmetic the decode kernel used, reads their slots ([head group][dim][8 heads] fp16 + 64
 // base-2 LSEs) and accumulates  sum_i exp2(lse_i - max) / den * O_i ; its 8 warps split the slots.
 #include "common.cuh"
 #include "launch.h"
@@ -32,16 +32,16 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
   const int g = v / p.batch, b = v % p.batch;
   const int tid = threadIdx.x;
   if (tid < 32) {  // seq_lens is an input of the step, not a product of the decode kernel
-    int64_t T = warp_total_tiles(p.seq_lens, p.batch);
+    int64_t T = warp_total_tiles(p.seq_lens, p.batch, p.seq_cap);
     int64_t run = 0;
-    for (int i = tid; i < b; i += 32) run += vtiles_of(p.seq_lens[i]);
+    for (int i = tid; i < b; i += 32) run += vtiles_of(capped_len(p.seq_lens, i, p.seq_cap));
     for (int o = 16; o > 0; o >>= 1) run += __shfl_xor_sync(0xffffffffu, run, o);
     if (tid == 0) { s_T = T; s_start = run; }
   }
   __syncthreads();
   const int64_t T = s_T;
   const int64_t Tt = T * p.groups;
-  const int tiles = vtiles_of(p.seq_lens[b]);  // of the flat space: phantom tiles included
+  const int tiles = vtiles_of(capped_len(p.seq_lens, b, p.seq_cap));  // of the flat space: phantom tiles included
   int qpos, head0;
   group_coords(g, p.num_heads, qpos, head0);
   const int heads_here = min(kGroupHeads, p.num_heads - head0);
@@ -127,10 +127,10 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
     const float4 w0 = *reinterpret_cast<const float4*>(&lse_s[i][8 * h8]);
     const float4 w1 = *reinterpret_cast<const float4*>(&lse_s[i][8 * h8 + 4]);
     const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-    const uint16_t* row = so + size_t(dchunk * kCombDims + dq) * kGroupHeads + 8 * h8;
+    const uint16_t* row = so + slot_o_index(dchunk * kCombDims + dq, 8 * h8);  // 8 heads of one dim: 16 contiguous bytes
 #pragma unroll
     for (int q = 0; q < kCombDims / 4; ++q) {
-      const uint4 a = *reinterpret_cast<const uint4*>(row + size_t(4 * q) * kGroupHeads);
+      const uint4 a = *reinterpret_cast<const uint4*>(row + size_t(4 * q) * 8);
       const uint32_t u[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {

@@ -20,33 +20,49 @@ constexpr int kTile = MLA_FP4_TILE_TOKENS;         // 128 KV tokens per tile
 constexpr int kGroupHeads = MLA_FP4_GROUP_HEADS;   // 64 query heads per CTA
 constexpr float kLog2e = 1.4426950408889634f;
 
-// Split-KV partial slot in the workspace: normalised O as fp16 [512 dims][64 heads] divided by a
-// per-slot scale, then the base-2 LSE of the 64 heads as f32, then that scale (f32, padded to 16 B).
+// Split-KV partials in the workspace.  Layout:  header | tails [296] | partial O [slots]
+//   * partial O of slot s: normalised O as fp16 [8 head groups][512 dims][8 heads] divided by a per-slot
+//     scale (the decode kernel's lanes own one dim each: with this order a warp stores 32 dims x 8 heads =
+//     512 contiguous bytes at a time; with heads innermost over all 64 it would store 16 bytes every 128).
+//   * tail of slot s (272 bytes): the base-2 LSE of the 64 heads as f32, that scale (f32), the slot's flag
+//     (int32, see below), 8 bytes of padding.  The tails of all slots lie side by side, so the tails of the
+//     consecutive slots of one split request are one contiguous range (one bulk copy for a merging CTA).
 // The scale is 6 * max|token scale| * |output_scale| / 32768 rounded up to a power of two: an
 // upper bound of |O| mapped below the fp16 maximum, so the 11-bit partials can neither overflow nor
 // lose the small values (fp16 spans 29 binades below that bound).  Half the bytes of f32 partials.
 constexpr size_t kSlotOBytes = size_t(kLatent) * kGroupHeads * 2;
-constexpr size_t kSlotBytes = kSlotOBytes + kGroupHeads * sizeof(float) + 16;
+constexpr size_t kSlotTailBytes = kGroupHeads * sizeof(float) + 16;
+constexpr size_t kSlotBytes = kSlotOBytes + kSlotTailBytes;  // per slot, tail and partial O together
 constexpr float kSlotHalfRange = 32768.f;
-// The workspace starts with a header of counters that are zero whenever no decode step is running
-// (a step that completes leaves them zero again); the slots follow.  Counter pair c belongs to the
-// split request whose first CTA is c: how many of its partials have been published, how many of
-// its CTAs have finished merging.
-constexpr size_t kWsHeaderBytes = MLA_FP4_WORKSPACE_HEADER_BYTES;
-MLA_HD int32_t* ws_arrived(void* ws) { return static_cast<int32_t*>(ws); }
-MLA_HD int32_t* ws_done(void* ws) { return static_cast<int32_t*>(ws) + 256; }
-MLA_HD char* slot_base(void* ws, int slot) { return static_cast<char*>(ws) + kWsHeaderBytes + size_t(slot) * kSlotBytes; }
-MLA_HD const char* slot_base(const void* ws, int slot) { return static_cast<const char*>(ws) + kWsHeaderBytes + size_t(slot) * kSlotBytes; }
-MLA_HD uint16_t* slot_o(void* ws, int slot) { return reinterpret_cast<uint16_t*>(slot_base(ws, slot)); }
-MLA_HD float* slot_lse(void* ws, int slot) { return reinterpret_cast<float*>(slot_base(ws, slot) + kSlotOBytes); }
-MLA_HD const uint16_t* slot_o(const void* ws, int slot) { return reinterpret_cast<const uint16_t*>(slot_base(ws, slot)); }
-MLA_HD float* slot_scale(void* ws, int slot) { return slot_lse(ws, slot) + kGroupHeads; }
-MLA_HD const float* slot_lse(const void* ws, int slot) { return reinterpret_cast<const float*>(slot_base(ws, slot) + kSlotOBytes); }
-MLA_HD const float* slot_scale(const void* ws, int slot) { return slot_lse(ws, slot) + kGroupHeads; }
-// power-of-two scale that maps `bound` (an upper bound of |O|) to at most kSlotHalfRange
-MLA_HD float slot_scale_for(float bound) { return exp2f(ceilf(log2f(fmaxf(bound, 1e-30f) / kSlotHalfRange))); }
 // A request can be split over at most this many CTAs (= the largest decode grid accepted).
 constexpr int kMaxCombineSlots = 148;
+constexpr int kMaxSlots = 2 * kMaxCombineSlots;
+// The workspace starts with a header.  Header words (int32):
+//   [0]  generation of the last decode step that completed on this workspace
+//   [1]  CTAs of the running step that have finished (zero whenever no step is running)
+// Every slot's tail holds a flag: the generation of the step that last published the slot.  A step uses
+// generation g = header[0] + 1.  A writer stamps the flag of a slot with g once the slot's bytes are
+// visible; a merger waits until the flags of a request's slots equal g.  Flags of earlier steps never
+// match, so nothing has to be reset between steps, and a step that gave up on a wait leaves the workspace
+// consistent (its last CTA still advances the generation).  Each flag has a cache line of its own.
+constexpr size_t kWsHeaderBytes = MLA_FP4_WORKSPACE_HEADER_BYTES;
+constexpr size_t kWsTailsBytes = size_t(kMaxSlots) * kSlotTailBytes;
+constexpr size_t kWsFixedBytes = kWsHeaderBytes + kWsTailsBytes;  // what mla_fp4_workspace_init zeroes
+MLA_HD int32_t* ws_generation(void* ws) { return static_cast<int32_t*>(ws); }
+MLA_HD int32_t* ws_finished(void* ws) { return static_cast<int32_t*>(ws) + 1; }
+MLA_HD uint16_t* slot_o(void* ws, int slot) { return reinterpret_cast<uint16_t*>(static_cast<char*>(ws) + kWsFixedBytes + size_t(slot) * kSlotOBytes); }
+MLA_HD const uint16_t* slot_o(const void* ws, int slot) { return reinterpret_cast<const uint16_t*>(static_cast<const char*>(ws) + kWsFixedBytes + size_t(slot) * kSlotOBytes); }
+MLA_HD float* slot_lse(void* ws, int slot) { return reinterpret_cast<float*>(static_cast<char*>(ws) + kWsHeaderBytes + size_t(slot) * kSlotTailBytes); }
+MLA_HD const float* slot_lse(const void* ws, int slot) { return reinterpret_cast<const float*>(static_cast<const char*>(ws) + kWsHeaderBytes + size_t(slot) * kSlotTailBytes); }
+MLA_HD float* slot_scale(void* ws, int slot) { return slot_lse(ws, slot) + kGroupHeads; }
+MLA_HD const float* slot_scale(const void* ws, int slot) { return slot_lse(ws, slot) + kGroupHeads; }
+MLA_HD int32_t* slot_flag(void* ws, int slot) { return reinterpret_cast<int32_t*>(slot_scale(ws, slot) + 1); }
+// element (dim, head) of a slot's partial O
+MLA_HD size_t slot_o_index(int dim, int head) { return (size_t(head >> 3) * kLatent + size_t(dim)) * 8 + size_t(head & 7); }
+// bytes a grid of num_ctas CTAs needs: the fixed part and two partial-O slots per CTA
+__host__ __device__ constexpr size_t workspace_bytes_for(int num_ctas) { return kWsFixedBytes + size_t(2) * size_t(num_ctas) * kSlotOBytes; }
+// power-of-two scale that maps `bound` (an upper bound of |O|) to at most kSlotHalfRange
+MLA_HD float slot_scale_for(float bound) { return exp2f(ceilf(log2f(fmaxf(bound, 1e-30f) / kSlotHalfRange))); }
 
 MLA_HD int out_elem_bytes(int out_dtype) { return out_dtype == MLA_FP4_OUT_F32 ? 4 : (out_dtype == MLA_FP4_OUT_BF16 ? 2 : 1); }
 
@@ -65,6 +81,13 @@ MLA_HD int out_elem_bytes(int out_dtype) { return out_dtype == MLA_FP4_OUT_F32 ?
 // ----------------------------------------------------------------------------------------------
 
 MLA_HD int tiles_of(int seq_len) { return seq_len > 0 ? (seq_len + kTile - 1) / kTile : 0; }
+
+// A sequence length as the kernels use it: never more than `cap` tokens (the tokens a block-table row can
+// address), so a garbage seq_lens entry cannot walk a kernel past the row.
+MLA_HD int capped_len(const int32_t* seq_lens, int b, int cap) {
+  const int n = seq_lens[b];
+  return n < cap ? n : cap;
+}
 
 // The flat space that is cut into CTA ranges counts kPhantom extra tiles in front of every non-empty
 // request: moving on to another request costs a CTA about as much as two tiles (the epilogue of the
@@ -123,6 +146,7 @@ struct Segment {
 // first flat tile and are found once per CTA (find_start on the device, a plain loop on the host).
 struct Walker {
   const int32_t* seq_lens;
+  int cap;         // most tokens a request may have (see capped_len)
   int batch, groups;
   int64_t f, hi;   // current flat tile, end of the CTA's range
   int b, g, t;     // current request, group, tile inside the request
@@ -133,7 +157,7 @@ struct Walker {
   MLA_HD bool next(Segment& s) {
     while (f < hi) {
       if (g >= groups) return false;
-      int sl = seq_lens[b];
+      int sl = capped_len(seq_lens, b, cap);
       int tb = vtiles_of(sl);  // t, end, room and f count phantom tiles; the segment holds real ones
       if (t >= tb) {
         t = 0;
@@ -165,22 +189,22 @@ MLA_HD void group_coords(int g, int num_heads, int& qpos, int& head0) {
 
 #ifdef __CUDACC__
 // Warp-cooperative: total tile count of the batch. All 32 lanes must call; all get the result.
-__device__ __forceinline__ int64_t warp_total_tiles(const int32_t* seq_lens, int batch) {
+__device__ __forceinline__ int64_t warp_total_tiles(const int32_t* seq_lens, int batch, int cap) {
   int lane = threadIdx.x & 31;
   int64_t acc = 0;
-  for (int i = lane; i < batch; i += 32) acc += vtiles_of(seq_lens[i]);
+  for (int i = lane; i < batch; i += 32) acc += vtiles_of(capped_len(seq_lens, i, cap));
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   return acc;
 }
 
 // Warp-cooperative: locate flat tile r (0 <= r < T, within one group) -> request b and tile t.
-__device__ __forceinline__ void warp_locate(const int32_t* seq_lens, int batch, int64_t r, int& b_out, int& t_out) {
+__device__ __forceinline__ void warp_locate(const int32_t* seq_lens, int batch, int cap, int64_t r, int& b_out, int& t_out) {
   int lane = threadIdx.x & 31;
   int64_t run = 0;
   b_out = batch; t_out = 0;
   for (int base = 0; base < batch; base += 32) {
     int i = base + lane;
-    int64_t v = i < batch ? vtiles_of(seq_lens[i]) : 0;
+    int64_t v = i < batch ? vtiles_of(capped_len(seq_lens, i, cap)) : 0;
     int64_t inc = v;
     for (int o = 1; o < 32; o <<= 1) {
       int64_t u = __shfl_up_sync(0xffffffffu, inc, o);
@@ -200,10 +224,10 @@ __device__ __forceinline__ void warp_locate(const int32_t* seq_lens, int batch, 
 }
 
 // Initialise a walker for CTA `cta` of `n`. Warp-cooperative (all 32 lanes call, all get it).
-__device__ __forceinline__ Walker make_walker(const int32_t* seq_lens, int batch, int groups, int cta, int n) {
+__device__ __forceinline__ Walker make_walker(const int32_t* seq_lens, int batch, int cap, int groups, int cta, int n) {
   Walker w;
-  w.seq_lens = seq_lens; w.batch = batch; w.groups = groups; w.cta = cta; w.first = true;
-  int64_t T = warp_total_tiles(seq_lens, batch);
+  w.seq_lens = seq_lens; w.cap = cap; w.batch = batch; w.groups = groups; w.cta = cta; w.first = true;
+  int64_t T = warp_total_tiles(seq_lens, batch, cap);
   int64_t Tt = T * groups;
   w.Tt = Tt;
   w.f = cta_lo(Tt, n, cta);
@@ -211,7 +235,7 @@ __device__ __forceinline__ Walker make_walker(const int32_t* seq_lens, int batch
   w.b = 0; w.g = groups; w.t = 0;
   if (T > 0 && w.f < w.hi) {
     w.g = int(w.f / T);
-    warp_locate(seq_lens, batch, w.f % T, w.b, w.t);
+    warp_locate(seq_lens, batch, cap, w.f % T, w.b, w.t);
   }
   return w;
 }

@@ -25,14 +25,15 @@
 // split the 64 heads).
 //
 // Requests that are split across CTAs are merged at the end of the same kernel (tail_merge): the
-// CTAs publish their partials through counters in the workspace header and each takes a share of
-// the output dims.  The two-kernel mode leaves the merge to the combine kernel instead.
+// CTAs publish their partials through a flag in each slot and each takes a share of the output dims.  The two-kernel mode leaves the merge to the combine kernel instead.
 //
 // The per-role loops are kept small on purpose: the instruction streams share one
 // instruction cache, and an MMA-issue or softmax loop that misses it starves the tensor pipe.
 //
 // Every wait is bounded: when a wait expires the CTA records MLA_FP4_ERR_DEVICE_TIMEOUT in the
 // status words, stops issuing work, drains and exits normally.
+#include <atomic>
+
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -67,14 +68,17 @@ constexpr uint32_t kOffP = kOffQRope + kGroupHeads * 64;                  // [2]
 constexpr uint32_t kOffScale = kOffP + kStages * 2 * kTile * 64;          // [2][128] f32
 constexpr uint32_t kOffM = kOffScale + kStages * kTile * 4;               // [64] f32 NEGATED reference -(M - shift)
 constexpr uint32_t kOffF = kOffM + kGroupHeads * 4;                       // [64] f32 rescale factor
-constexpr uint32_t kOffWmax = kOffF + kGroupHeads * 4;                    // [4][64] f32 per-warp column max / sum
+constexpr uint32_t kOffDelta = kOffF + kGroupHeads * 4;                   // [64] f32 how far the reference moved at its last refresh
+constexpr uint32_t kOffWmax = kOffDelta + kGroupHeads * 4;                // [4][64] f32 per-warp column max / sum
 constexpr uint32_t kOffLinv = kOffWmax + 4 * kGroupHeads * 4;             // [64] f32 output_scale / l
 constexpr uint32_t kOffLse = kOffLinv + kGroupHeads * 4;                  // [64] f32
 constexpr uint32_t kOffScMax = kOffLse + kGroupHeads * 4;                 // [8] f32 per-warp largest token scale
 constexpr uint32_t kOffBars = kOffScMax + 8 * 4;                          // mbarriers (8 B each)
 constexpr int kNumBars = 2 * 4 /*kv_full*/ + 2 * 4 /*kv_empty*/ + 2 /*aux_full*/ + 2 /*s_full*/ + 2 /*s_empty*/ +
-                         2 /*p_full*/ + 1 /*q_full*/ + 1 /*q_empty*/ + 1 /*o_free*/ + 1 /*drain*/;
-constexpr uint32_t kOffSegs = kOffBars + kNumBars * 8;                    // Segment[kMaxSeg]
+                         2 /*p_full*/ + 1 /*q_full*/ + 1 /*q_empty*/ + 1 /*o_free*/ + 1 /*drain*/ + 1 /*tail*/;
+constexpr uint32_t kOffTail = kOffBars + kNumBars * 8;                    // merge plan: [148] slot ids, then [64] f32 1/sum of weights
+constexpr uint32_t kOffTailInv = kOffTail + kMaxCombineSlots * 4;
+constexpr uint32_t kOffSegs = kOffTailInv + kGroupHeads * 4;              // Segment[kMaxSeg]
 constexpr uint32_t kOffMisc = kOffSegs + kMaxSeg * 24;                    // tmem base, abort flag, walker
 constexpr uint32_t kSmemBytes = kOffMisc + 256;
 constexpr uint32_t kSmemAlloc = kSmemBytes + 1024;                        // slack for manual 1024-alignment
@@ -89,7 +93,7 @@ __device__ __forceinline__ constexpr int bar_aux_full(int s) { return 16 + s; }
 __device__ __forceinline__ constexpr int bar_s_full(int s) { return 18 + s; }
 __device__ __forceinline__ constexpr int bar_s_empty(int s) { return 20 + s; }
 __device__ __forceinline__ constexpr int bar_p_full(int s) { return 22 + s; }
-constexpr int kBarQFull = 24, kBarQEmpty = 25, kBarOFree = 26, kBarDrain = 27;
+constexpr int kBarQFull = 24, kBarQEmpty = 25, kBarOFree = 26, kBarDrain = 27, kBarTail = 28;
 
 // TMEM columns
 constexpr uint32_t kColSLat = 0;     // + 64 * stage
@@ -104,7 +108,7 @@ constexpr uint32_t kIdescPV = ptx::idesc_e4m3(128, kGroupHeads, true, true) | kF
 // A split request this CTA wrote a partial for (at most two: its first and its last segment).
 struct MergeReq {
   int b, g, tiles;
-  int counter;    // index of the request's counters in the workspace header: the first CTA of its span
+  int counter;    // the first CTA of the request's span
   int slot;       // the slot this CTA wrote (even: the segment was the CTA's first)
   int64_t start;  // flat tile index of the request's first tile
 };
@@ -116,9 +120,8 @@ struct Misc {
   Walker walker;
   int n_merge;
   MergeReq merge[2];
-  // scratch of the tail merge
-  int64_t total_tiles;
-  int n_slots, n_part, rank;
+  // the merge plan (plan_merge)
+  int n_slots, n_part, rank, merge_k;
 };
 static_assert(sizeof(Misc) <= 256, "misc area");
 
@@ -127,6 +130,8 @@ struct Ctx {
   uint8_t* smem_ptr;  // generic pointer to the same
   Misc* misc;
   int32_t* status;
+  uint32_t polls;     // poll budget of a bounded wait
+  int32_t gen;        // generation of this decode step (flags of its partial slots carry it)
 #ifdef MLA_FP4_TRACE
   int trace_cta;  // the CTA whose timeline is recorded (status word 7; the last CTA when negative)
 #endif
@@ -158,7 +163,7 @@ __device__ __noinline__ void flag_timeout(const Ctx& c, int idx, uint32_t parity
 __device__ __noinline__ bool wait_slow(const Ctx& c, int idx, uint32_t parity) {
   const uint32_t bar = bar_addr(c, idx);
 #pragma unroll 1
-  for (uint32_t i = 0; i < (1u << 22); ++i) {
+  for (uint32_t i = 0; i < c.polls; ++i) {
     if (c.misc->abort) return false;
     if (ptx::mbar_try_wait(bar, parity)) return true;  // suspends in hardware for a while: not a hot spin
     if (i > 4096) __nanosleep(128);
@@ -179,11 +184,26 @@ __device__ __forceinline__ bool wait_warp(const Ctx& c, int idx, uint32_t parity
 // Bounded wait that ignores the abort flag: lets in-flight asynchronous work land before exit.
 __device__ __noinline__ void drain_wait(const Ctx& c, int idx, uint32_t parity) {
   const uint32_t bar = bar_addr(c, idx);
+  const uint32_t limit = c.polls < (1u << 20) ? c.polls : (1u << 20);
 #pragma unroll 1
-  for (uint32_t i = 0; i < (1u << 20); ++i) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (ptx::mbar_try_wait(bar, parity)) return;
     __nanosleep(64);
   }
+}
+
+__device__ __forceinline__ int ld_acquire(const int32_t* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_relaxed(const int32_t* p) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release(int32_t* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // Optional timeline trace (debug builds only, -DMLA_FP4_TRACE): clock64 stamps of the last CTA for the
@@ -233,8 +253,9 @@ __device__ __forceinline__ void tma_role(const DecodeParams& p, const Ctx& c, co
     // (never beyond the request's pages).
     auto page_of = [&](int tile) {
       const int lp = tile * ppt + lane;
-      return (tile < g.tile_end && lane < ppt && lp < pages_total) ? __ldg(bt_req + lp) : -1;
-    };
+      const int id = (tile < g.tile_end && lane < ppt && lp < pages_total) ? __ldg(bt_req + lp) : -1;
+      return int64_t(id) < p.num_pages ? id : -1;  // an id outside the pool is never turned into an address: the tile's barrier
+    };                                              // then never completes and the bounded wait reports it
     int pg = page_of(g.tile_begin), pg1 = page_of(g.tile_begin + 1), pg2 = page_of(g.tile_begin + 2);
 #pragma unroll 1
     for (int t = g.tile_begin; t < g.tile_end; ++t, ++st.it) {
@@ -488,11 +509,28 @@ __device__ __forceinline__ float lds_f32(uint32_t addr) {
   asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
   return v;
 }
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float2 lds_f32x2(uint32_t addr) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 lds_f32x4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
   asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
-// two-term E4M3 split of a pair: hi = e4m3(v), lo = e4m3(v - hi); returns hi (16 bits), lo via reference
+// two-term E4M3 split of a pair: hi = e4m3(v), lo = e4m3(v - hi); returns hi (16 bits), lo via reference.
+// Five two-wide instructions; the softmax pass is bound by instruction issue (two warps per scheduler), and a
+// split on the FMA pipe (Veltkamp) measured slower because it needs one more.
 __device__ __forceinline__ uint32_t split_e4m3x2(uint64_t v2, uint32_t& lo) {
   float a, b;
   unpack2(v2, a, b);
@@ -533,10 +571,30 @@ struct SoftmaxTile {
   bool valid;
 };
 
-// One pass over the 32 heads this thread owns of its token: e = exp2(x*c - m), l += acc * e, and
-// P' = e*scale_t split into two E4M3 terms and written to the swizzled P rows.  Returns the
-// largest exponent argument seen (for the lazy-reference check).
-__device__ __forceinline__ float softmax_pass(const SoftmaxTile& t, uint64_t (&l2)[kHalfHeads / 2], uint64_t acc2) {
+// One pass over the 32 heads this thread owns of its token: e = exp2(x*c - m) and P' = e*scale_t split into two
+// E4M3 terms and written to the swizzled P rows.
+//
+// First pass (kSecond = false), speculative, with the reference as it stands: the row sums take e, and the largest
+// exponent argument seen is returned for the lazy-reference check.  An argument above kArgCap is clamped before it
+// is exponentiated: a score may beat the reference by hundreds of binades (heavy-tailed token scales), 2^arg would be
+// infinite and the sums lost.  Such a tile always has its reference refreshed and its P' recomputed.
+//
+// Second pass (kSecond = true), after a refresh that moved the reference of head h by delta_h: the caller has scaled the
+// sums by f = 2^-delta, which turns every e of the first pass into its new value, (l + e_old) * f = l * f + e_new,
+// except where the first pass clamped: there 2^(kArgCap - delta) went in instead of e_new, and this pass adds the difference.
+constexpr float kArgCap = 64.f;
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+template <bool kSecond>
+__device__ __forceinline__ float softmax_pass(const SoftmaxTile& t, uint64_t (&l2)[kHalfHeads / 2]) {
   float mx = -INFINITY;
 #pragma unroll
   for (int cidx = 0; cidx < 2; ++cidx) {
@@ -546,7 +604,9 @@ __device__ __forceinline__ float softmax_pass(const SoftmaxTile& t, uint64_t (&l
     ptx::tmem_wait_ld();
     const uint32_t off = (((2 * t.half + uint32_t(cidx)) ^ t.psw) << 4);
     if (t.valid) {
-      uint32_t hi16[8], lo16[8];
+      // exponent arguments of the chunk's 16 heads against the current references
+      float arg[16];
+      float cm = -INFINITY;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {  // 4 heads per shared load of the references
         uint64_t nm0, nm1;
@@ -555,14 +615,32 @@ __device__ __forceinline__ float softmax_pass(const SoftmaxTile& t, uint64_t (&l
         for (int h = 0; h < 2; ++h) {
           const int i = 4 * q + 2 * h;
           const uint64_t x2 = fma2(pack2u(a[i], a[i + 1]), t.sc2, pack2u(b[i], b[i + 1]));
-          const uint64_t arg2 = fma2(x2, t.cs2, h ? nm1 : nm0);
-          float a0, a1;
-          unpack2(arg2, a0, a1);
-          mx = fmaxf(mx, fmaxf(a0, a1));
-          const uint64_t e2 = pack2(ptx::ex2(a0), ptx::ex2(a1));
-          l2[8 * cidx + 2 * q + h] = fma2(e2, acc2, l2[8 * cidx + 2 * q + h]);
-          hi16[2 * q + h] = split_e4m3x2(mul2(e2, t.sc2), lo16[2 * q + h]);
+          unpack2(fma2(x2, t.cs2, h ? nm1 : nm0), arg[i], arg[i + 1]);
+          cm = max3(cm, arg[i], arg[i + 1]);
         }
+      }
+      if (!kSecond) {
+        mx = fmaxf(mx, cm);
+        if (cm > kArgCap) {  // rare: one compare and branch per chunk instead of a clamp per value
+#pragma unroll
+          for (int i = 0; i < 16; ++i) arg[i] = fminf(arg[i], kArgCap);
+        }
+      }
+      uint32_t hi16[8], lo16[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float e0 = ptx::ex2(arg[2 * q]), e1 = ptx::ex2(arg[2 * q + 1]);
+        const uint64_t e2 = pack2(e0, e1);
+        if (!kSecond) {
+          l2[8 * cidx + q] = add2(l2[8 * cidx + q], e2);
+        } else {
+          const float d0 = lds_f32(t.negm + (kOffDelta - kOffM) + 64 * cidx + 8 * q);
+          const float d1 = lds_f32(t.negm + (kOffDelta - kOffM) + 64 * cidx + 8 * q + 4);
+          const float c0 = (arg[2 * q] + d0 > kArgCap) ? e0 - ptx::ex2(kArgCap - d0) : 0.f;
+          const float c1 = (arg[2 * q + 1] + d1 > kArgCap) ? e1 - ptx::ex2(kArgCap - d1) : 0.f;
+          l2[8 * cidx + q] = add2(l2[8 * cidx + q], pack2(c0, c1));
+        }
+        hi16[q] = split_e4m3x2(mul2(e2, t.sc2), lo16[q]);
       }
       asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(t.p_hi + off), "r"(hi16[0] | (hi16[1] << 16)),
                    "r"(hi16[2] | (hi16[3] << 16)), "r"(hi16[4] | (hi16[5] << 16)), "r"(hi16[6] | (hi16[7] << 16)) : "memory");
@@ -605,6 +683,7 @@ __device__ __noinline__ void refresh_reference(const Ctx& c, uint32_t t_lat, uin
     const float mold = have_m ? -lds_f32(c.smem + kOffM + 4 * tid) : -INFINITY;
     mnew = fmaxf(mnew, mold);
     sts_f32(c.smem + kOffF + 4 * tid, have_m ? ptx::ex2(mold - mnew) : 0.f);
+    sts_f32(c.smem + kOffDelta + 4 * tid, have_m ? mnew - mold : 0.f);
     sts_f32(c.smem + kOffM + 4 * tid, -mnew);
   }
   ptx::bar_sync(1, kSoftmaxThreads);
@@ -628,6 +707,7 @@ __device__ __noinline__ void rescale_output(const Ctx& c, uint32_t tmem_lane, ui
 }
 
 // Normalise O^T and write it: to the output tensor (slot < 0) or to a split-KV partial slot.
+// Runs once per segment, so its instructions are fetched cold: rolled loops over (block, 16 heads), a small body.
 __device__ __noinline__ void write_output(const DecodeParams& p, const Ctx& c, uint32_t tmem_lane, int row, int half,
                                           int tid, int b, int g, int slot, float slot_scale_v) {
   int qpos, head0;
@@ -636,47 +716,45 @@ __device__ __noinline__ void write_output(const DecodeParams& p, const Ctx& c, u
   const size_t row0 = (size_t(b) * p.q_len + qpos) * p.num_heads + head0;
   const bool direct = slot < 0;
   __half* so = reinterpret_cast<__half*>(slot_o(p.workspace, direct ? 0 : slot));
-  // output_scale / l of this thread's 32 heads (times 1 / slot scale for a partial), read once
-  const float post = direct ? 1.f : 1.f / slot_scale_v;
-  float li[32];
-#pragma unroll
-  for (int i = 0; i < 32; ++i) li[i] = lds_f32(c.smem + kOffLinv + 4 * (32 * half + i)) * post;
+  const float post = direct ? 1.f : 1.f / slot_scale_v;  // a partial is stored divided by its slot scale
+  const uint32_t esz = uint32_t(out_elem_bytes(p.out_dtype));
 #pragma unroll 1
-  for (int jb = 0; jb < kBlocks; ++jb) {
-    uint32_t o[2][16];  // both 16-head halves of the block in flight before one wait
-    ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(jb) + uint32_t(32 * half), o[0]);
-    ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(jb) + uint32_t(32 * half + 16), o[1]);
+  for (int it = 0; it < kBlocks * 2; ++it) {
+    const int jb = it >> 1, h0 = 32 * half + 16 * (it & 1);  // block of 128 dims, first of 16 heads
+    uint32_t o[16];
+    ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(jb) + uint32_t(h0), o);
+    float li[16];  // output_scale / l of the 16 heads
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float4 f = lds_f32x4(c.smem + kOffLinv + 4 * (h0 + 4 * q));
+      li[4 * q] = f.x; li[4 * q + 1] = f.y; li[4 * q + 2] = f.z; li[4 * q + 3] = f.w;
+    }
     ptx::tmem_wait_ld();
     const int dim = 128 * jb + row;
-    const int h0 = 32 * half;
-    float v[32];
+    float v[16];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i >> 4][i & 15]) * li[i];
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(o[i]) * (li[i] * post);
     if (!direct) {
-      uint32_t pk[16];
+      uint32_t pk[8];
 #pragma unroll
-      for (int q = 0; q < 16; ++q) {
+      for (int q = 0; q < 8; ++q) {
         __half2 h2 = __floats2half2_rn(v[2 * q], v[2 * q + 1]);
         pk[q] = *reinterpret_cast<uint32_t*>(&h2);
       }
-      uint4* dst = reinterpret_cast<uint4*>(so + size_t(dim) * kGroupHeads + h0);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) dst[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-    } else if (p.out_dtype == MLA_FP4_OUT_BF16) {
-      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (row0 + h0) * kLatent + dim;
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (h0 + i < heads_here) dst[size_t(i) * kLatent] = __float2bfloat16_rn(v[i]);
-    } else if (p.out_dtype == MLA_FP4_OUT_F32) {
-      float* dst = reinterpret_cast<float*>(p.out) + (row0 + h0) * kLatent + dim;
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (h0 + i < heads_here) dst[size_t(i) * kLatent] = v[i];
+      // the warp's 32 dims x 8 heads are 512 contiguous bytes of the slot
+      *reinterpret_cast<uint4*>(so + slot_o_index(dim, h0)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      *reinterpret_cast<uint4*>(so + slot_o_index(dim, h0 + 8)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
     } else {
-      uint8_t* dst = reinterpret_cast<uint8_t*>(p.out) + (row0 + h0) * kLatent + dim;
+      char* dst = static_cast<char*>(p.out) + ((row0 + h0) * kLatent + dim) * esz;
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (h0 + i < heads_here) dst[size_t(i) * kLatent] = __nv_cvt_float_to_fp8(v[i], __NV_SATFINITE, __NV_E4M3);
+      for (int i = 0; i < 16; ++i) {
+        if (h0 + i < heads_here) {
+          char* d = dst + size_t(i) * kLatent * esz;
+          if (p.out_dtype == MLA_FP4_OUT_BF16) *reinterpret_cast<__nv_bfloat16*>(d) = __float2bfloat16_rn(v[i]);
+          else if (p.out_dtype == MLA_FP4_OUT_F32) *reinterpret_cast<float*>(d) = v[i];
+          else *reinterpret_cast<uint8_t*>(d) = __nv_cvt_float_to_fp8(v[i], __NV_SATFINITE, __NV_E4M3);
+        }
+      }
     }
   }
   const float lse = lds_f32(c.smem + kOffLse + 4 * (tid & 63));
@@ -697,13 +775,12 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
   const int row = quarter * 32 + lane;    // token of the tile (S) / dim of the block (O) of this thread
   const uint32_t tmem_lane = tmem + ((uint32_t(quarter) * 32u) << 16);
   const float cscale = p.softmax_scale * kLog2e;
-  const uint64_t one2 = pack2(1.f, 1.f);
   SoftmaxTile t;
   t.negm = c.smem + kOffM + 4 * kHalfHeads * half;
   t.cs2 = pack2(cscale, cscale);
   t.psw = (uint32_t(row) >> 1) & 3u;
   t.half = uint32_t(half);
-  int pending0 = 0, pending1 = 0, n_pending = 0;  // counters of the partials written in this call, published together at its end
+  int pending0 = 0, pending1 = 0, n_pending = 0;  // slots of the partials written in this call, published together at its end
 
 #pragma unroll 1
   for (int si = 0; si < nseg; ++si, ++st.seg) {
@@ -746,7 +823,7 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
 
       // Speculative pass with the current reference.  It stands unless some score beat the
       // reference by more than the lazy threshold (P' would leave the E4M3 range).
-      const float mx = softmax_pass(t, l2, one2);
+      const float mx = softmax_pass<false>(t, l2);
       const bool need = t.valid && (mx + lg > kPShift + kLazyThreshold);
       if (ptx::bar_or(1, kSoftmaxThreads, need)) {
         // Refresh the reference.  (l + e_old) * f equals l * f + e_new, so the row sums only need
@@ -766,7 +843,7 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
           ptx::tc_fence_after();
           rescale_output(c, tmem_lane, uint32_t(half));
         }
-        (void)softmax_pass(t, l2, 0ull);
+        (void)softmax_pass<true>(t, l2);
       }
       if (tid == 0) MLA_TRACE(0, it, 3);
       ptx::tc_fence_before();  // orders the S reads and any O rescale before the arrives
@@ -800,14 +877,15 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
 #pragma unroll
       for (int w8 = 0; w8 < kSoftmaxThreads / 32; ++w8) sc_all = fmaxf(sc_all, lds_f32(c.smem + kOffScMax + 4 * w8));
       const float slot_scale_v = slot_scale_for(6.f * sc_all * fabsf(p.output_scale));
+      if (tid == 0) MLA_TRACE(0, lit, 7);
       if (!c.misc->abort) write_output(p, c, tmem_lane, row, half, tid, g.b, g.g, g.slot, slot_scale_v);
+      if (tid == 0) MLA_TRACE(0, lit, 4);
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar_addr(c, kBarOFree));
       if (g.slot >= 0) {  // a partial: published (below) once this CTA has written all its partials of the round
         if (p.fused_merge && n_pending < 2) {
-          const int counter = c.misc->merge[st.part].counter;
-          if (n_pending == 0) pending0 = counter;
-          else pending1 = counter;
+          if (n_pending == 0) pending0 = g.slot;
+          else pending1 = g.slot;
           ++n_pending;
         }
         ++st.part;
@@ -815,15 +893,23 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       if (tid == 0) MLA_TRACE(0, lit, 6);
     }
   }
-  // Publish the partials: the tail merge of their requests' CTAs waits for these counts.  One fence for
+  // Publish the partials: the tail merge of their requests' CTAs waits for these flags.  One fence for
   // all of them, after the last segment: a fence in the middle would hold up the next segment's first tile,
   // and nobody can use a partial before this CTA, itself a writer of the later request, is done anyway.
   if (n_pending > 0) {
     __threadfence();
     ptx::bar_sync(1, kSoftmaxThreads);
     if (tid == 0) {
-      atomicAdd(ws_arrived(p.workspace) + pending0, 1);
-      if (n_pending > 1) atomicAdd(ws_arrived(p.workspace) + pending1, 1);
+      st_release(slot_flag(p.workspace, pending0), c.gen);
+      if (n_pending > 1) st_release(slot_flag(p.workspace, pending1), c.gen);
+      MLA_TRACE(3, 2u, 0);
+#ifdef MLA_FP4_TRACE
+      if (c.status) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        (reinterpret_cast<unsigned long long*>(c.status + 8) + 12 * 16 * 8 + 4 * blockIdx.x)[3] = t;
+      }
+#endif
     }
   }
 }
@@ -860,36 +946,32 @@ __device__ __noinline__ void stage_segments(const Ctx& c) {
 // ------------------------------------------------------------------------------------------
 // tail: merge of the split-KV partials inside the decode kernel
 // ------------------------------------------------------------------------------------------
-// Every CTA that wrote a partial of a split request publishes it (a counter in the workspace
-// header) right after writing it.  In the tail, the CTAs whose partial of a request was their
-// first segment wait until all partials of that request are there and then merge, each, a share
-// of the 512 output dims: out = sum_i w_i * O_i with w_i = 2^(lse_i - max) / sum * slot scale, the
-// same arithmetic as the combine kernel.  A CTA has published everything it will ever publish
-// before it waits for anybody else, so the waits cannot form a cycle; the launch is cooperative,
-// so every CTA of the grid is resident; the waits are bounded like all others.  The last CTA to
-// finish a request's merge zeroes its counters again.
-constexpr int kTailLseStride = kGroupHeads + 4;                        // padded: the slot lanes of a unit hit different banks
-constexpr uint32_t kTailLse = kOffKV;                                  // [148][68] f32: LSEs, then weights
-constexpr uint32_t kTailList = kTailLse + kMaxCombineSlots * kTailLseStride * 4;  // [148] slot ids
-constexpr uint32_t kTailScale = kTailList + kMaxCombineSlots * 4;      // [148] f32 slot scales
-static_assert(kTailScale + kMaxCombineSlots * 4 <= kOffKV + kStages * kBlocks * kBlockBytes, "tail scratch fits the idle KV ring");
+// Every CTA that wrote a partial of a split request stamps the slot's flag (the last words of the slot)
+// with the generation of this step.  In the tail, the CTAs whose partial of a request was their
+// first segment merge it, each a share of the 512 output dims: thread i watches the flag of the
+// request's i-th slot and, the moment it is up, starts bulk copies of that slot's LSEs and of this
+// CTA's share of its rows into shared memory (the main loop's buffers are idle by now).  The slots
+// therefore stream in as their writers finish; what is left after the last writer is one copy and one
+// pass over shared memory:  out = sum_i w_i * O_i  with  w_i = 2^(lse_i - max) / sum * slot scale,
+// accumulated in slot order whatever the order of arrival (bit-reproducible).  A CTA has published
+// everything it will ever publish before it waits for anybody else, so the waits cannot form a cycle;
+// the launch is cooperative, so every CTA of the grid is resident; the waits are bounded like all others.
+constexpr uint32_t kTailLseBytes = uint32_t(kSlotTailBytes);            // a slot's tail: 64 LSEs, the slot scale, the flag, padding
+constexpr uint32_t kTailStage = kOffKV;                                 // staging: [slots][this CTA's bytes of a slot], then the tails
+constexpr uint32_t kTailStageBytes = kOffScale - kOffKV;                // the KV ring, the RoPE stages, Q and P
+static_assert(kTailStageBytes >= 2 * kSlotOBytes + 4 * kTailLseBytes, "two whole slots fit (a request cut once)");
+static_assert(kTailStageBytes >= kSlotOBytes + kSlotOBytes / 8 + kWsTailsBytes, "a request cut 148 times fits");
 
-// Loads that happen only under a predicate and leave the destination untouched otherwise (the caller
-// never reads a destination whose load was off): no zero fill, no branch.
-__device__ __forceinline__ void ldcg_v4_if(uint4& d, const void* ptr, bool on) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t@p ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];\n\t}"
-               : "=r"(d.x), "=r"(d.y), "=r"(d.z), "=r"(d.w)
-               : "l"(ptr), "r"(uint32_t(on))
-               : "memory");
-}
-__device__ __forceinline__ void ldcg_f32_if(float& d, const float* ptr, bool on) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %2, 0;\n\t@p ld.global.cg.f32 %0, [%1];\n\t}" : "=f"(d) : "l"(ptr), "r"(uint32_t(on)) : "memory");
-}
-
-__device__ __forceinline__ int ld_acquire(const int32_t* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
+// two consecutive output elements (an even index) in the output's element type
+__device__ __noinline__ void store_out_pair(void* out, int out_dtype, size_t idx, float a, float b) {
+  if (out_dtype == MLA_FP4_OUT_BF16) {
+    __nv_bfloat162 b2 = __floats2bfloat162_rn(a, b);
+    *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(out) + idx) = *reinterpret_cast<uint32_t*>(&b2);
+  } else if (out_dtype == MLA_FP4_OUT_F32) {
+    *reinterpret_cast<float2*>(static_cast<float*>(out) + idx) = make_float2(a, b);
+  } else {
+    *reinterpret_cast<uint16_t*>(static_cast<uint8_t*>(out) + idx) = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  }
 }
 
 // The tail runs once per CTA, so its instructions are fetched cold: it is written for few
@@ -900,7 +982,7 @@ __device__ __noinline__ void zero_empty_requests(const DecodeParams& p, int tid)
 #pragma unroll 1
   for (int v = blockIdx.x; v < total; v += gridDim.x) {
     const int g = v / p.batch, b = v - g * p.batch;
-    if (p.seq_lens[b] > 0) continue;
+    if (capped_len(p.seq_lens, b, p.seq_cap) > 0) continue;
     int qpos, head0;
     group_coords(g, p.num_heads, qpos, head0);
     const int heads_here = min(kGroupHeads, p.num_heads - head0);
@@ -913,250 +995,234 @@ __device__ __noinline__ void zero_empty_requests(const DecodeParams& p, int tid)
   }
 }
 
+// The merge plan of this CTA, made by one warp while the main loop is still waiting for its first tile: the slots
+// of the request this CTA merges (in CTA order), how many CTAs merge it and this CTA's place among them.
+// A CTA merges only the request of its first segment (even slot): every CTA then takes part in at most one
+// merge, and the first writer of a request, which reaches it last, in none.  Writers of the request: CTA m.counter,
+// then every following CTA whose range starts before the request ends and holds a real tile of it.  The first
+// writer uses slot 2i+1 unless its range starts with the request; the others start inside the request, use slot 2i
+// and take part in the merge.
+__device__ __noinline__ void plan_merge(const Ctx& c, int lane) {
+  Misc* misc = c.misc;
+  const int n = gridDim.x;
+  int k = -1;
+  for (int i = 0; i < misc->n_merge; ++i)
+    if (!(misc->merge[i].slot & 1)) k = i;
+  if (k < 0) {
+    if (lane == 0) misc->n_slots = 0;
+    return;
+  }
+  const MergeReq m = misc->merge[k];
+  const int64_t Tt = misc->walker.Tt;
+  const int64_t end = m.start + m.tiles;
+  const bool small = Tt * n < (int64_t(1) << 32);  // the usual case: 32-bit division
+  int cnt = 0, part = 0, rank = 0;
+#pragma unroll 1
+  for (int base = m.counter & ~31; base < n; base += 32) {
+    const int i = base + lane;
+    bool writer = false, merger = false;
+    if (i < n && i >= m.counter) {
+      int64_t lo, nlo;
+      if (small) {
+        lo = int64_t(uint32_t(Tt) * uint32_t(i) / uint32_t(n));
+        nlo = int64_t(uint32_t(Tt) * uint32_t(i + 1) / uint32_t(n));
+      } else {
+        lo = cta_lo(Tt, n, i);
+        nlo = cta_lo(Tt, n, i + 1);
+      }
+      writer = lo < end && nlo > lo && nlo > m.start + kPhantom;  // holds at least one real tile of the request
+      merger = writer && lo >= m.start;
+    }
+    const uint32_t bw = __ballot_sync(0xffffffffu, writer), bm = __ballot_sync(0xffffffffu, merger);
+    const uint32_t below = (1u << lane) - 1u;
+    if (writer) {
+      const int pos = cnt + __popc(bw & below);
+      if (pos < kMaxCombineSlots) sts_f32(c.smem + kOffTail + 4u * uint32_t(pos), __int_as_float(slot_of(i, merger)));
+    }
+    const int mine = (i == int(blockIdx.x) && merger) ? part + __popc(bm & below) : 0;
+    rank += __reduce_add_sync(0xffffffffu, mine);
+    cnt += __popc(bw);
+    part += __popc(bm);
+    if (bw == 0 && cnt > 0) break;  // past the request
+  }
+  if (lane == 0) {
+    misc->n_slots = min(cnt, kMaxCombineSlots);
+    misc->n_part = part;
+    misc->rank = rank;
+    misc->merge_k = k;
+  }
+}
+
+// The tail runs once per CTA: small loop bodies, shared memory read with ld.shared in batches (a chain of
+// dependent load-then-add iterations is what made an earlier version slow, not the amount of work).
 __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int tid) {
   Misc* misc = c.misc;
-  float* lse_s = reinterpret_cast<float*>(c.smem_ptr + kTailLse);
-  int* list_s = reinterpret_cast<int*>(c.smem_ptr + kTailList);
-  float* scale_s = reinterpret_cast<float*>(c.smem_ptr + kTailScale);
   void* ws = p.workspace;
-  const int n = gridDim.x;
-  const int n_merge = misc->n_merge;
-
+  const int ns = misc->n_slots;
+  if (ns == 0) return;
+  const int np = misc->n_part, rank = misc->rank;
+  const MergeReq m = misc->merge[misc->merge_k];
+  const uint32_t list = c.smem + kOffTail;
+  int qpos, head0;
+  group_coords(m.g, p.num_heads, qpos, head0);
+  const int heads_here = min(kGroupHeads, p.num_heads - head0);
+  const size_t row0 = (size_t(m.b) * p.q_len + qpos) * p.num_heads + head0;
+  // This CTA's share of every slot: units [2048*rank/np, 2048*(rank+1)/np) of 32 bytes (a pair of dims of one head
+  // group, in the slot's own order), so a share is one contiguous range of the slot: one bulk copy.
+  const int U0 = (2048 * rank) / np, U1 = (2048 * (rank + 1)) / np;
+  const uint32_t share_bytes = uint32_t(U1 - U0) * 32u;
+  const int s0 = int(lds_u32(list));
+  const uint32_t rows = c.smem + kTailStage;
+  const uint32_t tails = rows + uint32_t(ns) * share_bytes;  // the tails of slots s0 .. last, as they lie in the workspace
+  const int warps = (ns + 31) >> 5;
+  const bool fits = uint32_t(ns) * share_bytes + uint32_t(2 * ns + 2) * kTailLseBytes <= kTailStageBytes;
+  if (tid == 0) {
+    ptx::mbar_init(bar_addr(c, kBarTail), uint32_t(ns + warps));  // one arrival per slot and one per warp's range of tails
+    ptx::fence_barrier_init();
+    if (!fits) flag_timeout(c, 200, uint32_t(ns));  // cannot happen: mergers >= writers - 1
+    MLA_TRACE(3, 1u, 1);
+  }
+  __syncthreads();
+  // Thread i: wait for slot i, then fetch this CTA's share of it.  The warps poll in step (a ballot ends the loop)
+  // and the lanes whose flags came up in the same round issue their copies together.  A bulk copy costs about
+  // fifty clocks to issue whatever its size: one per slot, and one per warp for the tails of its 32 slots.
+  if (tid < 32 * warps && !misc->abort) {
+    const bool mine = tid < ns;
+    const int slot = mine ? int(lds_u32(list + 4u * uint32_t(tid))) : 0;
+    const int32_t* flag = slot_flag(ws, slot);
+    const uint32_t bar = bar_addr(c, kBarTail);
+    bool done = !mine;
 #pragma unroll 1
-  for (int k = 0; k < n_merge; ++k) {
-    const MergeReq m = misc->merge[k];
-    // A CTA merges only the request of its first segment (even slot): every CTA then takes part in
-    // at most one merge, and the first writer of a request, which reaches it last, in none.
-    if (m.slot & 1) continue;
-    int32_t* arrived = ws_arrived(ws) + m.counter;
-    int32_t* done = ws_done(ws) + m.counter;
-    // Writers of the request: CTA m.counter, then every following CTA whose range starts before the
-    // request ends and is not empty.  The first writer uses slot 2i+1 unless its range starts with the
-    // request; the others start inside the request, use slot 2i and take part in the merge.  Thread i
-    // looks at CTA i (one thread walking the CTAs cost 6000 clocks of dependent 64-bit arithmetic);
-    // ballots and per-warp counts give every writer its place in the list, in CTA order.
-    static_assert(kMaxCombineSlots <= kThreads, "one thread per CTA of the grid");
-    {
-      const int64_t Tt = misc->walker.Tt;
-      const int64_t end = m.start + m.tiles;
-      bool writer = false, merger = false;
-      if (tid < n && tid >= m.counter) {
-        int64_t lo, nlo;
-        if (Tt * n < (int64_t(1) << 32)) {  // the usual case: 32-bit division
-          lo = int64_t(uint32_t(Tt) * uint32_t(tid) / uint32_t(n));
-          nlo = int64_t(uint32_t(Tt) * uint32_t(tid + 1) / uint32_t(n));
+    for (uint32_t i = 0; i < c.polls; ++i) {
+      const bool now = !done && ld_acquire(flag) == c.gen;  // acquire: the slot's bytes, written before the flag, are read after it
+      if (now) {
+        done = true;
+#ifdef MLA_FP4_TRACE
+        if (int(blockIdx.x) == c.trace_cta && c.status && tid < 128) {
+          unsigned long long t;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+          long long* tr = reinterpret_cast<long long*>(c.status + 8) + ((4 + (tid >> 4)) * 16 + (tid & 15)) * 8;
+          tr[0] = (long long)t;
+          tr[1] = slot;
+        }
+#endif
+        if (fits) {
+          // The copy reads the slot from L2, where its writer's fence put it before the flag: no proxy fence is
+          // needed for that, and a full fence.proxy.async here cost microseconds.
+          ptx::mbar_arrive_expect_tx(bar, share_bytes);
+          ptx::bulk_load(rows + uint32_t(tid) * share_bytes, reinterpret_cast<const char*>(slot_o(ws, slot)) + size_t(U0) * 32, share_bytes, bar);
         } else {
-          lo = cta_lo(Tt, n, tid);
-          nlo = cta_lo(Tt, n, tid + 1);
+          ptx::mbar_arrive(bar);
         }
-        writer = lo < end && nlo > lo && nlo > m.start + kPhantom;  // holds at least one real tile of the request
-        merger = writer && lo >= m.start;
       }
-      const uint32_t bw = __ballot_sync(0xffffffffu, writer), bm = __ballot_sync(0xffffffffu, merger);
-      int* wcount = reinterpret_cast<int*>(scale_s);  // [12][2]; the slot scales are written two barriers later
-      const int warp = tid >> 5;
-      if ((tid & 31) == 0) {
-        wcount[2 * warp] = __popc(bw);
-        wcount[2 * warp + 1] = __popc(bm);
-      }
-      __syncthreads();
-      int before_w = 0, before_m = 0, cnt = 0, part = 0;
-#pragma unroll
-      for (int w = 0; w < kThreads / 32; ++w) {
-        const int cw = wcount[2 * w], cm = wcount[2 * w + 1];
-        if (w < warp) { before_w += cw; before_m += cm; }
-        cnt += cw;
-        part += cm;
-      }
-      const uint32_t below = (1u << (tid & 31)) - 1u;
-      if (writer) {
-        const int pos = before_w + __popc(bw & below);
-        if (pos < kMaxCombineSlots) list_s[pos] = slot_of(tid, merger);
-      }
-      if (tid == int(blockIdx.x)) misc->rank = merger ? before_m + __popc(bm & below) : 0;
-      if (tid == 0) {
-        const int ns = min(cnt, kMaxCombineSlots);
-        MLA_TRACE(3, 1u, 1);
-        misc->n_slots = ns;
-        misc->n_part = part;
-        bool ok = false;  // bounded wait for the other writers
-#pragma unroll 1
-        for (uint32_t i = 0; i < (1u << 22); ++i) {
-          if (ld_acquire(arrived) >= ns) { ok = true; break; }
-          if (misc->abort) break;
-          __nanosleep(32);
-        }
-        if (!ok && !misc->abort) flag_timeout(c, 100 + k, uint32_t(ns));
-      }
+      if (__all_sync(0xffffffffu, done) || misc->abort) break;
+      __nanosleep(64);
     }
-    __syncthreads();
-    const int ns = misc->n_slots, np = misc->n_part, rank = misc->rank;
-    if (tid == 0) MLA_TRACE(3, 1u, 2);
-    if (!misc->abort) {
-      int qpos, head0;
-      group_coords(m.g, p.num_heads, qpos, head0);
-      const int heads_here = min(kGroupHeads, p.num_heads - head0);
-      const size_t row0 = (size_t(m.b) * p.q_len + qpos) * p.num_heads + head0;
-      // This CTA's dims: pairs [256*rank/np, 256*(rank+1)/np).  A unit is (pair of dims, 8 heads, slot
-      // lane); the SL lanes of a unit are consecutive lanes of a warp, split the slots (eight per batch,
-      // all their loads in flight together) and add their sums with a fixed shuffle tree
-      // (bit-reproducible).  Lane 0 of the unit writes 8 x 2 outputs.
-      // (integer quotients through float: the operands are small and never within 1/300 of a boundary)
-      const float rnp = 1.0f / float(np);
-      const int u0 = int((float(256 * rank) + 0.5f) * rnp), u1 = int((float(256 * (rank + 1)) + 0.5f) * rnp);
-      const int d0 = 2 * u0, pairs = u1 - u0;
-      const int og = (heads_here + 7) >> 3;  // 8-head groups that hold heads of this launch
-      const float rog = 1.0f / float(og);
-      const int items = pairs * og;
-      constexpr int kBatch = 8;  // slots whose rows a unit lane has in flight together
-      int SL = 1, lg = 0;
-      while (SL < 32 && kBatch * SL < ns && items * SL * 2 <= kThreads) { SL *= 2; ++lg; }  // one round of threads if possible
-      const int units = items << lg;
-      const char* slot0 = reinterpret_cast<const char*>(slot_o(ws, 0));
-      auto load_batch = [&](const char* src, bool live_unit, int i0, uint4 (&a)[kBatch][2]) {
-#pragma unroll
-        for (int qq = 0; qq < kBatch; ++qq) {
-          const bool ld = live_unit && i0 + qq * SL < ns;  // no load for a slot that does not exist (its list entry is stale)
-          const char* sp = src + size_t(list_s[i0 + qq * SL]) * kSlotBytes;
-          ldcg_v4_if(a[qq][0], sp, ld);
-          ldcg_v4_if(a[qq][1], sp + kGroupHeads * 2, ld);
-        }
-      };
-      // LSEs and slot scales: four lanes per head split the slots; a lane has eight slots' loads in flight
-      // together (one round of latency for up to 32 slots).  They go out first: the weights are computed
-      // while the partial rows, requested right behind them, are still on their way.
-      const bool wlane = tid < 4 * kGroupHeads;
-      const int wh = tid >> 2, wj = tid & 3;
-      float v[8], sc[8];
-      auto load_lse = [&](int i0) {
-#pragma unroll
-        for (int qq = 0; qq < 8; ++qq) {
-          const int i = i0 + 4 * qq;
-          const float* src = slot_lse(ws, list_s[i]);
-          ldcg_f32_if(v[qq], src + wh, i < ns);
-          ldcg_f32_if(sc[qq], src + kGroupHeads, i < ns);  // element 64 is the slot scale
-        }
-      };
-      if (wlane) load_lse(wj);
-      // The first batch of partial rows does not depend on the weights: its loads go out in the same round.
-      uint4 a[kBatch][2];
-      const int base0 = tid & ~31;
-      if (base0 < units) {
-        const int unit = tid;
-        const int item = min(unit, units - 1) >> lg, sl = unit & (SL - 1);
-        const int pr = int((float(item) + 0.5f) * rog), o = item - pr * og;
-        load_batch(slot0 + (size_t(d0 + 2 * pr) * kGroupHeads + 8 * o) * 2, unit < units, sl, a);
-      }
-      // A weight lane keeps the running maximum and leaves the values in shared memory for its own second
-      // pass; butterflies give all four lanes of a head the results.
-      if (tid == 0) MLA_TRACE(3, 1u, 3);
-      if (wlane) {
-        const int h = wh, j = wj;
-        float* col = lse_s + h;
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int i0 = j; i0 < ns; i0 += 32) {
-          if (i0 != j) load_lse(i0);
-#pragma unroll
-          for (int qq = 0; qq < 8; ++qq) {
-            const int i = i0 + 4 * qq;
-            if (i < ns) {
-              col[i * kTailLseStride] = v[qq];
-              scale_s[i] = sc[qq];  // every head's lane writes the same value; a lane reads back only what it wrote
-              mx = fmaxf(mx, v[qq]);
-            }
-          }
-        }
-#pragma unroll
-        for (int off = 2; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-        float dsum = 0.f;
-#pragma unroll 4
-        for (int i = j; i < ns; i += 4) {
-          const float l = col[i * kTailLseStride];
-          const float e = (l == -INFINITY) ? 0.f : ptx::ex2(l - mx);
-          col[i * kTailLseStride] = e;
-          dsum += e;
-        }
-#pragma unroll
-        for (int off = 2; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
-        const float inv = dsum > 0.f ? __frcp_rn(dsum) : 0.f;
-#pragma unroll 4
-        for (int i = j; i < ns; i += 4) col[i * kTailLseStride] *= inv * scale_s[i];  // weights, times the slot's fp16 scale
-        if (j == 0 && rank == 0 && p.lse && h < heads_here) p.lse[row0 + h] = (dsum > 0.f) ? (__log2f(dsum) + mx) : -INFINITY;
-      }
-      __syncthreads();
-      if (tid == 0) MLA_TRACE(3, 1u, 4);
-#pragma unroll 1
-      for (int base = (tid & ~31); base < units; base += kThreads) {
-        const int unit = base + (tid & 31);
-        const bool live_unit = unit < units;
-        const int item = min(unit, units - 1) >> lg, sl = unit & (SL - 1);
-        const int pr = int((float(item) + 0.5f) * rog), o = item - pr * og;
-        const char* src = slot0 + (size_t(d0 + 2 * pr) * kGroupHeads + 8 * o) * 2;
-        const float* wrow = lse_s + 8 * o;
-        float acc[2][8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[0][e] = acc[1][e] = 0.f;
-#pragma unroll 1
-        for (int i0 = sl; i0 < ns; i0 += kBatch * SL) {  // eight slots x two dims: sixteen independent 16-byte loads in flight
-          if (!(base == base0 && i0 == sl)) load_batch(src, live_unit, i0, a);  // the first batch is already here
-#pragma unroll
-          for (int qq = 0; qq < kBatch; ++qq) {
-            const int i = i0 + qq * SL;
-            if (i >= ns) break;  // the remaining slots of the batch do not exist
-            const float* w = wrow + i * kTailLseStride;
-            const float4 w0 = *reinterpret_cast<const float4*>(w), w1 = *reinterpret_cast<const float4*>(w + 4);
-            const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-            for (int dd = 0; dd < 2; ++dd) {
-              const uint32_t u[4] = {a[qq][dd].x, a[qq][dd].y, a[qq][dd].z, a[qq][dd].w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u[e]));
-                acc[dd][2 * e] += wv[2 * e] * f.x;
-                acc[dd][2 * e + 1] += wv[2 * e + 1] * f.y;
-              }
-            }
-          }
-        }
-#pragma unroll 1
-        for (int off = SL >> 1; off > 0; off >>= 1) {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            acc[0][e] += __shfl_down_sync(0xffffffffu, acc[0][e], off);
-            acc[1][e] += __shfl_down_sync(0xffffffffu, acc[1][e], off);
-          }
-        }
-        if (live_unit && sl == 0) {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int h = 8 * o + e;
-            if (h < heads_here) {
-              const size_t idx = (row0 + h) * kLatent + d0 + 2 * pr;
-              if (p.out_dtype == MLA_FP4_OUT_BF16) {
-                __nv_bfloat162 b2 = __floats2bfloat162_rn(acc[0][e], acc[1][e]);
-                *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(p.out) + idx) = *reinterpret_cast<uint32_t*>(&b2);
-              } else if (p.out_dtype == MLA_FP4_OUT_F32) {
-                *reinterpret_cast<float2*>(reinterpret_cast<float*>(p.out) + idx) = make_float2(acc[0][e], acc[1][e]);
-              } else {
-                *reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(p.out) + idx) =
-                    __nv_cvt_float2_to_fp8x2(make_float2(acc[0][e], acc[1][e]), __NV_SATFINITE, __NV_E4M3);
-              }
-            }
-          }
-        }
-      }
-      if (tid == 0) MLA_TRACE(3, 1u, 5);
+    const bool all = __all_sync(0xffffffffu, done);
+    if (!done) {  // the budget ran out (or the CTA is giving up): the barrier still gets this slot's arrival
+      if (!misc->abort) flag_timeout(c, 100, uint32_t(slot));
+      ptx::mbar_arrive(bar);
     }
-    __syncthreads();
-    if (tid == 0) {  // the last CTA through leaves the counters of this request at zero
-      const int old = atomicAdd(done, 1);
-      if (old == np - 1) {
-        *done = 0;
-        *arrived = 0;
+    if ((tid & 31) == 0) {  // the tails of this warp's slots: one contiguous range of the workspace
+      const int first = slot, last = int(lds_u32(list + 4u * uint32_t(min(tid + 31, ns - 1))));
+      if (all && fits) {
+        const uint32_t bytes = uint32_t(last - first + 1) * kTailLseBytes;
+        ptx::mbar_arrive_expect_tx(bar, bytes);
+        ptx::bulk_load(tails + uint32_t(first - s0) * kTailLseBytes, slot_lse(ws, first), bytes, bar);
+      } else {
+        ptx::mbar_arrive(bar);
       }
     }
   }
+  if (tid == 0) MLA_TRACE(3, 1u, 2);
+  const bool landed = wait(c, kBarTail, 0);
+  if (tid == 0) MLA_TRACE(3, 1u, 3);
+  if (landed && !misc->abort) {
+    // weights: four lanes per head split the slots; butterflies give all four the results.  w_i = 2^(lse_i - max) *
+    // slot scale, left in place of the LSE; the division by their sum is one multiply per output at the end.
+    if (tid < 4 * kGroupHeads) {
+      const int h = tid >> 2, j = tid & 3;
+      const uint32_t col = tails + 4u * uint32_t(h);
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int i0 = j; i0 < ns; i0 += 16) {
+        float l[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int i = min(i0 + 4 * q, ns - 1);
+          l[q] = lds_f32(col + uint32_t(int(lds_u32(list + 4u * uint32_t(i))) - s0) * kTailLseBytes);
+        }
+        mx = fmaxf(fmaxf(mx, fmaxf(l[0], l[1])), fmaxf(l[2], l[3]));
+      }
+#pragma unroll
+      for (int off = 2; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      float dsum = 0.f;
+#pragma unroll 1
+      for (int i0 = j; i0 < ns; i0 += 16) {
+        float l[4], sc[4];
+        uint32_t at[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int i = min(i0 + 4 * q, ns - 1);
+          at[q] = uint32_t(int(lds_u32(list + 4u * uint32_t(i))) - s0) * kTailLseBytes;
+          l[q] = lds_f32(col + at[q]);
+          sc[q] = lds_f32(tails + at[q] + 4u * kGroupHeads);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (i0 + 4 * q < ns) {
+            const float e = (l[q] == -INFINITY) ? 0.f : ptx::ex2(l[q] - mx);
+            sts_f32(col + at[q], e * sc[q]);
+            dsum += e;
+          }
+        }
+      }
+#pragma unroll
+      for (int off = 2; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
+      if (j == 0) sts_f32(c.smem + kOffTailInv + 4u * uint32_t(h), dsum > 0.f ? __frcp_rn(dsum) : 0.f);
+      if (j == 0 && rank == 0 && p.lse && h < heads_here) p.lse[row0 + h] = (dsum > 0.f) ? (__log2f(dsum) + mx) : -INFINITY;
+    }
+    __syncthreads();
+    if (tid == 0) MLA_TRACE(3, 1u, 4);
+    // An item is (unit of this CTA's share, pair of heads of the unit's group): 4 bytes per dim and slot.
+    const int items = (U1 - U0) * 4;
+#pragma unroll 1
+    for (int item = tid; item < items; item += kThreads) {
+      const int u = U0 + (item >> 2), hq = item & 3;
+      const int head = 8 * (u >> 8) + 2 * hq, dim = 2 * (u & 255);
+      const uint32_t src = rows + uint32_t(item >> 2) * 32u + 4u * uint32_t(hq);
+      const uint32_t wcol = tails + 4u * uint32_t(head);
+      float a00 = 0.f, a01 = 0.f, a10 = 0.f, a11 = 0.f;  // [dim][head]
+#pragma unroll 1
+      for (int i0 = 0; i0 < ns; i0 += 4) {  // four slots at a time: their loads first; the sums still in slot order
+        uint32_t u0[4], u1[4];
+        float2 wv[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int i = min(i0 + q, ns - 1);
+          u0[q] = lds_u32(src + uint32_t(i) * share_bytes);
+          u1[q] = lds_u32(src + uint32_t(i) * share_bytes + 16u);
+          wv[q] = lds_f32x2(wcol + uint32_t(int(lds_u32(list + 4u * uint32_t(i))) - s0) * kTailLseBytes);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (i0 + q < ns) {  // in slot order: bit-reproducible whatever the order of arrival
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u0[q])), f1 = __half22float2(*reinterpret_cast<const __half2*>(&u1[q]));
+            a00 += wv[q].x * f0.x;
+            a01 += wv[q].y * f0.y;
+            a10 += wv[q].x * f1.x;
+            a11 += wv[q].y * f1.y;
+          }
+        }
+      }
+      const float2 inv = lds_f32x2(c.smem + kOffTailInv + 4u * uint32_t(head));
+      const size_t idx = (row0 + head) * kLatent + dim;
+      if (head < heads_here) store_out_pair(p.out, p.out_dtype, idx, a00 * inv.x, a10 * inv.x);
+      if (head + 1 < heads_here) store_out_pair(p.out, p.out_dtype, idx + kLatent, a01 * inv.y, a11 * inv.y);
+    }
+    if (tid == 0) MLA_TRACE(3, 1u, 5);
+  }
+  __syncthreads();
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1176,6 +1242,10 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   }
   c.misc = reinterpret_cast<Misc*>(c.smem_ptr + kOffMisc);
   c.status = p.status;
+  c.polls = p.wait_polls;
+  // The generation of this step: one more than that of the last completed step.  No CTA of this step
+  // can have advanced it yet (that takes every CTA of the grid to have finished).
+  c.gen = p.fused_merge ? ld_acquire(ws_generation(p.workspace)) + 1 : 0;
 #ifdef MLA_FP4_TRACE
   c.trace_cta = (p.status && p.status[7] >= 0 && p.status[7] < int(gridDim.x) && p.status[7] != 0) ? p.status[7] : int(gridDim.x) - 1;
 #endif
@@ -1183,7 +1253,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   const int warp = tid >> 5;
 
   if (warp == 0) {
-    Walker w = make_walker(p.seq_lens, p.batch, p.groups, blockIdx.x, gridDim.x);
+    Walker w = make_walker(p.seq_lens, p.batch, p.seq_cap, p.groups, blockIdx.x, gridDim.x);
     if (tid == 0) {
       c.misc->walker = w;
       c.misc->abort = 0;
@@ -1222,12 +1292,15 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   if (tid == 0) MLA_TRACE(3, 0u, 0);
 #ifdef MLA_FP4_TRACE
   auto gtimer = [] { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
-  unsigned long long* cta_times = p.status ? reinterpret_cast<unsigned long long*>(p.status + 8) + 12 * 16 * 8 + 3 * blockIdx.x : nullptr;
+  unsigned long long* cta_times = p.status ? reinterpret_cast<unsigned long long*>(p.status + 8) + 12 * 16 * 8 + 4 * blockIdx.x : nullptr;
   if (tid == 0 && cta_times) cta_times[0] = gtimer();
 #endif
   // Let a dependent kernel (the split-KV combine) start its launch and prologue early; it still waits
   // for this whole grid before it reads the partial slots.
   if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  // the PV issue warps have nothing to do until the first P is there: one of them makes the merge plan meanwhile
+  if (warp == kWarpPV2 && p.fused_merge) plan_merge(c, tid & 31);
 
   RoleState st;
   st.it = 0;
@@ -1276,6 +1349,14 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
 #ifdef MLA_FP4_TRACE
     if (tid == 0 && cta_times) cta_times[2] = gtimer();
 #endif
+    // The last CTA to finish advances the generation: the next step's flags differ from all of this one's.
+    if (tid == 0) {
+      __threadfence();
+      if (atomicAdd(ws_finished(p.workspace), 1) == int(gridDim.x) - 1) {
+        *ws_finished(p.workspace) = 0;
+        st_release(ws_generation(p.workspace), c.gen);
+      }
+    }
   }
 }
 
@@ -1356,14 +1437,14 @@ cudaError_t launch_decode_sm100(const DecodeParams& p, int num_ctas, cudaStream_
     }
   }
   {
-    static bool attr_done[64] = {};
+    static std::atomic<bool> attr_done[64];  // zero-initialised; setting the attribute twice is harmless
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+    if (dev < 0 || dev >= 64 || !attr_done[dev].load(std::memory_order_acquire)) {
       e = cudaFuncSetAttribute(mla_fp4_decode_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemAlloc));
       if (e != cudaSuccess) return e;
-      if (dev >= 0 && dev < 64) attr_done[dev] = true;
+      if (dev >= 0 && dev < 64) attr_done[dev].store(true, std::memory_order_release);
     }
   }
   cudaLaunchConfig_t cfg = {};

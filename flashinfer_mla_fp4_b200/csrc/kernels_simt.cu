@@ -2,8 +2,8 @@
 //   * merge_partials_kernel- context-parallel merge of per-rank partial outputs + LSE
 //   * fp32_check_kernel    - plain-FP32 decode over the same work partition; a slow, exact-
 //                            arithmetic cross-check of the tcgen05 kernel used by tests
-//   * dequant_kernel       - E2M1 -> E4M3 byte dequantisation (same device routine as the
-//                            tcgen05 kernel), for the bit-exact table test
+//   * dequant_kernel       - E2M1 -> E4M3 byte dequantisation (the routine fp32_check_kernel uses), for the
+//                            bit-exact table test; the tcgen05 kernel hands the packed codes to the MMA unchanged
 #include "common.cuh"
 #include "dequant.cuh"
 #include "launch.h"
@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(256) fp32_check_kernel(DecodeParams p) {
 
   const int tid = threadIdx.x;
   if (tid < 32) {
-    Walker w = make_walker(p.seq_lens, p.batch, p.groups, blockIdx.x, gridDim.x);
+    Walker w = make_walker(p.seq_lens, p.batch, p.seq_cap, p.groups, blockIdx.x, gridDim.x);
     if (tid == 0) s_walker = w;
   }
   __syncthreads();
@@ -113,6 +113,10 @@ __global__ void __launch_bounds__(256) fp32_check_kernel(DecodeParams p) {
         if (t < nt) {
           int tok = t0 + t;
           int page = p.block_tables[size_t(s.b) * p.block_table_stride + tok / p.page_size];
+          if (page < 0 || page >= p.num_pages) {  // a page id outside the pool: report it, read page 0 instead
+            if (p.status) atomicCAS(p.status, 0, MLA_FP4_ERR_DEVICE_TIMEOUT);
+            page = 0;
+          }
           size_t rowi = size_t(page) * p.page_size + tok % p.page_size;
           uint32_t word = *reinterpret_cast<const uint32_t*>(cache + rowi * kRowBytes + 4 * wv);
           if (wv < kLatent / 8) {
@@ -215,8 +219,8 @@ __global__ void __launch_bounds__(256) fp32_check_kernel(DecodeParams p) {
 #pragma unroll
       for (int h = 0; h < kGroupHeads; ++h) {
         float inv = p.output_scale / l_s[h] / sscale;
-        so[size_t(tid) * kGroupHeads + h] = __float2half_rn(o0[h] * inv);
-        so[size_t(tid + 256) * kGroupHeads + h] = __float2half_rn(o1[h] * inv);
+        so[slot_o_index(tid, h)] = __float2half_rn(o0[h] * inv);
+        so[slot_o_index(tid + 256, h)] = __float2half_rn(o1[h] * inv);
       }
       if (tid == 0) slot_scale(p.workspace, s.slot)[0] = sscale;
       if (tid < kGroupHeads) slot_lse(p.workspace, s.slot)[tid] = log2f(l_s[tid]) + m_s[tid];

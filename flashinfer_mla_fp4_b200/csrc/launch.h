@@ -23,6 +23,8 @@ struct DecodeParams {
   int32_t out_dtype;
   int32_t pdl;
   int32_t fused_merge;  // the decode kernel merges the split-KV partials itself (cooperative launch)
+  int32_t seq_cap;      // most tokens a request may have: block-table width * page_size (INT_MAX when not given)
+  uint32_t wait_polls;  // poll budget of every bounded wait
 };
 
 struct CombineParams {
@@ -31,6 +33,7 @@ struct CombineParams {
   void* out;
   float* lse;
   int32_t batch, q_len, num_heads, groups, num_ctas, out_dtype, pdl;
+  int32_t seq_cap;  // as in DecodeParams
 };
 
 cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);

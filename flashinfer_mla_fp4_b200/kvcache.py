@@ -90,6 +90,10 @@ def write_tokens(
     if kv_cache_sf.numel() != num_slots:
         raise ValueError("kv_cache_sf must hold one scale per cache row")
     tokens = latent.shape[0]
+    for name, t in (("rope", rope), ("kv_cache", kv_cache), ("kv_cache_sf", kv_cache_sf), ("slot_mapping", slot_mapping),
+                    ("token_scale", token_scale)):
+        if t is not None and (not t.is_cuda or t.device != latent.device):
+            raise ValueError(f"{name} must be a CUDA tensor on the device of latent ({latent.device}), got {t.device}")
     if slot_mapping is not None:
         if slot_mapping.dtype != torch.int64 or slot_mapping.numel() != tokens or not slot_mapping.is_contiguous():
             raise ValueError("slot_mapping must be a contiguous int64 tensor [T]")
@@ -105,58 +109,3 @@ def write_tokens(
             slot_mapping.data_ptr() if slot_mapping is not None else None,
             tokens, kv_cache.data_ptr(), kv_cache_sf.data_ptr(), num_slots,
             torch.cuda.current_stream(latent.device).cuda_stream))
-
-
-def _bench_writer(tokens: int, reps: int, profile_only: bool) -> None:
-    """Time write_tokens on `tokens` bf16 tokens (inputs and cache larger than L2) and print one JSON line."""
-    import json
-    import statistics
-    from pathlib import Path
-
-    dev = torch.device("cuda:0")
-    page_size = 64
-    pages = (tokens + page_size - 1) // page_size
-    g = torch.Generator(device=dev).manual_seed(1234)
-    latent = torch.randn(tokens, LATENT_DIM, generator=g, device=dev, dtype=torch.float32).bfloat16()
-    rope = torch.randn(tokens, ROPE_DIM, generator=g, device=dev, dtype=torch.float32).bfloat16()
-    slots = torch.randperm(pages * page_size, generator=g, device=dev)[:tokens].contiguous()
-    cache = torch.empty(pages, page_size, ROW_BYTES, dtype=torch.uint8, device=dev)
-    sf = torch.empty(pages, page_size, 1, dtype=torch.float32, device=dev)
-    for _ in range(3):
-        write_tokens(latent, rope, slots, cache, sf)
-    torch.cuda.synchronize()
-    if profile_only:
-        print(json.dumps({"profile": "cache_write", "tokens": tokens}))
-        return
-    times = []
-    for _ in range(reps):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        write_tokens(latent, rope, slots, cache, sf)
-        e1.record()
-        torch.cuda.synchronize()
-        times.append(e0.elapsed_time(e1) * 1e-3)
-    t = statistics.median(times)
-    bytes_per_token = HEAD_DIM_QK * 2 + BYTES_PER_TOKEN + 8  # bf16 inputs, cache row + scale, slot id
-    peak = 6650.0
-    kind = "fallback"
-    peaks_file = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
-    if peaks_file.exists():
-        peak, kind = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured"
-    achieved = tokens * bytes_per_token / t / 1e9
-    print(json.dumps({"metric": "fp4_cache_write_tokens_per_s", "value": tokens / t, "unit": "tokens/s", "tokens": tokens,
-                      "us": t * 1e6, "dtype": "bf16->e2m1/e4m3",
-                      "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                                   "peak_kind": kind, "algorithmic_bytes_per_token": bytes_per_token},
-                      "l2": f"cold by size: {tokens * bytes_per_token / 2**20:.0f} MiB touched per call"}))
-
-
-if __name__ == "__main__":
-    import argparse
-
-    ap = argparse.ArgumentParser(description="time the CUDA cache writer (one JSON line)")
-    ap.add_argument("--tokens", type=int, default=1 << 20)
-    ap.add_argument("--reps", type=int, default=10)
-    ap.add_argument("--profile-only", action="store_true", help="three warm-up calls and exit (the command line for ncu)")
-    a = ap.parse_args()
-    _bench_writer(a.tokens, a.reps, a.profile_only)

@@ -15,6 +15,7 @@ Additions over the reference (all opt-in, defaults keep the reference behaviour)
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional, Tuple, Union
 
 import torch
@@ -51,6 +52,7 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         self._status: Optional[torch.Tensor] = None
         self._num_ctas = 0
         self._phase_mask = 0  # profiling aid of the two-kernel mode: 1 = decode kernel only, 2 = combine kernel only
+        self._wait_polls = 0  # 0 = the library's default poll budget of a bounded device wait
 
     # ------------------------------------------------------------------ plan
     @api_logged
@@ -107,7 +109,7 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         self._planned = True
 
     def _init_workspace(self) -> None:
-        """Zero the workspace's counter header (every completed step leaves it zero again)."""
+        """Zero the workspace's header (generation and slot flags of the split-KV merge)."""
         if self._workspace_buffer.is_cuda and self._workspace_buffer.numel() >= _cabi.WORKSPACE_HEADER_BYTES:
             with torch.cuda.device(self._device):
                 _cabi.workspace_init(self._workspace_buffer.data_ptr(), self._workspace_buffer.numel(),
@@ -185,10 +187,19 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         batch_size, q_len, num_heads, _ = q.shape
         if block_tables.shape[0] != batch_size or seq_lens.shape[0] != batch_size:
             raise ValueError("block_tables and seq_lens must have one row per request")
+        if max_seq_len > block_tables.shape[1] * self._page_size:
+            raise ValueError(f"max_seq_len={max_seq_len} exceeds what block_tables can address "
+                             f"({block_tables.shape[1]} pages of {self._page_size} tokens)")
+        if os.environ.get("MLA_FP4_VALIDATE", "0") not in ("", "0"):
+            validate_page_ids(block_tables, seq_lens, self._page_size, kv_cache.shape[0])
         need = _cabi.workspace_bytes(batch_size, q_len, num_heads, self._num_ctas)
         if self._workspace_buffer.numel() < need:
             raise ValueError(f"workspace_buffer has {self._workspace_buffer.numel()} bytes, but {need} are required")
 
+        # every pointer handed to the kernels must be a device pointer of q's device
+        for name, t in (("block_tables", block_tables), ("seq_lens", seq_lens), ("out", out)):
+            if t is not None and (not t.is_cuda or t.device != q.device):
+                raise ValueError(f"{name} must be a CUDA tensor on the device of q ({q.device}), got {t.device}")
         if out is None:
             out = torch.empty((batch_size, q_len, num_heads, self._kv_lora_rank), dtype=self._o_dtype, device=q.device)
         elif tuple(out.shape) != (batch_size, q_len, num_heads, self._kv_lora_rank) or not out.is_contiguous():
@@ -219,8 +230,11 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         a.num_ctas = self._num_ctas
         a.enable_pdl = 1 if self._enable_pdl else 0
         a.phase_mask = self._phase_mask
-        a.stream = torch.cuda.current_stream(q.device).cuda_stream
-        _cabi.check(_cabi.lib.mla_fp4_decode(C.byref(a)))
+        a.max_pages_per_request = block_tables.shape[1]
+        a.wait_polls = self._wait_polls
+        with torch.cuda.device(q.device):
+            a.stream = torch.cuda.current_stream(q.device).cuda_stream
+            _cabi.check(_cabi.lib.mla_fp4_decode(C.byref(a)))
         if return_lse:
             return out, lse
         return out
@@ -236,10 +250,34 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         st = self.device_status()
         if st[0] != 0:
             self._status.zero_()
-            self._init_workspace()  # a step that timed out may have left the merge counters non-zero
+            self._init_workspace()  # start from a clean header after a step that gave up on a wait
             raise RuntimeError(
                 f"mla_fp4 device error {st[0]} (barrier {st[1]}, CTA {st[2]}, thread {st[3]}, parity {st[4]})"
             )
 
 
-__all__ = ["BatchMLADecodeCuteDSLFP4Wrapper"]
+def validate_page_ids(block_tables: torch.Tensor, seq_lens: torch.Tensor, page_size: int, num_pages: int) -> None:
+    """Debug check (``MLA_FP4_VALIDATE=1``; synchronises): every block-table entry a step will read is a page of the pool.
+
+    The kernels read entries ``[0, ceil(seq_len / page_size))`` of each row and nothing beyond
+    (the reference reads the ids unchecked: flashinfer ``roles/mla_loader_fp8.py:185-210``).
+    Raises ``ValueError`` naming the first offending request.
+    """
+    lens = seq_lens.detach().to("cpu", torch.int64)
+    bt = block_tables.detach().to("cpu")
+    width = bt.shape[1]
+    for b in range(bt.shape[0]):
+        n = int(lens[b])
+        if n <= 0:
+            continue
+        used = -(-n // page_size)
+        if used > width:
+            raise ValueError(f"request {b}: seq_len {n} needs {used} pages but block_tables has {width} per request")
+        row = bt[b, :used]
+        bad = (row < 0) | (row >= num_pages)
+        if bool(bad.any()):
+            i = int(bad.nonzero()[0])
+            raise ValueError(f"request {b}: block_tables[{b}, {i}] = {int(row[i])} is outside the pool of {num_pages} pages")
+
+
+__all__ = ["BatchMLADecodeCuteDSLFP4Wrapper", "validate_page_ids"]

@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define MLA_FP4_ABI_VERSION 3
+#define MLA_FP4_ABI_VERSION 4
 
 /* status codes */
 #define MLA_FP4_OK 0
@@ -48,9 +48,11 @@ extern "C" {
 #define MLA_FP4_KERNEL_TCGEN05_2PASS 2   /* the tcgen05 kernel followed by a separate combine
                                             kernel (the reference's two-kernel structure)      */
 
-/* The workspace starts with this many bytes of counters that must be zero before the first
-   decode step on that workspace (mla_fp4_workspace_init) and that every completed step leaves
-   zero; the split-KV partial slots follow. */
+/* The workspace starts with a header of this many bytes: the generation of the last decode step
+   that ran on it and one flag per split-KV partial slot (the generation that last published the
+   slot).  It must be zero before the first decode step on that workspace
+   (mla_fp4_workspace_init); steps keep it consistent by themselves afterwards, also a step that
+   reported MLA_FP4_ERR_DEVICE_TIMEOUT, as long as its kernel returned.  The partial slots follow. */
 #define MLA_FP4_WORKSPACE_HEADER_BYTES 2048
 
 /* input element types of mla_fp4_cache_write */
@@ -103,6 +105,13 @@ typedef struct MlaFp4DecodeArgs {
   int32_t phase_mask;  /* two-kernel modes only: 0 = decode + combine; 1 = decode kernel only;
                           2 = combine kernel only (profiling) */
   void* stream;        /* cudaStream_t */
+  /* Width of a block-table row in pages (block_tables.shape[1]).  The kernels never read a row
+     beyond it: a seq_lens entry larger than max_pages_per_request * page_size is treated as
+     that many tokens.  0 = not given (rows are trusted to cover seq_lens). */
+  int32_t max_pages_per_request;
+  /* Poll budget of every bounded device-side wait (0 = the default, 2^22).  When a wait runs
+     out the kernel records MLA_FP4_ERR_DEVICE_TIMEOUT in the status words and returns. */
+  int32_t wait_polls;
 } MlaFp4DecodeArgs;
 
 /* ABI version of the loaded library (== MLA_FP4_ABI_VERSION of the header it was built from). */
@@ -129,7 +138,7 @@ int mla_fp4_plan_partition(const int32_t* seq_lens_host, int32_t batch, int32_t 
                            int32_t* seg_tile_begin, int32_t* seg_tile_end, int32_t* seg_slot,
                            int32_t* num_segments);
 
-/* Zero the counter header of a workspace (an asynchronous memset on `stream`).  Call once after
+/* Zero the header of a workspace (an asynchronous memset on `stream`).  Call once after
    allocating the workspace, and again after a step that reported MLA_FP4_ERR_DEVICE_TIMEOUT.
    The reference's workspace needs no preparation (wrappers/batch_mla_fp4.py:413-420). */
 int mla_fp4_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
@@ -153,8 +162,9 @@ int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, i
                            int32_t out_dtype, float* lse, void* stream);
 
 /* Bit-exact E2M1 nibble -> E4M3 byte dequantisation of `n_bytes` packed bytes on the device
-   (out holds 2*n_bytes E4M3 bytes, low nibble first), using the same device routine as the
-   decode kernel.  Pins the table of tests/test_cute_dsl_mla_fp4.py:80-84. */
+   (out holds 2*n_bytes E4M3 bytes, low nibble first).  Pins the table of
+   tests/test_cute_dsl_mla_fp4.py:80-84.  (The decode kernel itself hands the packed codes to the
+   tensor core unchanged; this is the routine of the FP32 cross-check kernel.) */
 int mla_fp4_dequant_e2m1_to_e4m3(const void* packed, void* out, int64_t n_bytes, void* stream);
 
 /* Write `num_tokens` tokens into the paged cache (the producer of the format mla_fp4_decode reads):
@@ -192,11 +202,19 @@ int mla_fp4_cache_write(const void* latent, int64_t latent_stride, const void* r
    - The first call on a device looks the scratch address up once (with that device current) and
      keeps it; make that first call before any stream capture begins.
    - All calls on a device share the one scratch array.  It keeps the previous call's partials, which
-     is harmless: a step only reads the slots it has just written.  Its counter header starts at
-     zero (static storage) and every completed step leaves it zero.
+     is harmless: a step only reads slots whose flag carries its own generation.  Its header starts
+     at zero (static storage) and every step whose kernel returns leaves it consistent, a step that
+     reported MLA_FP4_ERR_DEVICE_TIMEOUT included.  Should a kernel ever be torn down half-way (a
+     sticky CUDA error in the process), mla_fp4_static_reset puts the header back to zero.
      Two calls whose kernels overlap on the GPU (different streams) would overwrite each other's
      partials: run them in order on one stream, or use mla_fp4_decode with separate workspaces. */
 int mla_fp4_decode_static(const MlaFp4DecodeArgs* args);
+
+/* No counterpart in the reference.  Zero the header of the built-in scratch of mla_fp4_decode_static
+   on the current device (an asynchronous memset on `stream`; allocates nothing).  The caller cannot
+   reach that array with mla_fp4_workspace_init, since its address never leaves the library.  Needed
+   only after a decode kernel did not run to its end; harmless at any other time between steps. */
+int mla_fp4_static_reset(void* stream);
 
 #ifdef __cplusplus
 }

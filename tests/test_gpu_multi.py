@@ -33,19 +33,22 @@ def _cp_worker(rank: int, world: int, port: int, tmp: str) -> None:
         from flashinfer_mla_fp4_b200.distributed import ContextParallelDecoder, shard_context
         from oracle import mla_fp4_oracle as O
 
-        # every rank builds the same global case (same seed), then keeps only its shard's page lists
-        case = synth.build_case("cp", [5000, 130, 64, 1, 9000, 777], 64, 64, seed=31, device=dev)
-        bt, sl = shard_context(case.block_tables, case.seq_lens, case.page_size, rank, world)
+        # every rank builds the same global case (same seed), then keeps only its shard's page lists:
+        # a ragged batch with shards that are empty on one rank, and the shape of the context-parallel
+        # benchmark configuration (B=8, H=64) at 4096 tokens per rank
         w = BatchMLADecodeCuteDSLFP4Wrapper(torch.empty(64 << 20, dtype=torch.int8, device=dev))
-        w.plan(num_heads=case.num_heads, page_size=case.page_size)
         cp = ContextParallelDecoder(w, dist.group.WORLD)
-        out, lse = cp.run(case.q, case.kv_cache, bt, sl, case.max_seq_len, case.softmax_scale,
-                          kv_cache_sf=case.kv_cache_sf, return_lse=True)
-        torch.cuda.synchronize()
-        ref, ref_lse = O.mla_decode(case.q, case.kv_cache, case.kv_cache_sf, case.block_tables, case.seq_lens,
-                                    case.softmax_scale)
-        O.assert_parity(out, ref, f"cp rank {rank}")
-        torch.testing.assert_close(lse.cpu(), ref_lse, atol=2e-3, rtol=1e-4)
+        for name, lens, seed in (("cp_ragged", [5000, 130, 64, 1, 9000, 777], 31), ("cp_b8", [4096 * world] * 8, 32)):
+            case = synth.build_case(name, lens, 64, 64, seed=seed, device=dev)
+            bt, sl = shard_context(case.block_tables, case.seq_lens, case.page_size, rank, world)
+            w.plan(num_heads=case.num_heads, page_size=case.page_size)
+            out, lse = cp.run(case.q, case.kv_cache, bt, sl, case.max_seq_len, case.softmax_scale,
+                              kv_cache_sf=case.kv_cache_sf, return_lse=True)
+            torch.cuda.synchronize()
+            ref, ref_lse = O.mla_decode(case.q, case.kv_cache, case.kv_cache_sf, case.block_tables, case.seq_lens,
+                                        case.softmax_scale)
+            O.assert_parity(out, ref, f"{name} rank {rank}")
+            torch.testing.assert_close(lse.cpu(), ref_lse, atol=2e-3, rtol=1e-4)
         Path(tmp, f"ok{rank}").write_text("ok")
     finally:
         dist.destroy_process_group()

@@ -249,9 +249,87 @@ def test_e4m3_output(kernel):
     assert (got[2] == 0).all()  # the empty request
 
 
+@pytest.mark.parametrize("config", ["northstar", "varlen", "spec"])
+def test_benchmark_configs_at_full_size_against_the_oracle(config):
+    """The benchmark configurations at their stated sizes, tcgen05 kernel against the CPU oracle on the same
+    seeded inputs: B=8 H=64 KV=32768; B=128 log-uniform 128..32768 with Student-t latents; B=2 H=128 q_len=2
+    KV=131072.  The oracle needs a second or so for each on the box's cores."""
+    from flashinfer_mla_fp4_b200 import synth
+
+    check_case(synth.config_case(config, device=_dev()), "tcgen05")
+
+
+@pytest.mark.parametrize("page_size", [8, 64])
+def test_product_path_decodes_every_e2m1_code_exactly(page_size):
+    """The packed codes go from the cache to the tensor core untouched (a 4-bit tensor map, no software
+    dequantisation), so the product path needs its own pin of the E2M1 table, the nibble order and the
+    sign bit: one token whose 512 nibbles cycle through all 16 codes, a power-of-two scale, FP32 output.
+    With a single token the softmax weight is 1 and every head's output row must equal scale x value of
+    each code to FP32 rounding; a wrong code, sign or nibble position is off by 25 % or more."""
+    dev = _dev()
+    from flashinfer_mla_fp4_b200 import synth
+
+    heads = 64
+    scale = 0.25
+    codes = (torch.arange(512) * 7 + 3) % 16           # every code, in an order that differs between neighbours
+    row = torch.zeros(320, dtype=torch.uint8)
+    row[:256] = (codes[0::2] | (codes[1::2] << 4)).to(torch.uint8)   # low nibble = even element
+    row[256:] = torch.randint(0, 120, (64,), dtype=torch.uint8)      # finite E4M3 RoPE bytes
+    pages = 3
+    cache = torch.randint(0, 256, (pages, page_size, 320), dtype=torch.uint8)
+    cache[1, 0] = row
+    sf = torch.full((pages, page_size, 1), 7.0)
+    sf[1, 0, 0] = scale
+    q = torch.randn(1, 1, heads, 576, generator=torch.Generator().manual_seed(5)).to(torch.float8_e4m3fn)
+    case = synth.DecodeCase("codes", q.to(dev), cache.to(dev), sf.to(dev), torch.tensor([[1]], dtype=torch.int32, device=dev),
+                            torch.tensor([1], dtype=torch.int32, device=dev), page_size, heads, 1, 1.0 / 512 ** 0.5, 0, [1])
+    out, _ = run_case(case, "tcgen05", out_dtype=torch.float32)
+    expect = torch.from_numpy(O.e2m1_decode_table())[codes] * scale
+    got = out[0, 0].cpu()
+    assert got.shape == (heads, 512)
+    torch.testing.assert_close(got, expect.expand(heads, 512), rtol=1e-5, atol=0)
+
+
+def test_a_wait_that_runs_out_is_reported_and_recovered_from():
+    """The failure path, made on the host, with nothing that faults: one block-table entry of a split request
+    names a page outside the pool.  The kernel never turns such an id into an address, so that tile's copy is
+    never issued, its barrier never completes and the bounded wait (a small poll budget here) runs out: the
+    CTA records MLA_FP4_ERR_DEVICE_TIMEOUT, stops issuing, drains and returns; the CTAs that wait for its
+    partial give up the same way.  check_device_status() must raise and re-initialise the workspace header,
+    and the next step with the entry repaired must equal the step before the damage."""
+    from flashinfer_mla_fp4_b200 import BatchMLADecodeCuteDSLFP4Wrapper, _cabi, synth
+
+    dev = _dev()
+    case = synth.build_case("timeout", [3000, 5000], 64, 64, seed=21, device=dev)  # both requests are split across CTAs
+    ws = torch.empty(64 << 20, dtype=torch.int8, device=dev)
+    w = BatchMLADecodeCuteDSLFP4Wrapper(ws)
+    w.plan(num_heads=case.num_heads, page_size=case.page_size)
+
+    def step(bt):
+        return w.run(case.q, case.kv_cache, bt, case.seq_lens, case.max_seq_len, case.softmax_scale, kv_cache_sf=case.kv_cache_sf)
+
+    good = step(case.block_tables).clone()
+    torch.cuda.synchronize()
+    w.check_device_status()
+    bad_bt = case.block_tables.clone()
+    bad_bt[1, 40] = case.kv_cache.shape[0] + 5
+    w._wait_polls = 2000
+    step(bad_bt)
+    torch.cuda.synchronize()
+    assert w.device_status()[0] == _cabi.ERR_DEVICE_TIMEOUT
+    with pytest.raises(RuntimeError, match="device error 5"):
+        w.check_device_status()
+    assert w.device_status()[0] == 0
+    w._wait_polls = 0
+    out = step(case.block_tables)
+    torch.cuda.synchronize()
+    w.check_device_status()
+    assert torch.equal(out, good)
+
+
 def test_full_size_properties_north_star():
-    """BASELINE's full size (B=8, H=64, KV=32768; too large for the CPU oracle inside a test): the tensor-core
-    kernel against the exact-FP32 GPU kernel over the same partition (itself pinned to the oracle above), and
+    """B=8, H=64, KV=32768 once more (the oracle comparison at this size is the test above): the tensor-core
+    kernel against the exact-FP32 GPU kernel over the same partition, as a second opinion, and
     two properties that hold at any size: the result does not depend on where the pages live in the pool
     (bit-identical after a physical page permutation) nor, beyond rounding, on how many CTAs share the work."""
     from flashinfer_mla_fp4_b200 import BatchMLADecodeCuteDSLFP4Wrapper, synth

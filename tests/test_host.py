@@ -22,7 +22,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in the header but not exported"
     assert set(_cabi.EXPORTS) == declared
-    assert lib.mla_fp4_abi_version() == _cabi.ABI_VERSION == 3
+    assert lib.mla_fp4_abi_version() == _cabi.ABI_VERSION == 4
 
 
 def test_abi_rejects_bad_arguments_without_a_gpu():
@@ -32,7 +32,7 @@ def test_abi_rejects_bad_arguments_without_a_gpu():
     assert "null" in _cabi.last_error()
     n = ctypes.c_size_t(0)
     assert _cabi.lib.mla_fp4_workspace_bytes(8, 1, 64, 148, ctypes.byref(n)) == 0
-    assert n.value == 2048 + 2 * 148 * (512 * 64 * 2 + 64 * 4 + 16)  # counter header + two slots per CTA
+    assert n.value == 2048 + 2 * 148 * (512 * 64 * 2 + 64 * 4 + 16)  # header (generation, slot flags) + two slots per CTA
     assert _cabi.lib.mla_fp4_workspace_init(None, 4096, None) == _cabi.ERR_BAD_ARG
     assert _cabi.lib.mla_fp4_cache_write(None, 512, None, 64, 0, None, None, 4, None, None, 16, None) == _cabi.ERR_BAD_ARG
     assert _cabi.lib.mla_fp4_cache_write(None, 512, None, 64, 0, None, None, 0, None, None, 16, None) == 0  # nothing to write
@@ -180,6 +180,52 @@ def test_wrapper_run_validation(monkeypatch):
     small.__dict__.update({k: v for k, v in w.__dict__.items() if k != "_workspace_buffer"})
     with pytest.raises(ValueError, match="are required"):
         small.run(**ok)
+
+
+def test_wrapper_rejects_host_tensors_before_any_launch(monkeypatch):
+    """Every pointer the kernels dereference must be a device pointer of q's device: a host (or other-device)
+    block table, seq_lens or out would be read as a device address.  The checks run before the C call."""
+    import flashinfer_mla_fp4_b200.wrapper as W
+    from flashinfer_mla_fp4_b200 import _cabi, synth
+
+    w = _planned_cpu_wrapper(monkeypatch)
+    c = synth.config_case("small")
+    called = []
+    monkeypatch.setattr(_cabi.lib, "mla_fp4_decode", lambda *a: called.append(a) or 0, raising=False)
+    # on this GPU-less host every tensor is a host tensor: the first one the kernels would dereference is refused
+    with pytest.raises(ValueError, match="block_tables must be a CUDA tensor"):
+        w.run(c.q, c.kv_cache, c.block_tables, c.seq_lens, 256, c.softmax_scale, kv_cache_sf=c.kv_cache_sf)
+    assert not called
+    # a sequence longer than the block table can address is refused on the host
+    monkeypatch.setattr(torch.Tensor, "is_cuda", property(lambda self: True))
+    with pytest.raises(ValueError, match="exceeds what block_tables can address"):
+        w.run(c.q, c.kv_cache, c.block_tables, c.seq_lens, 64 * c.block_tables.shape[1] + 1, c.softmax_scale,
+              kv_cache_sf=c.kv_cache_sf)
+    assert not called
+
+
+def test_write_tokens_rejects_host_tensors():
+    from flashinfer_mla_fp4_b200.kvcache import write_tokens
+
+    lat, rope = torch.zeros(4, 512, dtype=torch.bfloat16), torch.zeros(4, 64, dtype=torch.bfloat16)
+    cache, sf = torch.zeros(1, 64, 320, dtype=torch.uint8), torch.zeros(1, 64, 1)
+    with pytest.raises(ValueError, match="CUDA"):
+        write_tokens(lat, rope, torch.arange(4), cache, sf)
+
+
+def test_page_id_validator():
+    """MLA_FP4_VALIDATE=1 makes run() check, on the host, every block-table entry a step will read."""
+    from flashinfer_mla_fp4_b200.wrapper import validate_page_ids
+
+    bt = torch.tensor([[0, 1, 2, 99], [3, 4, -7, 5]], dtype=torch.int32)
+    validate_page_ids(bt, torch.tensor([192, 128]), 64, 6)          # entries beyond ceil(seq_len / page) are never read
+    validate_page_ids(bt, torch.tensor([0, 1]), 64, 6)
+    with pytest.raises(ValueError, match=r"block_tables\[0, 3\] = 99"):
+        validate_page_ids(bt, torch.tensor([193, 128]), 64, 100 - 1)
+    with pytest.raises(ValueError, match=r"block_tables\[1, 2\] = -7"):
+        validate_page_ids(bt, torch.tensor([10, 129]), 64, 6)
+    with pytest.raises(ValueError, match="needs 5 pages"):
+        validate_page_ids(bt, torch.tensor([257, 1]), 64, 200)
 
 
 def test_partition_charges_phantom_tiles_for_a_request_start():

@@ -4,8 +4,10 @@ Some callers cannot allocate device memory or lend a workspace: a plugin inside 
 pool owns the device, worker threads on which cudaMalloc is forbidden, a step that must still run when
 the allocator is exhausted.  For them the library carries its own scratch array.  This test calls the
 entry point through the C ABI, twice in a row on the same stream (the second call finds the first call's
-partials still in the scratch), and compares with mla_fp4_decode on the same inputs.  It lives in its
-own file, collected last, and does not depend on what ran before it.
+partials still in the scratch), and compares with mla_fp4_decode on the same inputs and with the CPU
+oracle; between two further steps it zeroes the scratch header with mla_fp4_static_reset, the way back
+after a kernel that did not run to its end.  It lives in its own file, collected last, and does not
+depend on what ran before it.
 """
 import ctypes as C
 
@@ -68,6 +70,23 @@ def test_static_scratch_entry_point_matches_regular_entry_point():
         assert (out.float() - ref_out.float()).abs().max() <= 2e-2 * rms
         torch.testing.assert_close(lse, ref_lse, atol=2e-3, rtol=1e-4)
         assert torch.isfinite(out).all()
+        # and against the CPU oracle, with the tolerance of the parity tests
+        from oracle import mla_fp4_oracle as O
+
+        want, want_lse = O.mla_decode(case.q, case.kv_cache, case.kv_cache_sf, case.block_tables, case.seq_lens,
+                                      case.softmax_scale)
+        O.assert_parity(out, want, f"static/{case.name}")
+        torch.testing.assert_close(lse.cpu(), want_lse, atol=2e-3, rtol=1e-4)
+
+    # the reset entry point: header back to zero (generation restarts), the next static step is still right
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    first = out.clone()
+    _cabi.check(_cabi.lib.mla_fp4_static_reset(stream))
+    out.zero_()
+    _cabi.check(_cabi.lib.mla_fp4_decode_static(C.byref(_args(cases[-1], out, lse, status))))
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    assert torch.equal(out, first)
 
     # sizes beyond the built-in scratch are refused with a clear message, nothing is launched
     a = _args(cases[0], out, lse, status)
