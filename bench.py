@@ -1,24 +1,34 @@
 #!/usr/bin/env python
 """Benchmark of the FP4 MLA decode hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--mode dp|cp] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--mode auto|dp|cp]
+                    [--impl native|reference|reference_gpu] [--exchange peer|nccl]
 
-One "step" = one decode step (decode kernel + split-KV combine) over one batch of synthetic
-requests.  At N=1 the workload is the configuration the headline metric is quoted on:
-B=8, H=64, KV=32768, page 64 (``northstar``).  At N>1 every rank runs that workload on its own
-requests (data-parallel attention: no data-path collective, weak scaling) unless ``--mode cp``
-asks for the context-parallel case (KV sharded over ranks, partial outputs + LSE all-gathered
-over NCCL and merged by the merge kernel).
+One "step" = one decode step over one batch of synthetic requests (one launch of the decode kernel,
+which also merges the split-KV partials).
 
-Prints ONE JSON line (rank 0).  ``value`` is device time per step in microseconds with all
-inputs resident in HBM, cold L2 (the timed CUDA graph rotates through cache copies whose
-combined size exceeds L2); ``e2e`` is the same step through the public wrapper with the step's
-inputs (q, block tables, seq_lens) copied from pinned host memory and the BF16 output read back,
-inside the timed region.  The KV cache itself is persistent device state and is not a step input.
+* N = 1: the workload is the configuration the headline metric is quoted on: B=8, H=64, KV=32768,
+  page 64 (``northstar``).  The line also carries ``extra``: the other single-GPU configurations
+  (uniform, small, varlen, spec), measured in the same run after the headline.
+* N > 1 (``--mode auto`` = ``cp``): decode context parallel.  B=8, H=64, KV = 32768 x N tokens per request,
+  every request's pages sharded contiguously over the N ranks, so that each rank does exactly the
+  north-star work and N=8 is the KV=262144 configuration; the step is decode + exchange of the
+  partials over NVLink + merge, all inside the timed CUDA graph.  ``value`` is the max over ranks.
+  ``--mode dp`` measures data-parallel attention instead (every rank its own north-star batch, no
+  data-path collective).  ``extra`` holds the other mode's figure.
 
-``--impl reference`` times the reference's dequantise-then-attend arithmetic on the host cores
-(the CPU restatement under oracle/; the reference ships no CPU path and its GPU kernel needs
-flashinfer-python==0.6.17, which is not installable offline).
+Prints ONE JSON line (rank 0).  ``value`` is device time per step in microseconds with all inputs
+resident in HBM, cold L2 (the timed CUDA graph rotates through cache copies whose combined size exceeds
+L2); ``e2e`` is the same step through the public wrapper with the step's inputs (q, block tables,
+seq_lens) copied from pinned host memory and the BF16 output read back, inside the timed region.  The
+KV cache itself is persistent device state and is not a step input.
+
+``--impl reference`` times the reference's dequantise-then-attend arithmetic on the host cores (the CPU
+restatement under oracle/: the reference ships no CPU path).  ``--impl reference_gpu`` (not run by default)
+times, on the same GPU and with the same harness, FlashInfer's installed FP8 MLA decode kernel on the same
+cache materialised as E4M3 and the reference's own CuTe-DSL FP4 kernel from ``baseline/_ref`` under a shim
+for its version gate; whatever cannot be imported, compiled or launched is reported as unavailable with the
+error text.
 """
 from __future__ import annotations
 
@@ -40,11 +50,19 @@ METRIC = "fp4_mla_decode_us_per_step"
 UNIT = "us"
 L2_BYTES = 126 * 1024 * 1024
 PUBLISHED_US = {"northstar": 37.726, "uniform": 13.461}  # reference README, one B300, cold L2
+TRAFFIC_SUMMARY = ROOT / "profiles" / "decode_sm100_northstar_ncu_full.md"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel, from the ncu capture summarised in
-# profiles/decode_sm100_northstar_ncu_full.md (87.26 MB read + 15.18 MB written); None where no capture exists.
-NCU_TRAFFIC_BYTES = {("northstar", "fused"): 100.8e6}
+def ncu_traffic_bytes():
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel on the north-star workload, read
+    from the tracked ncu summary (a line ``dram_bytes_per_launch: <number>``); None when the summary has none."""
+    try:
+        for line in TRAFFIC_SUMMARY.read_text().splitlines():
+            if line.strip().startswith("dram_bytes_per_launch:"):
+                return float(line.split(":", 1)[1].strip().split()[0])
+    except OSError:
+        pass
+    return None
 
 
 def peaks():
@@ -112,14 +130,12 @@ class ClockSampler:
 
 
 def build_workload(name: str, device, rank: int, world: int, mode: str):
-    from flashinfer_mla_fp4_b200 import synth
+    from flashinfer_mla_fp4_b200 import synth  # helper module: does not load the product library
 
     if mode == "cp":
-        # context parallel: B=8, H=64, KV=262144 sharded contiguously over the ranks (page aligned)
-        total = 262144
-        per = (total // world // 64) * 64
-        lens = [per if rank < world - 1 else total - per * (world - 1)] * 8
-        return synth.build_case(f"cp{world}", lens, 64, 64, 1, 1100 + rank, device)
+        # context parallel: B=8, H=64, KV = 32768 tokens per request and rank (N=8: KV 262144), the rank's shard of
+        # every request's pages (contiguous, page aligned), as ContextParallelDecoder expects them
+        return synth.build_case(f"cp{world}", [32768] * 8, 64, 64, 1, 1100 + rank, device)
     if name == "dp512":
         lens = synth.dp_lens()
         per = (len(lens) + world - 1) // world
@@ -151,30 +167,230 @@ def cpu_oracle_us_per_step(case, sample_requests: int, threads: int, repeats: in
 
 
 def run_reference_arm(args, rank: int, world: int):
+    """The reference arithmetic on the host cores.  Nothing of the product (package library, kernels) is loaded here."""
     if rank != 0:
         return
     case = build_workload(args.workload, "cpu", 0, 1, "dp")
     threads = os.cpu_count() or 1
-    # warm-up + K steps, each a bounded sample (one request)
+    sample = min(case.batch, 8)
     for _ in range(max(1, min(args.warmup, 1))):
-        cpu_oracle_us_per_step(case, 1, threads)
+        cpu_oracle_us_per_step(case, sample, threads)
     t0 = time.perf_counter()
     vals = []
+    what = ""
     for _ in range(args.steps):
-        v, sample = cpu_oracle_us_per_step(case, 1, threads)
+        v, what = cpu_oracle_us_per_step(case, sample, threads)
         vals.append(v)
+        if time.perf_counter() - t0 > 150.0:  # keep the whole run within a few minutes
+            break
     us = statistics.median(vals)
     line = {
-        "impl": "reference", "metric": METRIC, "value": us, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "impl": "reference", "metric": METRIC, "value": us, "unit": UNIT, "n_gpus": world, "steps": len(vals),
         "warmup": args.warmup, "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": case.name, "batch": case.batch, "heads": case.num_heads, "kv_len": case.max_seq_len,
                    "page_size": case.page_size, "note": "reference arithmetic (dequantise, dense FP32 attention) on host cores"},
-        "cpu_baseline": {"value": us, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": us, "unit": UNIT, "cores": threads, "kind": "port", "sample": what},
         "e2e": {"value": us, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": time.perf_counter() - t0,
     }
     print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# timing helpers (device time with CUDA events on the launching stream, steps inside one CUDA graph)
+# ----------------------------------------------------------------------------------------------------------------
+def cache_copies(case, copies: int = 0):
+    n = copies or max(2, -(-int(1.5 * L2_BYTES) // max(case.kv_bytes(), 1)))
+    n = min(n, 16)
+    return [(case.kv_cache, case.kv_cache_sf)] + [(case.kv_cache.clone(), case.kv_cache_sf.clone()) for _ in range(n - 1)]
+
+
+def time_graph(step, K: int, stream, repeats: int, barrier=None, warm: int = 3):
+    """Median device time per step (us) of a CUDA graph holding K calls of step(i), replayed `repeats` times."""
+    with torch.cuda.stream(stream):
+        for i in range(warm):
+            step(i)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(K):
+                step(i)
+    times = []
+
+    def replay():
+        if barrier is not None:
+            barrier()
+        else:
+            torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            graph.replay()
+            e1.record(stream)
+        if barrier is not None:
+            barrier()
+        else:
+            torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3 / K)
+
+    for _ in range(max(1, repeats)):
+        replay()
+    return times, replay
+
+
+def measure_single(name: str, device, K: int, repeats: int):
+    """One single-GPU configuration: us per step (cold L2, graph of K steps) and its roofline fraction."""
+    from flashinfer_mla_fp4_b200 import BatchMLADecodeCuteDSLFP4Wrapper
+
+    case = build_workload(name, device, 0, 1, "dp")
+    caches = cache_copies(case)
+    w = BatchMLADecodeCuteDSLFP4Wrapper(torch.empty(64 << 20, dtype=torch.int8, device=device))
+    w.plan(num_heads=case.num_heads, page_size=case.page_size, out_dtype=torch.bfloat16, is_var_seq=True)
+    out = torch.empty(case.batch, case.q_len, case.num_heads, 512, dtype=torch.bfloat16, device=device)
+
+    def step(i):
+        kc, sf = caches[i % len(caches)]
+        w.run(case.q, kc, case.block_tables, case.seq_lens, case.max_seq_len, case.softmax_scale, out=out, kv_cache_sf=sf)
+
+    times, _ = time_graph(step, K, torch.cuda.Stream(device), repeats)
+    torch.cuda.synchronize()
+    w.check_device_status()
+    us = statistics.median(times)
+    hbm_peak, bf16_peak, kind = peaks()
+    t_hbm = case.step_bytes() / (hbm_peak * 1e9) * 1e6
+    t_fp8 = case.flops() / (2.0 * bf16_peak * 1e12) * 1e6
+    return {"us_per_step": us, "tb_per_s": case.kv_bytes() / (us * 1e-6) / 1e12, "kv_tokens": case.kv_tokens,
+            "batch": case.batch, "heads": case.num_heads, "q_len": case.q_len,
+            "roofline_us": max(t_hbm, t_fp8), "bound": "hbm" if t_hbm >= t_fp8 else "tensor (FP8 peak taken as 2 x measured BF16)",
+            "frac_of_roofline": max(t_hbm, t_fp8) / us, "cache_copies": len(caches)}
+
+
+def bench_cache_write(device, tokens: int = 1 << 20, reps: int = 10):
+    """The CUDA cache writer on `tokens` bf16 tokens (inputs and cache larger than L2): tokens/s and roofline fraction."""
+    from flashinfer_mla_fp4_b200.kvcache import BYTES_PER_TOKEN, HEAD_DIM_QK, LATENT_DIM, ROPE_DIM, ROW_BYTES, write_tokens
+
+    page_size = 64
+    pages = (tokens + page_size - 1) // page_size
+    g = torch.Generator(device=device).manual_seed(1234)
+    latent = torch.randn(tokens, LATENT_DIM, generator=g, device=device, dtype=torch.float32).bfloat16()
+    rope = torch.randn(tokens, ROPE_DIM, generator=g, device=device, dtype=torch.float32).bfloat16()
+    slots = torch.randperm(pages * page_size, generator=g, device=device)[:tokens].contiguous()
+    cache = torch.empty(pages, page_size, ROW_BYTES, dtype=torch.uint8, device=device)
+    sf = torch.empty(pages, page_size, 1, dtype=torch.float32, device=device)
+    for _ in range(3):
+        write_tokens(latent, rope, slots, cache, sf)
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        write_tokens(latent, rope, slots, cache, sf)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e-3)
+    t = statistics.median(times)
+    bytes_per_token = HEAD_DIM_QK * 2 + BYTES_PER_TOKEN + 8  # bf16 inputs, cache row + scale, slot id
+    peak, _, kind = peaks()
+    achieved = tokens * bytes_per_token / t / 1e9
+    return {"metric": "fp4_cache_write_tokens_per_s", "value": tokens / t, "unit": "tokens/s", "tokens": tokens, "us": t * 1e6,
+            "dtype": "bf16->e2m1/e4m3", "higher_is_better": True, "data": "synthetic", "n_gpus": 1,
+            "config": {"workload": "cache_write", "tokens": tokens, "l2": f"cold by size: {tokens * bytes_per_token / 2**20:.0f} MiB touched per call"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": kind, "algorithmic_bytes_per_token": bytes_per_token, "kernel": "cache_write_kernel"}}
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# the reference's kernels on this GPU (not the default arm)
+# ----------------------------------------------------------------------------------------------------------------
+def run_reference_gpu_arm(args, rank: int, world: int):
+    if rank != 0:
+        return
+    import importlib
+    import traceback
+
+    device = torch.device("cuda", 0)
+    from oracle import mla_fp4_oracle as O  # the reference's fixture builder restated: the E4M3 materialisation of the cache
+
+    case = build_workload(args.workload, device, 0, 1, "dp")
+    res = {"impl": "reference_gpu", "metric": METRIC, "unit": UNIT, "n_gpus": 1, "higher_is_better": False, "data": "synthetic",
+           "config": {"workload": case.name, "batch": case.batch, "heads": case.num_heads, "kv_len": case.max_seq_len,
+                      "page_size": case.page_size, "l2": "cold: cache copies rotated", "harness": "same CUDA-graph harness as the native arm"}}
+    import flashinfer
+
+    res["flashinfer_version"] = getattr(flashinfer, "__version__", "?")
+    # the same cache as E4M3 [pages, page, 576]: dequantised latent (exact when the scales are powers of two, else rounded
+    # to E4M3: the FP8 kernel then sees slightly different data; only its time is used here) + the RoPE bytes
+    with torch.no_grad():
+        lat, _ = O.dequantize_cache(case.kv_cache.cpu(), case.kv_cache_sf.cpu())
+        fp8 = torch.cat((lat.to(torch.float8_e4m3fn).view(torch.uint8), case.kv_cache.cpu()[..., 256:]), dim=-1).to(device)
+    K = args.steps
+    out = torch.empty(case.batch, 1, case.num_heads, 512, dtype=torch.bfloat16, device=device)
+    ws = torch.empty(256 << 20, dtype=torch.int8, device=device)
+    common = dict(kv_lora_rank=512, qk_rope_head_dim=64, num_heads=case.num_heads, page_size=case.page_size,
+                  q_dtype=case.q.dtype, out_dtype=torch.bfloat16, is_var_seq=True, enable_pdl=False)
+
+    def timed(make_step, copies):
+        times, _ = time_graph(make_step, K, torch.cuda.Stream(device), args.repeats)
+        torch.cuda.synchronize()
+        return statistics.median(times)
+
+    # (a) FlashInfer's installed FP8 kernel
+    try:
+        from flashinfer.cute_dsl.attention.wrappers.batch_mla import BatchMLADecodeCuteDSLWrapper
+
+        w8 = BatchMLADecodeCuteDSLWrapper(ws)
+        w8.plan(**common)
+        n = min(16, max(2, -(-int(1.5 * L2_BYTES) // max(fp8.numel(), 1))))
+        fp8s = [fp8.view(torch.float8_e4m3fn)] + [fp8.clone().view(torch.float8_e4m3fn) for _ in range(n - 1)]
+
+        def step8(i):
+            w8.run(q=case.q, kv_cache=fp8s[i % n], block_tables=case.block_tables, seq_lens=case.seq_lens,
+                   max_seq_len=case.max_seq_len, softmax_scale=case.softmax_scale, out=out)
+
+        res["flashinfer_fp8_us"] = timed(step8, n)
+        res["flashinfer_fp8_label"] = f"flashinfer {res['flashinfer_version']} BatchMLADecodeCuteDSLWrapper, E4M3 cache of the same tokens"
+        del fp8s
+    except Exception as e:  # noqa: BLE001
+        res["flashinfer_fp8_unavailable"] = f"unavailable on this box: {type(e).__name__}: {e}"[:600]
+        res["flashinfer_fp8_trace"] = traceback.format_exc()[-800:]
+    # (b) the reference's own FP4 kernel, unmodified sources from baseline/_ref, under a shim for its version gate
+    try:
+        ref_dir = ROOT / "baseline" / "_ref"
+        if not (ref_dir / "flashinfer_mla_fp4").exists():
+            raise ImportError("baseline/_ref/flashinfer_mla_fp4 is missing (install the reference there)")
+        import importlib.metadata as md
+
+        real_version = md.version
+
+        def shim_version(name):  # the reference refuses anything but flashinfer-python 0.6.17
+            return "0.6.17" if name.replace("_", "-").lower() == "flashinfer-python" else real_version(name)
+
+        md.version = shim_version
+        import flashinfer.cute_dsl.utils as fu
+
+        if not hasattr(fu, "require_cute_dsl_arch"):  # the one symbol the installed release lacks
+            fu.require_cute_dsl_arch = lambda *a, **k: None
+        sys.path.insert(0, str(ref_dir))
+        try:
+            ref = importlib.import_module("flashinfer_mla_fp4")
+        finally:
+            md.version = real_version
+        w4 = ref.BatchMLADecodeCuteDSLFP4Wrapper(ws)
+        w4.plan(**common, kv_dtype=torch.uint8)
+        caches = cache_copies(case)
+
+        def step4(i):
+            kc, sf = caches[i % len(caches)]
+            w4.run(q=case.q, kv_cache=kc, block_tables=case.block_tables, seq_lens=case.seq_lens,
+                   max_seq_len=case.max_seq_len, softmax_scale=case.softmax_scale, out=out, kv_cache_sf=sf)
+
+        res["reference_fp4_us"] = timed(step4, len(caches))
+        res["reference_fp4_label"] = f"reference sources unmodified, shimmed onto flashinfer {res['flashinfer_version']} (pinned: 0.6.17)"
+    except Exception as e:  # noqa: BLE001
+        res["reference_fp4_unavailable"] = f"unavailable on this box: {type(e).__name__}: {e}"[:600]
+        res["reference_fp4_trace"] = traceback.format_exc()[-800:]
+    res["value"] = res.get("reference_fp4_us", res.get("flashinfer_fp8_us"))
+    print(json.dumps(res), flush=True)
 
 
 def main() -> None:
@@ -182,11 +398,13 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="northstar", choices=["small", "uniform", "northstar", "varlen", "spec", "dp512"])
-    ap.add_argument("--mode", default="dp", choices=["dp", "cp"])
-    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default="northstar", choices=["small", "uniform", "northstar", "varlen", "spec", "dp512", "cache_write"])
+    ap.add_argument("--mode", default="auto", choices=["auto", "dp", "cp"], help="N > 1: context parallel (auto, cp) or data parallel")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="context parallel: how the partials travel")
+    ap.add_argument("--impl", default="native", choices=["native", "reference", "reference_gpu"])
     ap.add_argument("--copies", type=int, default=0, help="cache copies rotated for cold L2 (0 = enough to exceed L2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the other configurations / the other multi-GPU mode")
     ap.add_argument("--repeats", type=int, default=5, help="timed graph replays; the median is reported")
     ap.add_argument("--kernel", default="fused", choices=["fused", "2pass"],
                     help="fused: one kernel that also merges the split-KV partials (the product path); "
@@ -203,148 +421,134 @@ def main() -> None:
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
+    if args.impl == "reference_gpu":
+        run_reference_gpu_arm(args, rank, world)
+        return
     warmup = max(args.warmup, 3)
 
     import torch.distributed as dist
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    if args.workload == "cache_write":
+        if rank == 0:
+            print(json.dumps(bench_cache_write(device)), flush=True)
+        return
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=device)
+    mode = args.mode
+    if mode == "auto":
+        mode = "cp" if world > 1 else "dp"
+    if world == 1:
+        mode = "dp"
 
-    from flashinfer_mla_fp4_b200 import BatchMLADecodeCuteDSLFP4Wrapper
+    from flashinfer_mla_fp4_b200 import BatchMLADecodeCuteDSLFP4Wrapper, _cabi
     from flashinfer_mla_fp4_b200.distributed import ContextParallelDecoder
-
-    case = build_workload(args.workload, device, rank, world, args.mode)
-    B, H, ql = case.batch, case.num_heads, case.q_len
-    cache_bytes = case.kv_cache.numel() + case.kv_cache_sf.numel() * 4
-    copies = args.copies or max(2, -(-int(1.5 * L2_BYTES) // max(case.kv_bytes(), 1)))
-    copies = min(copies, 16)
-    caches = [(case.kv_cache, case.kv_cache_sf)] + [(case.kv_cache.clone(), case.kv_cache_sf.clone()) for _ in range(copies - 1)]
-
-    ws = torch.empty(64 << 20, dtype=torch.int8, device=device)
-    wrapper = BatchMLADecodeCuteDSLFP4Wrapper(ws)
-    wrapper.plan(num_heads=H, page_size=case.page_size, out_dtype=torch.bfloat16, is_var_seq=True)
-    from flashinfer_mla_fp4_b200 import _cabi
-    wrapper._kernel = _cabi.KERNEL_TCGEN05 if args.kernel == "fused" else _cabi.KERNEL_TCGEN05_2PASS
-    launches_per_step = 1 if args.kernel == "fused" else 2
-    out = torch.empty(B, ql, H, 512, dtype=torch.bfloat16, device=device)
-    cp = ContextParallelDecoder(wrapper, dist.group.WORLD) if (args.mode == "cp" and world > 1) else None
-
-    def step(i: int):
-        kc, sf = caches[i % copies]
-        if cp is not None:
-            return cp.run(case.q, kc, case.block_tables, case.seq_lens, case.max_seq_len, case.softmax_scale,
-                          out=out, kv_cache_sf=sf)
-        return wrapper.run(case.q, kc, case.block_tables, case.seq_lens, case.max_seq_len, case.softmax_scale,
-                           out=out, kv_cache_sf=sf)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- warm-up (also the parity spot-check input)
-    for i in range(warmup):
-        step(i)
-    torch.cuda.synchronize()
-    wrapper.check_device_status()
-    if args.profile_steps > 0:
-        for i in range(args.profile_steps):
-            step(i)
-        torch.cuda.synchronize()
-        wrapper.check_device_status()
-        print(json.dumps({"profile_steps": args.profile_steps, "workload": case.name, "kernel": args.kernel}), flush=True)
-        return
-
-    # ---- device-timed K steps: one CUDA graph holding the K steps, replayed `repeats` times
     K = args.steps
     stream = torch.cuda.Stream(device)
-    use_graph = cp is None
-    graph = None
-    if use_graph:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(stream):
-            with torch.cuda.graph(graph, stream=stream):
-                for i in range(K):
-                    step(i)
-    sampler = ClockSampler(local_rank)
-    times = []
-    sampler.start()
-    sampler.wait_first_sample()
 
-    def timed_replay():
-        barrier()
-        with torch.cuda.stream(stream):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            if graph is not None:
-                graph.replay()
-            else:
-                for i in range(K):
-                    step(i)
-            e1.record(stream)
-        barrier()
-        times.append(e0.elapsed_time(e1) * 1e3 / K)  # us per step
+    def measure_mode(m: str, with_clocks: bool):
+        """us per step (max over ranks), kernel-only us, the case and the step function of one multi-GPU mode (or the 1-GPU run)."""
+        case = build_workload(args.workload, device, rank, world, m)
+        caches = cache_copies(case, args.copies)
+        copies = len(caches)
+        ws = torch.empty(64 << 20, dtype=torch.int8, device=device)
+        wrapper = BatchMLADecodeCuteDSLFP4Wrapper(ws)
+        wrapper.plan(num_heads=case.num_heads, page_size=case.page_size, out_dtype=torch.bfloat16, is_var_seq=True)
+        wrapper._kernel = _cabi.KERNEL_TCGEN05 if args.kernel == "fused" else _cabi.KERNEL_TCGEN05_2PASS
+        out = torch.empty(case.batch, case.q_len, case.num_heads, 512, dtype=torch.bfloat16, device=device)
+        cp = ContextParallelDecoder(wrapper, dist.group.WORLD, exchange=args.exchange) if (m == "cp" and world > 1) else None
+        runner = cp if cp is not None else wrapper
 
-    for _ in range(max(1, args.repeats)):
-        timed_replay()
-    # The K steps of one replay last a millisecond or two; nvidia-smi samples every 100 ms.  Keep taking timed
-    # replays (all of them count toward the median) until the device has been under load for about 0.7 s, the
-    # same number on every rank.
-    extra = torch.tensor([min(3000, int(0.7e6 / max(K * statistics.median(times), 1.0)))], dtype=torch.int64, device=device)
-    if world > 1:
-        dist.all_reduce(extra, op=dist.ReduceOp.MAX)
-    for _ in range(int(extra.item())):
-        timed_replay()
-    clocks = sampler.stop()
-    us_local = statistics.median(times)
+        def step(i: int, q=None, bt=None, sl=None):
+            kc, sf = caches[i % copies]
+            return runner.run(case.q if q is None else q, kc, case.block_tables if bt is None else bt,
+                              case.seq_lens if sl is None else sl, case.max_seq_len, case.softmax_scale, out=out, kv_cache_sf=sf)
 
-    # ---- decode kernel alone (roofline of the dominant kernel), same rotation, events on the launching stream
-    # (in the fused mode the decode kernel is the whole step; in the two-kernel mode the combine kernel is left out)
-    wrapper._phase_mask = 1
-    kgraph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(stream):
-        for i in range(3):
+        for i in range(warmup):
             step(i)
-        with torch.cuda.graph(kgraph, stream=stream):
-            for i in range(K):
-                wrapper.run(case.q, caches[i % copies][0], case.block_tables, case.seq_lens, case.max_seq_len,
-                            case.softmax_scale, out=out, kv_cache_sf=caches[i % copies][1])
-    ktimes = []
-    for _ in range(max(1, args.repeats)):
-        torch.cuda.synchronize()
-        with torch.cuda.stream(stream):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            kgraph.replay()
-            e1.record(stream)
-        torch.cuda.synchronize()
-        ktimes.append(e0.elapsed_time(e1) * 1e3 / K)
-    wrapper._phase_mask = 0
-    kernel_us = statistics.median(ktimes)
+        barrier()
+        runner.check_device_status()
+        if args.profile_steps > 0:
+            for i in range(args.profile_steps):
+                step(i)
+            torch.cuda.synchronize()
+            runner.check_device_status()
+            return None
+        sampler = ClockSampler(local_rank) if with_clocks else None
+        if sampler:
+            sampler.start()
+            sampler.wait_first_sample()
+        times, replay = time_graph(step, K, stream, args.repeats, barrier=barrier, warm=0)
+        clocks = None
+        if sampler:
+            # The K steps of one replay last a millisecond or two; nvidia-smi samples every 100 ms.  Keep taking timed
+            # replays (all of them count toward the median) until the device has been under load for about 0.7 s, the
+            # same number on every rank.
+            extra = torch.tensor([min(3000, int(0.7e6 / max(K * statistics.median(times), 1.0)))], dtype=torch.int64, device=device)
+            if world > 1:
+                dist.all_reduce(extra, op=dist.ReduceOp.MAX)
+            for _ in range(int(extra.item())):
+                replay()
+            clocks = sampler.stop()
+        barrier()
+        runner.check_device_status()
+        us_local = statistics.median(times)
+        # the decode kernel alone (roofline of the dominant kernel): same rotation, no exchange
+        ktimes, _ = time_graph(lambda i: wrapper.run(case.q, caches[i % copies][0], case.block_tables, case.seq_lens, case.max_seq_len,
+                                                     case.softmax_scale, out=out, kv_cache_sf=caches[i % copies][1]),
+                               K, stream, args.repeats)
+        kernel_us = statistics.median(ktimes)
+        return {"case": case, "us_local": us_local, "kernel_us": kernel_us, "clocks": clocks, "copies": copies, "n_times": len(times),
+                "step": step, "runner": runner, "out": out, "cp": cp}
 
-    # ---- end to end through the wrapper: step inputs from pinned host memory, output read back
+    main_run = measure_mode(mode, with_clocks=True)
+    if main_run is None:
+        if rank == 0:
+            print(json.dumps({"profile_steps": args.profile_steps, "workload": args.workload, "kernel": args.kernel}), flush=True)
+        return
+    case, out, step, runner = main_run["case"], main_run["out"], main_run["step"], main_run["runner"]
+    B, H, ql = case.batch, case.num_heads, case.q_len
+
+    # ---- end to end through the public API: the step's inputs come from pinned host memory into persistent device
+    # buffers, the step itself is a captured CUDA graph (what a serving engine replays), the output is read back
     q_h = case.q.cpu().pin_memory()
     bt_h = case.block_tables.cpu().pin_memory()
     sl_h = case.seq_lens.cpu().pin_memory()
     out_h = torch.empty(out.shape, dtype=out.dtype).pin_memory()
     q_d, bt_d, sl_d = torch.empty_like(case.q), torch.empty_like(case.block_tables), torch.empty_like(case.seq_lens)
+    q_d.copy_(q_h)
+    bt_d.copy_(bt_h)
+    sl_d.copy_(sl_h)
     h2d = q_h.numel() * q_h.element_size() + bt_h.numel() * 4 + sl_h.numel() * 4
     d2h = out_h.numel() * out_h.element_size()
+    copies = main_run["copies"]
+    e2e_graphs = []
+    with torch.cuda.stream(stream):
+        for j in range(copies):  # one captured step per cache copy, so the rotation (cold L2) stays
+            step(j, q_d, bt_d, sl_d)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                step(j, q_d, bt_d, sl_d)
+            e2e_graphs.append(g)
+    torch.cuda.synchronize()
 
     def e2e_step(i: int):
-        q_d.copy_(q_h, non_blocking=True)
-        bt_d.copy_(bt_h, non_blocking=True)
-        sl_d.copy_(sl_h, non_blocking=True)
-        kc, sf = caches[i % copies]
-        if cp is not None:
-            cp.run(q_d, kc, bt_d, sl_d, case.max_seq_len, case.softmax_scale, out=out, kv_cache_sf=sf)
-        else:
-            wrapper.run(q_d, kc, bt_d, sl_d, case.max_seq_len, case.softmax_scale, out=out, kv_cache_sf=sf)
-        out_h.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the caller consumes the result of every step
+        with torch.cuda.stream(stream):
+            q_d.copy_(q_h, non_blocking=True)
+            bt_d.copy_(bt_h, non_blocking=True)
+            sl_d.copy_(sl_h, non_blocking=True)
+            e2e_graphs[i % copies].replay()
+            out_h.copy_(out, non_blocking=True)
+        stream.synchronize()  # the caller consumes the result of every step
 
     for i in range(warmup):
         e2e_step(i)
@@ -354,16 +558,40 @@ def main() -> None:
         e2e_step(i)
     barrier()
     e2e_us_local = (time.perf_counter() - t0) * 1e6 / K
-    wrapper.check_device_status()
+    runner.check_device_status()
 
     # ---- reduce over ranks (max), aggregate
-    vals = torch.tensor([us_local, kernel_us, e2e_us_local], dtype=torch.float64, device=device)
+    vals = torch.tensor([main_run["us_local"], main_run["kernel_us"], e2e_us_local], dtype=torch.float64, device=device)
     tot = torch.tensor([float(case.kv_bytes()), float(case.step_bytes()), float(case.flops())], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
         dist.all_reduce(tot, op=dist.ReduceOp.SUM)
     us, kernel_us_max, e2e_us = (float(x) for x in vals.cpu())
     kv_bytes_all, step_bytes_all, flops_all = (float(x) for x in tot.cpu())
+    kernel_us = main_run["kernel_us"]
+
+    # ---- the other configurations / the other multi-GPU mode, in the same run
+    extra = {}
+    if not args.no_extra and args.workload == "northstar":
+        if world == 1:
+            for name in ("uniform", "small", "varlen", "spec"):
+                try:
+                    extra[name] = measure_single(name, device, K, args.repeats)
+                except Exception as e:  # noqa: BLE001
+                    extra[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+        else:
+            other = "dp" if mode == "cp" else "cp"
+            del step, runner
+            if main_run["cp"] is not None:
+                main_run["cp"].close()
+            o = measure_mode(other, with_clocks=False)
+            ov = torch.tensor([o["us_local"]], dtype=torch.float64, device=device)
+            dist.all_reduce(ov, op=dist.ReduceOp.MAX)
+            extra[f"{other}{world}"] = {"us_per_step": float(ov.item()), "kernel_us_rank0": o["kernel_us"],
+                                        "what": "every rank its own north-star batch, no data-path collective (weak scaling)" if other == "dp"
+                                        else "context parallel, KV = 32768 x N per request sharded over the ranks"}
+            if o["cp"] is not None:
+                o["cp"].close()
 
     if rank == 0:
         hbm_peak, bf16_peak, peak_kind = peaks()
@@ -372,32 +600,40 @@ def main() -> None:
         fp8_peak = 2.0 * bf16_peak  # no measured FP8 figure: 2 x measured BF16
         t_hbm = case.step_bytes() / (hbm_peak * 1e9) * 1e6
         t_fp8 = case.flops() / (fp8_peak * 1e12) * 1e6
+        traffic = ncu_traffic_bytes() if (args.workload == "northstar" and args.kernel == "fused") else None
+        launches_per_step = (1 if args.kernel == "fused" else 2) + (0 if mode != "cp" or world == 1 else (1 if args.exchange == "peer" else 2))
         line = {
             "metric": METRIC, "value": us, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": warmup,
             "ms_per_step": us / 1e3, "higher_is_better": False,
-            "scaling": "strong" if args.mode == "cp" and world > 1 else "weak",
+            "scaling": "weak",
             "vs_baseline": (us / PUBLISHED_US[args.workload]) if (world == 1 and args.workload in PUBLISHED_US) else None,
             "dtype": "fp4(e2m1)xfp8(e4m3)->f32", "data": "synthetic",
             "config": {"workload": case.name, "batch_per_gpu": B, "heads": H, "q_len": ql, "kv_len_max": case.max_seq_len,
-                       "kv_tokens_per_gpu": case.kv_tokens, "page_size": case.page_size, "parallelism": f"{args.mode}{world}",
+                       "kv_tokens_per_gpu": case.kv_tokens, "page_size": case.page_size, "parallelism": f"{mode}{world}",
+                       "what": ("context parallel: every request holds 32768 x N tokens, sharded over the N ranks (per-GPU work fixed as N grows); "
+                                f"step = decode + exchange ({args.exchange}) + merge" if mode == "cp" and world > 1 else
+                                "every GPU decodes its own batch; no data-path collective"),
                        "l2": f"cold: {copies} cache copies rotated ({copies * case.kv_bytes() / 2**20:.0f} MiB > L2)",
-                       "timing": f"CUDA graph of {K} steps, events on the launching stream, median of {len(times)} timed replays, max over ranks"
-                                 if use_graph else f"{K} eager steps between events, max over ranks",
+                       "timing": f"CUDA graph of {K} steps, events on the launching stream, median of {main_run['n_times']} timed replays, max over ranks",
                        "published_baseline": "reference README, one B300 (not a B200)"},
             "tb_per_s": kv_bytes_all / (us * 1e-6) / 1e12,
             "tflops": flops_all / (us * 1e-6) / 1e12,
             "roofline": {"bound": "hbm" if t_hbm >= t_fp8 else "tensor", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": achieved / hbm_peak, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, args.kernel)), "peak_kind": peak_kind,
+                         "frac": achieved / hbm_peak, "traffic": traffic,
+                         "traffic_source": f"{TRAFFIC_SUMMARY.relative_to(ROOT)} (ncu capture, not this run)" if traffic else None,
+                         "peak_kind": peak_kind,
                          "kernel": "mla_fp4_decode_sm100_kernel", "kernel_mode": args.kernel, "kernel_us": kernel_us, "algorithmic_bytes": case.step_bytes(),
                          "roofline_us": max(t_hbm, t_fp8), "step_frac_of_roofline": max(t_hbm, t_fp8) / us,
                          "fp8_peak_tflops_assumed": fp8_peak},
-            "e2e": {"value": e2e_us, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": launches_per_step * K + (1 if cp is not None else 0) * K,
-            "clocks": clocks,
+            "e2e": {"value": e2e_us, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "how": "pinned host -> persistent device buffers, replay of the captured step, output -> pinned host, stream synchronize"},
+            "gpu_launches": launches_per_step * K,
+            "clocks": main_run["clocks"],
+            "extra": extra,
         }
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            v, sample = cpu_oracle_us_per_step(case, 2, threads, repeats=2)
+            v, sample = cpu_oracle_us_per_step(case, 8, threads, repeats=2)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -75,7 +75,15 @@ EXPORTS = (
     "mla_fp4_cache_write",
     "mla_fp4_decode_static",
     "mla_fp4_static_reset",
+    "mla_fp4_cp_exchange_bytes",
+    "mla_fp4_cp_alloc",
+    "mla_fp4_cp_open",
+    "mla_fp4_cp_close",
+    "mla_fp4_cp_free",
+    "mla_fp4_cp_exchange_merge",
 )
+CP_MAX_RANKS = 8
+CP_HANDLE_BYTES = 64
 
 
 def _load() -> C.CDLL:
@@ -101,6 +109,19 @@ def _load() -> C.CDLL:
     lib.mla_fp4_decode_static.restype = C.c_int
     lib.mla_fp4_static_reset.argtypes = [C.c_void_p]
     lib.mla_fp4_static_reset.restype = C.c_int
+    lib.mla_fp4_cp_exchange_bytes.argtypes = [C.c_int32, C.c_int64, C.POINTER(C.c_size_t)]
+    lib.mla_fp4_cp_exchange_bytes.restype = C.c_int
+    lib.mla_fp4_cp_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]
+    lib.mla_fp4_cp_alloc.restype = C.c_int
+    lib.mla_fp4_cp_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+    lib.mla_fp4_cp_open.restype = C.c_int
+    lib.mla_fp4_cp_close.argtypes = [C.c_void_p]
+    lib.mla_fp4_cp_close.restype = C.c_int
+    lib.mla_fp4_cp_free.argtypes = [C.c_void_p]
+    lib.mla_fp4_cp_free.restype = C.c_int
+    lib.mla_fp4_cp_exchange_merge.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_void_p, C.c_int64, C.c_void_p,
+                                              C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]
+    lib.mla_fp4_cp_exchange_merge.restype = C.c_int
     lib.mla_fp4_merge_partials.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
                                            C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]
     lib.mla_fp4_merge_partials.restype = C.c_int

@@ -88,7 +88,7 @@ class FP4MLADecodeBackend:
         if cp_group is not None:
             from .distributed import ContextParallelDecoder
 
-            self._runner = ContextParallelDecoder(self.wrapper, cp_group)
+            self._runner = ContextParallelDecoder(self.wrapper, cp_group, max_rows=max_batch * q_len * num_heads)
         self.max_pages = (max_seq_len + page_size - 1) // page_size
         self.block_tables = torch.zeros(max_batch, self.max_pages, dtype=torch.int32, device=self.device)
         self.seq_lens = torch.zeros(max_batch, dtype=torch.int32, device=self.device)

@@ -10,7 +10,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = Path(os.environ.get("MLA_FP4_B200_LIB") or (PKG_DIR / "libmla_fp4_b200.so"))
-SOURCES = ["abi.cu", "kernels_simt.cu", "combine.cu", "cache_write.cu", "decode_sm100.cu"]
+SOURCES = ["abi.cu", "kernels_simt.cu", "combine.cu", "cache_write.cu", "cp_exchange.cu", "decode_sm100.cu"]
 HEADERS = ["common.cuh", "dequant.cuh", "launch.h", "ptx_sm100.cuh", "../../include/mla_fp4_b200.h"]
 
 

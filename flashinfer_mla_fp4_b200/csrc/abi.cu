@@ -271,6 +271,78 @@ int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, i
   return MLA_FP4_OK;
 }
 
+int mla_fp4_cp_exchange_bytes(int32_t world, int64_t max_rows, size_t* bytes_out) {
+  if (!bytes_out || world < 1 || world > MLA_FP4_CP_MAX_RANKS || max_rows < 0) return fail(MLA_FP4_ERR_BAD_ARG, "world/max_rows out of range");
+  const int64_t n = max_rows * mla::kLatent + ((max_rows + 3) / 4) * 4;
+  *bytes_out = mla::kCpHeaderBytes + size_t(2) * size_t(world) * size_t(n) * sizeof(float);
+  return MLA_FP4_OK;
+}
+
+int mla_fp4_cp_alloc(size_t bytes, void** block_out, unsigned char* handle_out) {
+  if (!block_out || !handle_out || bytes < mla::kCpHeaderBytes) return fail(MLA_FP4_ERR_BAD_ARG, "null pointer or too few bytes");
+  void* ptr = nullptr;
+  cudaError_t e = cudaMalloc(&ptr, bytes);
+  if (e == cudaSuccess) e = cudaMemset(ptr, 0, bytes);
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, ptr);
+  if (e != cudaSuccess) {
+    if (ptr) cudaFree(ptr);
+    return fail(MLA_FP4_ERR_CUDA, std::string("exchange block allocation: ") + cudaGetErrorString(e));
+  }
+  static_assert(sizeof(cudaIpcMemHandle_t) == MLA_FP4_CP_HANDLE_BYTES, "IPC handle size");
+  memcpy(handle_out, &h, sizeof h);
+  *block_out = ptr;
+  return MLA_FP4_OK;
+}
+
+int mla_fp4_cp_open(const unsigned char* handle, void** block_out) {
+  if (!handle || !block_out) return fail(MLA_FP4_ERR_BAD_ARG, "null pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof h);
+  void* ptr = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e));
+  *block_out = ptr;
+  return MLA_FP4_OK;
+}
+
+int mla_fp4_cp_close(void* peer_block) {
+  if (!peer_block) return MLA_FP4_OK;
+  cudaError_t e = cudaIpcCloseMemHandle(peer_block);
+  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("cudaIpcCloseMemHandle: ") + cudaGetErrorString(e));
+  return MLA_FP4_OK;
+}
+
+int mla_fp4_cp_free(void* own_block) {
+  if (!own_block) return MLA_FP4_OK;
+  cudaError_t e = cudaFree(own_block);
+  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("cudaFree: ") + cudaGetErrorString(e));
+  return MLA_FP4_OK;
+}
+
+int mla_fp4_cp_exchange_merge(void* const* blocks, int32_t world, int32_t rank, const float* partial, int64_t rows,
+                              void* out, int32_t out_dtype, float* lse, int32_t* status, int32_t wait_polls, void* stream) {
+  if (!blocks || world < 1 || world > MLA_FP4_CP_MAX_RANKS || rank < 0 || rank >= world) return fail(MLA_FP4_ERR_BAD_ARG, "blocks/world/rank out of range");
+  if (rows < 0 || wait_polls < 0) return fail(MLA_FP4_ERR_BAD_ARG, "rows/wait_polls out of range");
+  if (rows == 0) return MLA_FP4_OK;
+  if (!partial || !out) return fail(MLA_FP4_ERR_BAD_ARG, "null pointer");
+  if (out_dtype != MLA_FP4_OUT_BF16 && out_dtype != MLA_FP4_OUT_F32 && out_dtype != MLA_FP4_OUT_E4M3)
+    return fail(MLA_FP4_ERR_UNSUPPORTED, "bad out_dtype");
+  if (reinterpret_cast<uintptr_t>(partial) % 16 || reinterpret_cast<uintptr_t>(out) % 16) return fail(MLA_FP4_ERR_BAD_ARG, "partial and out must be 16-byte aligned");
+  mla::CpExchangeParams p;
+  for (int s = 0; s < 8; ++s) p.block[s] = s < world ? blocks[s] : nullptr;
+  for (int s = 0; s < world; ++s)
+    if (!p.block[s] || reinterpret_cast<uintptr_t>(p.block[s]) % 16) return fail(MLA_FP4_ERR_BAD_ARG, "an exchange block is null or misaligned");
+  p.part = partial; p.rows = rows; p.n = rows * mla::kLatent + ((rows + 3) / 4) * 4;
+  p.out = out; p.lse = lse; p.status = status; p.world = world; p.rank = rank; p.out_dtype = out_dtype;
+  p.wait_polls = wait_polls > 0 ? uint32_t(wait_polls) : (1u << 22);
+  // every CTA of the grid must be resident at once (CTAs that wait for peers hold their place): rows, capped well below that
+  const int ctas = int(rows < 296 ? rows : 296);
+  cudaError_t e = mla::launch_cp_exchange_merge(p, ctas, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("exchange launch: ") + cudaGetErrorString(e));
+  return MLA_FP4_OK;
+}
+
 int mla_fp4_cache_write(const void* latent, int64_t latent_stride, const void* rope, int64_t rope_stride,
                         int32_t in_dtype, const float* token_scale, const int64_t* slot_mapping,
                         int64_t num_tokens, void* kv_cache, float* kv_cache_sf, int64_t num_slots, void* stream) {

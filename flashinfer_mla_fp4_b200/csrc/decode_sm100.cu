@@ -17,7 +17,11 @@
 // MN-major A operand of PV: there is no conversion pass and no copy of the tile in any other format.
 // (Earlier versions expanded the codes to E4M3 with eight warps; those warps competed with the softmax
 // warps for issue slots and with the MMAs for shared-memory bandwidth, and were the busiest role.)
-// RoPE bytes, per-token scales and Q arrive by TMA as well; pages two tiles ahead are prefetched into L2.
+// RoPE bytes, per-token scales and Q arrive by TMA as well; pages four tiles ahead are prefetched into L2.
+// The latent blocks live in a ring of ten 16 KiB blocks (two and a half tiles): a block's copy is issued as soon as the
+// PV of the block ten positions earlier has completed, so the loads of a tile do not wait for the whole of the tile two
+// back.  To make room for the ten blocks there is one P buffer (the softmax warps keep a tile's P' in registers until the
+// PV of the previous tile has completed) and one RoPE buffer (released right after the two RoPE MMAs of a tile).
 //
 // Warp roles (384 threads): 0 QK^T issue, 1 TMA issue (lane i owns page i of the tile), 2 and 3 PV issue,
 // two 128-dim blocks each (issue warps run warp-uniform code, one elected lane per instruction),
@@ -52,21 +56,22 @@ constexpr int kWarpQK = 0, kWarpTMA = 1, kWarpPV = 2, kWarpPV2 = 3;
 constexpr int kWarpSoftmax0 = 4;       // 8 warps; warp & 3 is the TMEM lane quarter the warp may access
 constexpr int kThreads = 384;          // 12 warps, three per scheduler
 constexpr int kSoftmaxThreads = 256;   // 8 warps: warp w works on TMEM lanes 32*(w%4).. and heads 32*(w/4)..
-constexpr int kStages = 2;
+constexpr int kSStages = 2;                // S accumulators in TMEM and per-token scale buffers
+constexpr int kRing = 10;                  // latent blocks in flight: two and a half tiles
 constexpr int kBlocks = 4;                 // 128-dim blocks of the latent
 constexpr int kBlockBytes = kTile * 128;   // 16 KiB: [128 tokens][128 B], 128B swizzle
-constexpr int kMaxSeg = 48;                // segments staged per round
+constexpr int kMaxSeg = 16;                // segments staged per round
 constexpr float kPShift = 4.0f;            // P' = 2^(y - M + 4): keeps the E4M3 lo term out of the subnormals
 constexpr float kLazyThreshold = 4.0f;     // the reference is refreshed only when beaten by 2^4 (P' <= 2^8 < 448)
 
 // shared memory map (bytes from a 1024-aligned base)
-constexpr uint32_t kOffKV = 0;                                            // [2][4][16384]
-constexpr uint32_t kOffRope = kOffKV + kStages * kBlocks * kBlockBytes;   // [2][128][64]  64B swizzle
-constexpr uint32_t kOffQLat = kOffRope + kStages * kTile * 64;            // [4][64][128]  128B swizzle
+constexpr uint32_t kOffKV = 0;                                            // [10][16384]
+constexpr uint32_t kOffRope = kOffKV + kRing * kBlockBytes;               // [128][64]  64B swizzle
+constexpr uint32_t kOffQLat = kOffRope + kTile * 64;                      // [4][64][128]  128B swizzle
 constexpr uint32_t kOffQRope = kOffQLat + kBlocks * kGroupHeads * 128;    // [64][64]      64B swizzle
-constexpr uint32_t kOffP = kOffQRope + kGroupHeads * 64;                  // [2][hi,lo][128][64] 64B swizzle (MN-major)
-constexpr uint32_t kOffScale = kOffP + kStages * 2 * kTile * 64;          // [2][128] f32
-constexpr uint32_t kOffM = kOffScale + kStages * kTile * 4;               // [64] f32 NEGATED reference -(M - shift)
+constexpr uint32_t kOffP = kOffQRope + kGroupHeads * 64;                  // [hi,lo][128][64] 64B swizzle (MN-major)
+constexpr uint32_t kOffScale = kOffP + 2 * kTile * 64;                    // [2][128] f32
+constexpr uint32_t kOffM = kOffScale + kSStages * kTile * 4;              // [64] f32 NEGATED reference -(M - shift)
 constexpr uint32_t kOffF = kOffM + kGroupHeads * 4;                       // [64] f32 rescale factor
 constexpr uint32_t kOffDelta = kOffF + kGroupHeads * 4;                   // [64] f32 how far the reference moved at its last refresh
 constexpr uint32_t kOffWmax = kOffDelta + kGroupHeads * 4;                // [4][64] f32 per-warp column max / sum
@@ -74,8 +79,16 @@ constexpr uint32_t kOffLinv = kOffWmax + 4 * kGroupHeads * 4;             // [64
 constexpr uint32_t kOffLse = kOffLinv + kGroupHeads * 4;                  // [64] f32
 constexpr uint32_t kOffScMax = kOffLse + kGroupHeads * 4;                 // [8] f32 per-warp largest token scale
 constexpr uint32_t kOffBars = kOffScMax + 8 * 4;                          // mbarriers (8 B each)
-constexpr int kNumBars = 2 * 4 /*kv_full*/ + 2 * 4 /*kv_empty*/ + 2 /*aux_full*/ + 2 /*s_full*/ + 2 /*s_empty*/ +
-                         2 /*p_full*/ + 1 /*q_full*/ + 1 /*q_empty*/ + 1 /*o_free*/ + 1 /*drain*/ + 1 /*tail*/;
+// barrier indices
+__device__ __forceinline__ constexpr int bar_kv_full(int slot) { return slot; }            // a ring block has landed
+__device__ __forceinline__ constexpr int bar_kv_empty(int slot) { return kRing + slot; }   // PV has finished with it
+__device__ __forceinline__ constexpr int bar_sc_full(int s) { return 2 * kRing + s; }      // per-token scales of a tile
+__device__ __forceinline__ constexpr int bar_s_full(int s) { return 2 * kRing + 2 + s; }
+__device__ __forceinline__ constexpr int bar_s_empty(int s) { return 2 * kRing + 4 + s; }
+constexpr int kBarRopeFull = 2 * kRing + 6, kBarRopeEmpty = 2 * kRing + 7, kBarPFull = 2 * kRing + 8, kBarPEmpty = 2 * kRing + 9,
+              kBarQFull = 2 * kRing + 10, kBarQEmpty = 2 * kRing + 11, kBarOFree = 2 * kRing + 12, kBarDrain = 2 * kRing + 13,
+              kBarTail = 2 * kRing + 14;
+constexpr int kNumBars = 2 * kRing + 15;
 constexpr uint32_t kOffTail = kOffBars + kNumBars * 8;                    // merge plan: [148] slot ids, then [64] f32 1/sum of weights
 constexpr uint32_t kOffTailInv = kOffTail + kMaxCombineSlots * 4;
 constexpr uint32_t kOffSegs = kOffTailInv + kGroupHeads * 4;              // Segment[kMaxSeg]
@@ -85,15 +98,6 @@ constexpr uint32_t kSmemAlloc = kSmemBytes + 1024;                        // sla
 static_assert(sizeof(Segment) == 24, "segment staging layout");
 static_assert(kSmemAlloc <= 232448, "shared memory budget exceeded");
 static_assert(kOffBars % 8 == 0 && kOffSegs % 8 == 0 && kOffMisc % 8 == 0, "alignment");
-
-// barrier indices
-__device__ __forceinline__ constexpr int bar_kv_full(int s, int j) { return s * 4 + j; }
-__device__ __forceinline__ constexpr int bar_kv_empty(int s, int j) { return 8 + s * 4 + j; }
-__device__ __forceinline__ constexpr int bar_aux_full(int s) { return 16 + s; }
-__device__ __forceinline__ constexpr int bar_s_full(int s) { return 18 + s; }
-__device__ __forceinline__ constexpr int bar_s_empty(int s) { return 20 + s; }
-__device__ __forceinline__ constexpr int bar_p_full(int s) { return 22 + s; }
-constexpr int kBarQFull = 24, kBarQEmpty = 25, kBarOFree = 26, kBarDrain = 27, kBarTail = 28;
 
 // TMEM columns
 constexpr uint32_t kColSLat = 0;     // + 64 * stage
@@ -142,6 +146,12 @@ struct RoleState {
   uint32_t it;   // tiles processed so far by this CTA (selects stage and barrier phase)
   uint32_t seg;  // segments processed so far
   uint32_t part; // partial segments processed so far (softmax role)
+  uint32_t slot, lap;  // ring block of the role's next latent block, and how many times the ring has been filled before it
+  uint32_t n_rope, n_sc;  // TMA role: RoPE and scale buffers armed so far
+  __device__ __forceinline__ void advance(uint32_t n) {
+    slot += n;
+    if (slot >= uint32_t(kRing)) { slot -= kRing; ++lap; }
+  }
 };
 
 __device__ __forceinline__ uint32_t bar_addr(const Ctx& c, int idx) { return c.smem + kOffBars + 8u * idx; }
@@ -223,6 +233,11 @@ __device__ __forceinline__ void st_release(int32_t* p, int v) {
 // ------------------------------------------------------------------------------------------
 // The whole warp runs this role: lane i owns page i of the current tile (at most 16 pages of 8 tokens),
 // keeps its page id in a register and issues that page's copies; lane 0 does the waits and arms the barriers.
+//
+// Order of a tile's copies: latent blocks 0 and 1, RoPE, scales, latent blocks 2 and 3.  That is the order in which
+// their buffers come free in the steady state (blocks 0, 1 <- PV of the tile three back; RoPE <- the RoPE MMAs of
+// the previous tile; scales <- the softmax of the tile two back; blocks 2, 3 <- PV of the tile two back), so a wait
+// never holds up a copy whose buffer is already free.
 __device__ __forceinline__ void tma_role(const DecodeParams& p, const Ctx& c, const CUtensorMap* map_q_lat,
                                          const CUtensorMap* map_q_rope, const CUtensorMap* map_rope,
                                          const CUtensorMap* map_lat, RoleState& st) {
@@ -249,78 +264,102 @@ __device__ __forceinline__ void tma_role(const DecodeParams& p, const Ctx& c, co
     }
     const int pages_total = (g.seq_len + p.page_size - 1) / p.page_size;
     const int32_t* bt_req = p.block_tables + size_t(g.b) * p.block_table_stride;
-    // This lane's page id for the current tile and the two after it, loaded a tile ahead of their use
-    // (never beyond the request's pages).
+    // This lane's page id for a tile (never read beyond the request's pages); an id outside the pool is never turned into
+    // an address: the tile's barrier then never completes and the bounded wait reports it.
     auto page_of = [&](int tile) {
       const int lp = tile * ppt + lane;
       const int id = (tile < g.tile_end && lane < ppt && lp < pages_total) ? __ldg(bt_req + lp) : -1;
-      return int64_t(id) < p.num_pages ? id : -1;  // an id outside the pool is never turned into an address: the tile's barrier
-    };                                              // then never completes and the bounded wait reports it
-    int pg = page_of(g.tile_begin), pg1 = page_of(g.tile_begin + 1), pg2 = page_of(g.tile_begin + 2);
+      return int64_t(id) < p.num_pages ? id : -1;
+    };
+    // Rows are prefetched into L2 kAhead tiles ahead of their copy: HBM latency is paid there, and the copy, issued
+    // when a ring block comes free, finds the rows in L2.  The 32 lanes share the lines of each page (a page is one
+    // contiguous range).
+    constexpr int kAhead = 4;
+    auto prefetch_tile = [&](int pg_mine) {
+      const uint32_t page_bytes = uint32_t(p.page_size) * kRowBytes;
+#pragma unroll 1
+      for (int i = 0; i < ppt; ++i) {
+        const int pgi = __shfl_sync(0xffffffffu, pg_mine, i);
+        if (pgi < 0) break;
+        const uint8_t* base = reinterpret_cast<const uint8_t*>(p.kv_cache) + size_t(pgi) * page_bytes;
+#pragma unroll 1
+        for (uint32_t off = uint32_t(lane) * 128u; off < page_bytes; off += 32u * 128u)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off) : "memory");
+      }
+    };
+    int pg = page_of(g.tile_begin), pg1 = page_of(g.tile_begin + 1), pg2 = page_of(g.tile_begin + 2), pg3 = page_of(g.tile_begin + 3);
 #pragma unroll 1
     for (int t = g.tile_begin; t < g.tile_end; ++t, ++st.it) {
       const uint32_t s = st.it & 1, k = st.it >> 1;
       if (lane == 0) MLA_TRACE(1, st.it, 0);
       const int np = min(ppt, pages_total - t * ppt);
       const bool mine = pg >= 0;
-      const int pg3 = page_of(t + 3);  // in flight while this tile is issued
-      // Two tiles ahead there is no free shared-memory stage yet, but L2 can take the rows already: the
-      // copy issued later (when PV frees the stage) then finds them there instead of waiting for HBM.
-      // The 32 lanes share the lines of each page of that tile (a page is one contiguous range).
-      {
-        const uint32_t page_bytes = uint32_t(p.page_size) * kRowBytes;
-#pragma unroll 1
-        for (int i = 0; i < ppt; ++i) {
-          const int pgi = __shfl_sync(0xffffffffu, pg2, i);
-          if (pgi < 0) break;
-          const uint8_t* base = reinterpret_cast<const uint8_t*>(p.kv_cache) + size_t(pgi) * page_bytes;
-#pragma unroll 1
-          for (uint32_t off = uint32_t(lane) * 128u; off < page_bytes; off += 32u * 128u)
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off) : "memory");
-        }
-      }
-      // The RoPE tile of this stage was last read by QK of tile it-2 and the scales by the softmax
-      // of tile it-2; both are over once the softmax threads have released S of that tile.
-      if (k >= 1) wait_warp(c, bar_s_empty(s), (k - 1) & 1);
-      if (!c.misc->abort) {
-        const uint32_t bar = bar_addr(c, bar_aux_full(s));
-        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, uint32_t(np) * (page_rope_bytes + page_scale_bytes));
-        __syncwarp();
-        if (mine) {
-          ptx::tma_load_3d(c.smem + kOffRope + s * kTile * 64 + uint32_t(lane) * page_rope_bytes, map_rope, bar, kLatent / 2, 0, pg);
-          ptx::bulk_load(c.smem + kOffScale + s * kTile * 4 + uint32_t(lane) * page_scale_bytes,
-                         p.kv_cache_sf + size_t(pg) * p.page_size, page_scale_bytes, bar);
-        }
-      }
+      const int pg4 = page_of(t + kAhead);  // in flight while this tile is issued
+      // Every CTA of the grid asks for its first tiles at the same moment, and what is asked for first arrives first:
+      // nothing is prefetched while the ring fills (the copies of the first two and a half tiles go out at once anyway);
+      // from the second tile on, the tile kAhead ahead is prefetched, one per tile.
+      if (t != g.tile_begin) prefetch_tile(pg4);
       // The packed E2M1 latent: the tensor map's 4-bit type makes the copy write every 16 values as
       // 8 bytes of data + 8 bytes of padding, the form the MMA reads 4-bit operands in, so a block is
       // [128 tokens][128 B] with the same 128-byte swizzle as an 8-bit tile and needs no conversion pass.
-      // Block j of this stage is free once PV of tile it-2 has finished with it.
-#pragma unroll 1
-      for (int j = 0; j < kBlocks; ++j) {
-        if (k >= 1) wait_warp(c, bar_kv_empty(s, j), (k - 1) & 1);
-        if (c.misc->abort) break;
-        if (lane == 0) MLA_TRACE(1, st.it, 1 + j);
-        const uint32_t bar = bar_addr(c, bar_kv_full(s, j));
-        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, uint32_t(np) * (page_block_bytes / 2));  // the transaction count is in packed bytes
+      auto issue_block = [&](int j) {
+        if (st.lap >= 1) wait_warp(c, bar_kv_empty(st.slot), (st.lap - 1) & 1);  // PV of the block ten positions back has completed
+        if (!c.misc->abort) {
+          if (lane == 0) MLA_TRACE(1, st.it, 1 + j);
+          const uint32_t bar = bar_addr(c, bar_kv_full(st.slot));
+          if (lane == 0) ptx::mbar_arrive_expect_tx(bar, uint32_t(np) * (page_block_bytes / 2));  // the transaction count is in packed bytes
+          __syncwarp();
+          if (mine)
+            ptx::tma_load_3d(c.smem + kOffKV + st.slot * kBlockBytes + uint32_t(lane) * page_block_bytes, map_lat, bar, 128 * j, 0, pg);
+        }
+        st.advance(1);
+      };
+      issue_block(0);
+      issue_block(1);
+      // RoPE bytes: the one buffer is free once the two RoPE MMAs of the previous tile have completed
+      if (st.it >= 1) wait_warp(c, kBarRopeEmpty, (st.it - 1) & 1);
+      if (lane == 0) MLA_TRACE(1, st.it, 5);
+      if (!c.misc->abort) {
+        const uint32_t bar = bar_addr(c, kBarRopeFull);
+        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, uint32_t(np) * page_rope_bytes);
+        __syncwarp();
+        if (mine) ptx::tma_load_3d(c.smem + kOffRope + uint32_t(lane) * page_rope_bytes, map_rope, bar, kLatent / 2, 0, pg);
+        ++st.n_rope;
+      }
+      // per-token scales: this stage was last read by the softmax of tile it-2
+      if (lane == 0) MLA_TRACE(1, st.it, 6);
+      if (k >= 1) wait_warp(c, bar_s_empty(s), (k - 1) & 1);
+      if (lane == 0) MLA_TRACE(1, st.it, 7);
+      if (!c.misc->abort) {
+        const uint32_t bar = bar_addr(c, bar_sc_full(s));
+        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, uint32_t(np) * page_scale_bytes);
         __syncwarp();
         if (mine)
-          ptx::tma_load_3d(c.smem + kOffKV + (s * kBlocks + j) * kBlockBytes + uint32_t(lane) * page_block_bytes, map_lat, bar,
-                           128 * j, 0, pg);
+          ptx::bulk_load(c.smem + kOffScale + s * kTile * 4 + uint32_t(lane) * page_scale_bytes,
+                         p.kv_cache_sf + size_t(pg) * p.page_size, page_scale_bytes, bar);
+        ++st.n_sc;
       }
+      issue_block(2);
+      issue_block(3);
+      if (c.misc->abort) break;
       pg = pg1;
       pg1 = pg2;
       pg2 = pg3;
+      pg3 = pg4;
     }
   }
   if (c.misc->abort && lane == 0) {  // let copies that were issued but never consumed land before exit
-    for (uint32_t s = 0; s < kStages; ++s) {
-      const uint32_t used = (st.it + 1 - s) >> 1;  // tiles issued on stage s
-      if (used >= 1) {
-        drain_wait(c, bar_aux_full(s), (used - 1) & 1);
-        for (int j = 0; j < kBlocks; ++j) drain_wait(c, bar_kv_full(s, j), (used - 1) & 1);
-      }
+    // Whatever has been armed either completes (its copies were issued) or never will (a page id was refused): a
+    // bounded look at every barrier that can still be in its current phase is enough.
+    for (int slot = 0; slot < kRing; ++slot) {
+      const uint32_t pos = st.slot, lap = st.lap;  // next position to be filled: positions before it were armed
+      const bool used = lap > 0 || uint32_t(slot) < pos;
+      if (used) drain_wait(c, bar_kv_full(slot), ((uint32_t(slot) < pos ? lap : lap - 1)) & 1);
     }
+    const uint32_t n_rope = st.n_rope, n_sc = st.n_sc;
+    if (n_rope >= 1) drain_wait(c, kBarRopeFull, (n_rope - 1) & 1);
+    if (n_sc >= 1) drain_wait(c, bar_sc_full((n_sc - 1) & 1), ((n_sc - 1) >> 1) & 1);
+    if (n_sc >= 2) drain_wait(c, bar_sc_full(n_sc & 1), ((n_sc - 2) >> 1) & 1);
     if (st.seg >= 1) drain_wait(c, kBarQFull, (st.seg - 1) & 1);
   }
   __syncwarp();
@@ -345,29 +384,23 @@ __device__ __forceinline__ Desc make_desc(uint32_t addr, uint32_t lbo, uint32_t 
 }
 // Descriptors of every operand, built once.
 struct MmaDescs {
-  Desc kv_k;    // K tile block, K-major, 128B swizzle          (+ (stage*4+block)*1024 + kstep*2)
-  Desc kv_mn;   // same bytes as V^T, MN-major                  (+ (stage*4+block)*1024 + kstep*256)
+  Desc kv_k;    // K tile block, K-major, 128B swizzle          (+ ring block * 1024 + kstep*2)
+  Desc kv_mn;   // same bytes as V^T, MN-major                  (+ ring block * 1024 + kstep*256)
   Desc q_lat;   // Q latent block, K-major, 128B swizzle        (+ block*512 + kstep*2)
-  Desc rope;    // K rope, K-major, 64B swizzle                 (+ stage*512 + kstep*2)
+  Desc rope;    // K rope, K-major, 64B swizzle                 (+ kstep*2)
   Desc q_rope;  // Q rope                                       (+ kstep*2)
-  Desc p;       // P^T hi, MN-major, 64B swizzle                (+ stage*1024 + lo*512 + kstep*128)
+  Desc p;       // P^T hi, MN-major, 64B swizzle                (+ lo*512 + kstep*128)
 };
 
-// QK^T of one 128-dim block of tile `it` (4 MMAs); with the first block also the RoPE part, after the
-// last block the commit that hands S to the softmax warps.  The caller has seen the operands' barriers complete.
-__device__ __forceinline__ void issue_qk_block(const Ctx& c, const MmaDescs& d, uint32_t it, uint32_t j, uint32_t tmem) {
+// QK^T of one 128-dim block of tile `it` held in ring block `slot` (4 MMAs); after the last block the commit that
+// hands S to the softmax warps.  The caller has seen the operands' barriers complete.
+__device__ __forceinline__ void issue_qk_block(const Ctx& c, const MmaDescs& d, uint32_t it, uint32_t j, uint32_t slot, uint32_t tmem) {
   const uint32_t s = it & 1;
   const uint32_t d_lat = tmem + kColSLat + 64u * s;
-  const uint32_t a_off = (s * kBlocks + j) * (kBlockBytes >> 4);
+  const uint32_t a_off = slot * (kBlockBytes >> 4);
   const uint32_t b_off = j * ((kGroupHeads * 128) >> 4);
   ptx::tc_fence_after();
   if (ptx::elect_one()) {
-    if (j == 0) {  // the RoPE part first: its operands arrive by TMA long before the last latent block
-      const uint32_t d_rope = tmem + kColSRope + 64u * s;
-      const uint32_t r_off = s * ((kTile * 64) >> 4);
-#pragma unroll
-      for (uint32_t ks = 0; ks < 2; ++ks) ptx::umma_f8(d_rope, d.rope.at(r_off + 2 * ks), d.q_rope.at(2 * ks), kIdescQKRope, ks);
-    }
 #pragma unroll
     for (uint32_t ks = 0; ks < 4; ++ks)
       ptx::umma_f8(d_lat, d.kv_k.at(a_off + 2 * ks), d.q_lat.at(b_off + 2 * ks), kIdescQK, (j | ks) ? 1u : 0u);
@@ -375,32 +408,36 @@ __device__ __forceinline__ void issue_qk_block(const Ctx& c, const MmaDescs& d, 
   }
   __syncwarp();
 }
-
-// PV of tile `it`, blocks [j_begin, j_end): per block 4 token steps x (hi, lo); every block commits the barrier that frees it.
-__device__ __forceinline__ void issue_pv(const Ctx& c, const MmaDescs& d, uint32_t it, uint32_t tmem, bool first_of_segment,
-                                         uint32_t j_begin, uint32_t j_end) {
-  const uint32_t s = it & 1;
+// The RoPE part of QK^T of tile `it` (2 MMAs), first in the tile: its commit frees the one RoPE buffer for the next tile.
+__device__ __forceinline__ void issue_qk_rope(const Ctx& c, const MmaDescs& d, uint32_t it, uint32_t tmem) {
+  const uint32_t d_rope = tmem + kColSRope + 64u * (it & 1);
   ptx::tc_fence_after();
-  const uint32_t p_hi = s * ((2 * kTile * 64) >> 4);
-  const uint32_t p_lo = p_hi + ((kTile * 64) >> 4);
-  const uint32_t acc0 = first_of_segment ? 0u : 1u;
+  if (ptx::elect_one()) {
 #pragma unroll
-  for (uint32_t j = j_begin; j < j_end; ++j) {
-    // A = V^T block: MN-major, 128-byte swizzle; 32 tokens per step = 4 groups of 8 rows (4096 B)
-    const uint32_t a_off = (s * kBlocks + j) * (kBlockBytes >> 4);
-    const uint32_t dd = tmem + kColO + 64u * j;
-    if (ptx::elect_one()) {
-#pragma unroll
-      for (uint32_t ks = 0; ks < 4; ++ks) {
-        // B = P^T: MN-major (64 heads contiguous), 64-byte swizzle; 32 tokens per step = 2048 B.
-        // The hi and the lo term share A: it is fetched once and kept in the collector for the second.
-        ptx::umma_f8_a_fill(dd, d.kv_mn.at(a_off + 256 * ks), d.p.at(p_hi + 128 * ks), kIdescPV, ks ? 1u : acc0);
-        ptx::umma_f8_a_lastuse(dd, d.kv_mn.at(a_off + 256 * ks), d.p.at(p_lo + 128 * ks), kIdescPV, 1u);
-      }
-      ptx::umma_commit(bar_addr(c, bar_kv_empty(s, j)));
-    }
-    __syncwarp();
+    for (uint32_t ks = 0; ks < 2; ++ks) ptx::umma_f8(d_rope, d.rope.at(2 * ks), d.q_rope.at(2 * ks), kIdescQKRope, ks);
+    ptx::umma_commit(bar_addr(c, kBarRopeEmpty));
   }
+  __syncwarp();
+}
+
+// PV of one 128-dim block of a tile held in ring block `slot`: 4 token steps x (hi, lo); the commit frees the ring block.
+__device__ __forceinline__ void issue_pv_block(const Ctx& c, const MmaDescs& d, uint32_t j, uint32_t slot, uint32_t tmem, bool first_of_segment) {
+  const uint32_t p_hi = 0, p_lo = (kTile * 64) >> 4;
+  const uint32_t acc0 = first_of_segment ? 0u : 1u;
+  // A = V^T block: MN-major, 128-byte swizzle; 32 tokens per step = 4 groups of 8 rows (4096 B)
+  const uint32_t a_off = slot * (kBlockBytes >> 4);
+  const uint32_t dd = tmem + kColO + 64u * j;
+  if (ptx::elect_one()) {
+#pragma unroll
+    for (uint32_t ks = 0; ks < 4; ++ks) {
+      // B = P^T: MN-major (64 heads contiguous), 64-byte swizzle; 32 tokens per step = 2048 B.
+      // The hi and the lo term share A: it is fetched once and kept in the collector for the second.
+      ptx::umma_f8_a_fill(dd, d.kv_mn.at(a_off + 256 * ks), d.p.at(p_hi + 128 * ks), kIdescPV, ks ? 1u : acc0);
+      ptx::umma_f8_a_lastuse(dd, d.kv_mn.at(a_off + 256 * ks), d.p.at(p_lo + 128 * ks), kIdescPV, 1u);
+    }
+    ptx::umma_commit(bar_addr(c, bar_kv_empty(slot)));
+  }
+  __syncwarp();
 }
 
 // QK^T and PV are issued by two different warps.  Each runs straight-line code with blocking waits, so
@@ -430,15 +467,17 @@ __device__ __forceinline__ void qk_role(const Ctx& c, uint32_t tmem, RoleState& 
 #pragma unroll 1
     for (uint32_t t = 0; t < n && ok; ++t) {
       const uint32_t it = st.it + t, s = it & 1, k = it >> 1;
-      // S of this stage has been read by the softmax of tile it-2; RoPE bytes of this tile have landed
+      // S of this stage has been read by the softmax of tile it-2; the RoPE bytes of this tile have landed
       if (k >= 1) ok = wait_warp(c, bar_s_empty(s), (k - 1) & 1);
-      ok = ok && wait_warp(c, bar_aux_full(s), k & 1);
+      ok = ok && wait_warp(c, kBarRopeFull, it & 1);
       MLA_TRACE(2, it, 0);
+      if (ok) issue_qk_rope(c, d, it, tmem);
 #pragma unroll
       for (uint32_t j = 0; j < kBlocks; ++j) {
-        ok = ok && wait_warp(c, bar_kv_full(s, j), k & 1);
+        ok = ok && wait_warp(c, bar_kv_full(st.slot), st.lap & 1);
         MLA_TRACE(2, it, j == 0 ? 7 : (j == 1 ? 1 : (j == 2 ? 6 : 3)));  // block j has landed
-        if (ok) issue_qk_block(c, d, it, j, tmem);
+        if (ok) issue_qk_block(c, d, it, j, st.slot, tmem);
+        st.advance(1);
       }
       MLA_TRACE(2, it, 2);
     }
@@ -462,12 +501,20 @@ __device__ __forceinline__ void pv_role(const Ctx& c, uint32_t tmem, RoleState& 
     bool ok = st.seg == 0 || wait_warp(c, kBarOFree, (st.seg - 1) & 1);
 #pragma unroll 1
     for (uint32_t t = 0; t < n && ok; ++t) {
-      const uint32_t it = st.it + t, s = it & 1, k = it >> 1;
-      ok = wait_warp(c, bar_p_full(s), k & 1);
+      const uint32_t it = st.it + t;
+      ok = wait_warp(c, kBarPFull, it & 1);
       if (!ok) break;
       if (part == 0) MLA_TRACE(2, it, 4);
-      if (part == 0) issue_pv(c, d, it, tmem, t == 0, 0, kBlocks / 2);
-      else issue_pv(c, d, it, tmem, t == 0, kBlocks / 2, kBlocks);
+      ptx::tc_fence_after();
+      if (part == 1) st.advance(2);  // this warp's blocks are the tile's third and fourth
+      issue_pv_block(c, d, 2 * part, st.slot, tmem, t == 0);
+      st.advance(1);
+      issue_pv_block(c, d, 2 * part + 1, st.slot, tmem, t == 0);
+      st.advance(1);
+      if (part == 0) st.advance(2);
+      // both warps' commits together tell the softmax warps that P may be overwritten
+      if (ptx::elect_one()) ptx::umma_commit(bar_addr(c, kBarPEmpty));
+      __syncwarp();
       if (part == 1) MLA_TRACE(2, it, 5);
     }
     st.it += n;
@@ -570,9 +617,13 @@ struct SoftmaxTile {
   uint64_t sc2, cs2;       // (scale_t, scale_t), (c, c)
   bool valid;
 };
+// A thread's P' of one tile: 32 heads x (hi, lo) as bytes, kept in registers until the P buffer is free.
+struct PRegs {
+  uint32_t hi[8], lo[8];
+};
 
 // One pass over the 32 heads this thread owns of its token: e = exp2(x*c - m) and P' = e*scale_t split into two
-// E4M3 terms and written to the swizzled P rows.
+// E4M3 terms (left in registers: the one P buffer may still be in use by the PV of the previous tile).
 //
 // First pass (kSecond = false), speculative, with the reference as it stands: the row sums take e, and the largest
 // exponent argument seen is returned for the lazy-reference check.  An argument above kArgCap is clamped before it
@@ -582,6 +633,9 @@ struct SoftmaxTile {
 // Second pass (kSecond = true), after a refresh that moved the reference of head h by delta_h: the caller has scaled the
 // sums by f = 2^-delta, which turns every e of the first pass into its new value, (l + e_old) * f = l * f + e_new,
 // except where the first pass clamped: there 2^(kArgCap - delta) went in instead of e_new, and this pass adds the difference.
+//
+// The pass is bound by instruction issue (two softmax warps per scheduler), so it is written for the fewest
+// instructions per pair of heads; a version that collected the arguments of a chunk first measured 25 % slower.
 constexpr float kArgCap = 64.f;
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
@@ -594,7 +648,7 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   return d;
 }
 template <bool kSecond>
-__device__ __forceinline__ float softmax_pass(const SoftmaxTile& t, uint64_t (&l2)[kHalfHeads / 2]) {
+__device__ __forceinline__ float softmax_pass(const SoftmaxTile& t, uint64_t (&l2)[kHalfHeads / 2], PRegs& pr) {
   float mx = -INFINITY;
 #pragma unroll
   for (int cidx = 0; cidx < 2; ++cidx) {
@@ -602,56 +656,59 @@ __device__ __forceinline__ float softmax_pass(const SoftmaxTile& t, uint64_t (&l
     ptx::tmem_ld16(t.t_lat + 16 * cidx, a);
     ptx::tmem_ld16(t.t_rope + 16 * cidx, b);
     ptx::tmem_wait_ld();
-    const uint32_t off = (((2 * t.half + uint32_t(cidx)) ^ t.psw) << 4);
-    if (t.valid) {
-      // exponent arguments of the chunk's 16 heads against the current references
-      float arg[16];
-      float cm = -INFINITY;
+    uint32_t hi16[8], lo16[8];
+    if (!t.valid) {  // token beyond seq_len: weight exactly zero, whatever its row holds (its RoPE bytes may decode to NaN)
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {  // 4 heads per shared load of the references
-        uint64_t nm0, nm1;
-        lds_pairs(t.negm + 64 * cidx + 16 * q, nm0, nm1);
+      for (int q = 0; q < 8; ++q) hi16[q] = lo16[q] = 0u;
+    } else {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int i = 4 * q + 2 * h;
-          const uint64_t x2 = fma2(pack2u(a[i], a[i + 1]), t.sc2, pack2u(b[i], b[i + 1]));
-          unpack2(fma2(x2, t.cs2, h ? nm1 : nm0), arg[i], arg[i + 1]);
-          cm = max3(cm, arg[i], arg[i + 1]);
-        }
-      }
-      if (!kSecond) {
-        mx = fmaxf(mx, cm);
-        if (cm > kArgCap) {  // rare: one compare and branch per chunk instead of a clamp per value
+    for (int q = 0; q < 4; ++q) {  // 4 heads per shared load of the references
+      uint64_t nm0, nm1, dl0 = 0, dl1 = 0;
+      lds_pairs(t.negm + 64 * cidx + 16 * q, nm0, nm1);
+      if (kSecond) lds_pairs(t.negm + (kOffDelta - kOffM) + 64 * cidx + 16 * q, dl0, dl1);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) arg[i] = fminf(arg[i], kArgCap);
-        }
-      }
-      uint32_t hi16[8], lo16[8];
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        const float e0 = ptx::ex2(arg[2 * q]), e1 = ptx::ex2(arg[2 * q + 1]);
-        const uint64_t e2 = pack2(e0, e1);
+      for (int h = 0; h < 2; ++h) {
+        const int i = 4 * q + 2 * h;
+        const uint64_t x2 = fma2(pack2u(a[i], a[i + 1]), t.sc2, pack2u(b[i], b[i + 1]));
+        const uint64_t arg2 = fma2(x2, t.cs2, h ? nm1 : nm0);
+        float a0, a1;
+        unpack2(arg2, a0, a1);
+        uint64_t e2;
         if (!kSecond) {
-          l2[8 * cidx + q] = add2(l2[8 * cidx + q], e2);
+          mx = max3(mx, a0, a1);
+          e2 = pack2(ptx::ex2(fminf(a0, kArgCap)), ptx::ex2(fminf(a1, kArgCap)));
+          l2[8 * cidx + 2 * q + h] = add2(l2[8 * cidx + 2 * q + h], e2);
         } else {
-          const float d0 = lds_f32(t.negm + (kOffDelta - kOffM) + 64 * cidx + 8 * q);
-          const float d1 = lds_f32(t.negm + (kOffDelta - kOffM) + 64 * cidx + 8 * q + 4);
-          const float c0 = (arg[2 * q] + d0 > kArgCap) ? e0 - ptx::ex2(kArgCap - d0) : 0.f;
-          const float c1 = (arg[2 * q + 1] + d1 > kArgCap) ? e1 - ptx::ex2(kArgCap - d1) : 0.f;
-          l2[8 * cidx + q] = add2(l2[8 * cidx + q], pack2(c0, c1));
+          const float e0 = ptx::ex2(a0), e1 = ptx::ex2(a1);
+          e2 = pack2(e0, e1);
+          float d0, d1;
+          unpack2(h ? dl1 : dl0, d0, d1);
+          const float c0 = (a0 + d0 > kArgCap) ? e0 - ptx::ex2(kArgCap - d0) : 0.f;
+          const float c1 = (a1 + d1 > kArgCap) ? e1 - ptx::ex2(kArgCap - d1) : 0.f;
+          l2[8 * cidx + 2 * q + h] = add2(l2[8 * cidx + 2 * q + h], pack2(c0, c1));
         }
-        hi16[q] = split_e4m3x2(mul2(e2, t.sc2), lo16[q]);
+        hi16[2 * q + h] = split_e4m3x2(mul2(e2, t.sc2), lo16[2 * q + h]);
       }
-      asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(t.p_hi + off), "r"(hi16[0] | (hi16[1] << 16)),
-                   "r"(hi16[2] | (hi16[3] << 16)), "r"(hi16[4] | (hi16[5] << 16)), "r"(hi16[6] | (hi16[7] << 16)) : "memory");
-      asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(t.p_lo + off), "r"(lo16[0] | (lo16[1] << 16)),
-                   "r"(lo16[2] | (lo16[3] << 16)), "r"(lo16[4] | (lo16[5] << 16)), "r"(lo16[6] | (lo16[7] << 16)) : "memory");
-    } else {  // token beyond seq_len: weight exactly zero, whatever its row holds
-      asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(t.p_hi + off), "r"(0u) : "memory");
-      asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(t.p_lo + off), "r"(0u) : "memory");
+    }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      pr.hi[4 * cidx + q] = hi16[2 * q] | (hi16[2 * q + 1] << 16);
+      pr.lo[4 * cidx + q] = lo16[2 * q] | (lo16[2 * q + 1] << 16);
     }
   }
   return mx;
+}
+// Write a thread's P' row (32 of the 64 heads, hi and lo) to the swizzled P buffer.
+__device__ __forceinline__ void store_p(const SoftmaxTile& t, const PRegs& pr) {
+#pragma unroll
+  for (int cidx = 0; cidx < 2; ++cidx) {
+    const uint32_t off = (((2 * t.half + uint32_t(cidx)) ^ t.psw) << 4);
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(t.p_hi + off), "r"(pr.hi[4 * cidx]), "r"(pr.hi[4 * cidx + 1]),
+                 "r"(pr.hi[4 * cidx + 2]), "r"(pr.hi[4 * cidx + 3]) : "memory");
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(t.p_lo + off), "r"(pr.lo[4 * cidx]), "r"(pr.lo[4 * cidx + 1]),
+                 "r"(pr.lo[4 * cidx + 2]), "r"(pr.lo[4 * cidx + 3]) : "memory");
+  }
 }
 
 // Refresh the per-head reference: column max of y = x*c + log2(scale_t) over the tile's tokens,
@@ -719,40 +776,44 @@ __device__ __noinline__ void write_output(const DecodeParams& p, const Ctx& c, u
   const float post = direct ? 1.f : 1.f / slot_scale_v;  // a partial is stored divided by its slot scale
   const uint32_t esz = uint32_t(out_elem_bytes(p.out_dtype));
 #pragma unroll 1
-  for (int it = 0; it < kBlocks * 2; ++it) {
-    const int jb = it >> 1, h0 = 32 * half + 16 * (it & 1);  // block of 128 dims, first of 16 heads
-    uint32_t o[16];
-    ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(jb) + uint32_t(h0), o);
-    float li[16];  // output_scale / l of the 16 heads
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const float4 f = lds_f32x4(c.smem + kOffLinv + 4 * (h0 + 4 * q));
-      li[4 * q] = f.x; li[4 * q + 1] = f.y; li[4 * q + 2] = f.z; li[4 * q + 3] = f.w;
-    }
-    ptx::tmem_wait_ld();
+  for (int jb = 0; jb < kBlocks; ++jb) {  // a block of 128 dims: this thread's 32 heads as two TMEM loads in flight together
+    uint32_t o[2][16];
+    ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(jb) + uint32_t(32 * half), o[0]);
+    ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(jb) + uint32_t(32 * half + 16), o[1]);
     const int dim = 128 * jb + row;
-    float v[16];
+    ptx::tmem_wait_ld();
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(o[i]) * (li[i] * post);
-    if (!direct) {
-      uint32_t pk[8];
+    for (int hh = 0; hh < 2; ++hh) {
+      const int h0 = 32 * half + 16 * hh;
+      float v[16];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        __half2 h2 = __floats2half2_rn(v[2 * q], v[2 * q + 1]);
-        pk[q] = *reinterpret_cast<uint32_t*>(&h2);
+      for (int q = 0; q < 4; ++q) {  // output_scale / l of four heads per shared load
+        const float4 f = lds_f32x4(c.smem + kOffLinv + 4 * (h0 + 4 * q));
+        v[4 * q] = __uint_as_float(o[hh][4 * q]) * (f.x * post);
+        v[4 * q + 1] = __uint_as_float(o[hh][4 * q + 1]) * (f.y * post);
+        v[4 * q + 2] = __uint_as_float(o[hh][4 * q + 2]) * (f.z * post);
+        v[4 * q + 3] = __uint_as_float(o[hh][4 * q + 3]) * (f.w * post);
       }
-      // the warp's 32 dims x 8 heads are 512 contiguous bytes of the slot
-      *reinterpret_cast<uint4*>(so + slot_o_index(dim, h0)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-      *reinterpret_cast<uint4*>(so + slot_o_index(dim, h0 + 8)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-    } else {
-      char* dst = static_cast<char*>(p.out) + ((row0 + h0) * kLatent + dim) * esz;
+      if (!direct) {
+        uint32_t pk[8];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        if (h0 + i < heads_here) {
-          char* d = dst + size_t(i) * kLatent * esz;
-          if (p.out_dtype == MLA_FP4_OUT_BF16) *reinterpret_cast<__nv_bfloat16*>(d) = __float2bfloat16_rn(v[i]);
-          else if (p.out_dtype == MLA_FP4_OUT_F32) *reinterpret_cast<float*>(d) = v[i];
-          else *reinterpret_cast<uint8_t*>(d) = __nv_cvt_float_to_fp8(v[i], __NV_SATFINITE, __NV_E4M3);
+        for (int q = 0; q < 8; ++q) {
+          __half2 h2 = __floats2half2_rn(v[2 * q], v[2 * q + 1]);
+          pk[q] = *reinterpret_cast<uint32_t*>(&h2);
+        }
+        // the warp's 32 dims x 8 heads are 512 contiguous bytes of the slot
+        *reinterpret_cast<uint4*>(so + slot_o_index(dim, h0)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4*>(so + slot_o_index(dim, h0 + 8)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+      } else {
+        char* dst = static_cast<char*>(p.out) + ((row0 + h0) * kLatent + dim) * esz;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          if (h0 + i < heads_here) {
+            char* d = dst + size_t(i) * kLatent * esz;
+            if (p.out_dtype == MLA_FP4_OUT_BF16) *reinterpret_cast<__nv_bfloat16*>(d) = __float2bfloat16_rn(v[i]);
+            else if (p.out_dtype == MLA_FP4_OUT_F32) *reinterpret_cast<float*>(d) = v[i];
+            else *reinterpret_cast<uint8_t*>(d) = __nv_cvt_float_to_fp8(v[i], __NV_SATFINITE, __NV_E4M3);
+          }
         }
       }
     }
@@ -796,7 +857,7 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       const bool first = tt == g.tile_begin;
       if (tid == 0) MLA_TRACE(0, it, 0);
       // per-token scale
-      wait(c, bar_aux_full(s), k & 1);
+      wait(c, bar_sc_full(s), k & 1);
       t.valid = (tt * kTile + row) < g.seq_len;
       float sc = lds_f32(c.smem + kOffScale + 4 * (s * kTile + row));
       sc = t.valid ? sc : 0.f;
@@ -805,14 +866,9 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       t.sc2 = pack2(sc, sc);
       t.t_lat = tmem_lane + kColSLat + 64u * s + uint32_t(kHalfHeads * half);
       t.t_rope = tmem_lane + kColSRope + 64u * s + uint32_t(kHalfHeads * half);
-      t.p_hi = c.smem + kOffP + s * 2 * kTile * 64 + uint32_t(row) * 64u;
+      t.p_hi = c.smem + kOffP + uint32_t(row) * 64u;
       t.p_lo = t.p_hi + kTile * 64;
 
-      // the P buffer of this stage is free once PV of tile it-2 has completed
-      if (k >= 1) {  // both PV issue warps' last blocks
-        wait(c, bar_kv_empty(s, 1), (k - 1) & 1);
-        wait(c, bar_kv_empty(s, 3), (k - 1) & 1);
-      }
       wait(c, bar_s_full(s), k & 1);
       if (tid == 0) MLA_TRACE(0, it, 1);
       ptx::tc_fence_after();
@@ -823,9 +879,11 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
 
       // Speculative pass with the current reference.  It stands unless some score beat the
       // reference by more than the lazy threshold (P' would leave the E4M3 range).
-      const float mx = softmax_pass<false>(t, l2);
+      PRegs pr;
+      const float mx = softmax_pass<false>(t, l2, pr);
       const bool need = t.valid && (mx + lg > kPShift + kLazyThreshold);
-      if (ptx::bar_or(1, kSoftmaxThreads, need)) {
+      const bool refresh = ptx::bar_or(1, kSoftmaxThreads, need);
+      if (refresh) {
         // Refresh the reference.  (l + e_old) * f equals l * f + e_new, so the row sums only need
         // the factor; O^T is rescaled in TMEM; P' is recomputed with the new reference.
         refresh_reference(c, t.t_lat, t.t_rope, sc, t.valid, cscale, lg, true, tid);
@@ -836,20 +894,22 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
           l2[2 * q] = mul2(l2[2 * q], f0);
           l2[2 * q + 1] = mul2(l2[2 * q + 1], f1);
         }
-        if (!first) {  // O^T holds earlier tiles: rescale once their PV has completed
-          const uint32_t pit = it - 1;
-          wait(c, bar_kv_empty(pit & 1, 1), (pit >> 1) & 1);
-          wait(c, bar_kv_empty(pit & 1, 3), (pit >> 1) & 1);
-          ptx::tc_fence_after();
-          rescale_output(c, tmem_lane, uint32_t(half));
-        }
-        (void)softmax_pass<true>(t, l2);
+        (void)softmax_pass<true>(t, l2, pr);
       }
       if (tid == 0) MLA_TRACE(0, it, 3);
-      ptx::tc_fence_before();  // orders the S reads and any O rescale before the arrives
+      ptx::tc_fence_before();  // orders the S reads before the arrive
       ptx::mbar_arrive(bar_addr(c, bar_s_empty(s)));
+      // The one P buffer (and, for a rescale, O^T) is free once the PV of the previous tile has completed; until then
+      // this tile's P' stays in registers.
+      if (it >= 1) wait(c, kBarPEmpty, (it - 1) & 1);
+      if (refresh && !first) {  // O^T holds earlier tiles of the segment: rescale it
+        ptx::tc_fence_after();
+        rescale_output(c, tmem_lane, uint32_t(half));
+        ptx::tc_fence_before();
+      }
+      store_p(t, pr);
       ptx::fence_proxy_async_smem();
-      ptx::mbar_arrive(bar_addr(c, bar_p_full(s)));
+      ptx::mbar_arrive(bar_addr(c, kBarPFull));
       if (tid == 0) MLA_TRACE(0, it, 5);
     }
 
@@ -870,8 +930,7 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       }
       ptx::bar_sync(1, kSoftmaxThreads);
       // wait for the PV of the last tile
-      wait(c, bar_kv_empty(lit & 1, 1), (lit >> 1) & 1);
-      wait(c, bar_kv_empty(lit & 1, 3), (lit >> 1) & 1);
+      wait(c, kBarPEmpty, lit & 1);
       ptx::tc_fence_after();
       float sc_all = 0.f;
 #pragma unroll
@@ -1264,16 +1323,19 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
     ptx::tmem_alloc(c.smem + kOffMisc + offsetof(Misc, tmem_base), 512);
     ptx::tmem_relinquish();
   } else if (warp == kWarpTMA && (tid & 31) == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      for (int j = 0; j < kBlocks; ++j) {
-        ptx::mbar_init(bar_addr(c, bar_kv_full(s, j)), 1);
-        ptx::mbar_init(bar_addr(c, bar_kv_empty(s, j)), 1);
-      }
-      ptx::mbar_init(bar_addr(c, bar_aux_full(s)), 1);
+    for (int slot = 0; slot < kRing; ++slot) {
+      ptx::mbar_init(bar_addr(c, bar_kv_full(slot)), 1);
+      ptx::mbar_init(bar_addr(c, bar_kv_empty(slot)), 1);
+    }
+    for (int s = 0; s < kSStages; ++s) {
+      ptx::mbar_init(bar_addr(c, bar_sc_full(s)), 1);
       ptx::mbar_init(bar_addr(c, bar_s_full(s)), 1);
       ptx::mbar_init(bar_addr(c, bar_s_empty(s)), kSoftmaxThreads);
-      ptx::mbar_init(bar_addr(c, bar_p_full(s)), kSoftmaxThreads);
     }
+    ptx::mbar_init(bar_addr(c, kBarRopeFull), 1);
+    ptx::mbar_init(bar_addr(c, kBarRopeEmpty), 1);
+    ptx::mbar_init(bar_addr(c, kBarPFull), kSoftmaxThreads);
+    ptx::mbar_init(bar_addr(c, kBarPEmpty), 2);  // the two PV issue warps
     ptx::mbar_init(bar_addr(c, kBarQFull), 1);
     ptx::mbar_init(bar_addr(c, kBarQEmpty), 1);
     ptx::mbar_init(bar_addr(c, kBarOFree), kSoftmaxThreads);
@@ -1306,6 +1368,10 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   st.it = 0;
   st.seg = 0;
   st.part = 0;
+  st.slot = 0;
+  st.lap = 0;
+  st.n_rope = 0;
+  st.n_sc = 0;
   // Rounds: almost always exactly one; more only when a CTA's range spans more than kMaxSeg requests.
   for (;;) {
     if (warp >= kWarpSoftmax0) {

@@ -36,6 +36,25 @@ struct CombineParams {
   int32_t seq_cap;  // as in DecodeParams
 };
 
+// Exchange block of the context-parallel exchange (cp_exchange.cu): words of its 256-byte header, and where the
+// partial of rank `src` lies in the gather area that follows (two parities, `n` floats per partial).
+constexpr int kCpPushedWord = 8, kCpFinishedWord = 9, kCpStepWord = 10;
+constexpr size_t kCpHeaderBytes = 256;
+__host__ __device__ inline float* cp_gather(void* block, int parity, int world, int src, int64_t n) {
+  return reinterpret_cast<float*>(static_cast<char*>(block) + kCpHeaderBytes) + (int64_t(parity) * world + src) * n;
+}
+struct CpExchangeParams {
+  void* block[8];     // exchange block of every rank as mapped into this process (own block at [rank])
+  const float* part;  // this rank's packed partial: [rows][512] f32, then [rows] f32 LSEs (n floats in all, n % 4 == 0)
+  int64_t rows, n;
+  void* out;
+  float* lse;
+  int32_t* status;
+  int32_t world, rank, out_dtype;
+  uint32_t wait_polls;
+};
+cudaError_t launch_cp_exchange_merge(const CpExchangeParams& p, int num_ctas, cudaStream_t stream);
+
 cudaError_t launch_combine(const CombineParams& p, cudaStream_t stream);
 cudaError_t launch_merge_partials(const float* po, const float* pl, int parts, int64_t rows, int64_t stride_o,
                                   int64_t stride_l, void* out, int out_dtype, float* lse, cudaStream_t stream);

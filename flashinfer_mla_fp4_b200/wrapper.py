@@ -146,8 +146,12 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         out: Optional[torch.Tensor] = None,
         kv_cache_sf: Optional[torch.Tensor] = None,
         return_lse: bool = False,
+        lse_out: Optional[torch.Tensor] = None,
     ) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
-        """One decode step on torch's current stream; asynchronous, CUDA-graph capturable."""
+        """One decode step on torch's current stream; asynchronous, CUDA-graph capturable.
+
+        ``lse_out`` (f32, contiguous [batch, q_len, num_heads], on q's device) receives the base-2 LSE in
+        place when ``return_lse`` is set, instead of a freshly allocated tensor."""
         if not self._planned:
             raise RuntimeError("Call plan() before run().")
         self._validate_run_inputs(q, kv_cache, kv_cache_sf, out)
@@ -204,7 +208,15 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
             out = torch.empty((batch_size, q_len, num_heads, self._kv_lora_rank), dtype=self._o_dtype, device=q.device)
         elif tuple(out.shape) != (batch_size, q_len, num_heads, self._kv_lora_rank) or not out.is_contiguous():
             raise ValueError("out must be a contiguous [batch, q_len, num_heads, 512] tensor")
-        lse = torch.empty((batch_size, q_len, num_heads), dtype=torch.float32, device=q.device) if return_lse else None
+        lse = None
+        if return_lse:
+            if lse_out is not None:
+                if (lse_out.dtype != torch.float32 or tuple(lse_out.shape) != (batch_size, q_len, num_heads)
+                        or not lse_out.is_contiguous() or lse_out.device != q.device):
+                    raise ValueError("lse_out must be a contiguous float32 [batch, q_len, num_heads] tensor on the device of q")
+                lse = lse_out
+            else:
+                lse = torch.empty((batch_size, q_len, num_heads), dtype=torch.float32, device=q.device)
         cache_seqs = seq_lens if seq_lens.dtype == torch.int32 else seq_lens.to(torch.int32)
         if not cache_seqs.is_contiguous():
             cache_seqs = cache_seqs.contiguous()

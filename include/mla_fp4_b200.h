@@ -161,6 +161,35 @@ int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, i
                            int64_t rows, int64_t part_stride_out, int64_t part_stride_lse, void* out,
                            int32_t out_dtype, float* lse, void* stream);
 
+/* Decode context parallel without a library collective (no counterpart in the reference, which has no
+   multi-GPU path).  Every rank owns an "exchange block" of device memory that all peers map through CUDA
+   IPC; mla_fp4_cp_exchange_merge is ONE kernel per rank and step that pushes the rank's partial into every
+   peer's block with plain stores over NVLink, raises a flag there, waits (bounded) for the flags of all
+   peers in its own block and merges.  One process per GPU, all GPUs in one NVLink domain, at most
+   MLA_FP4_CP_MAX_RANKS ranks; every rank must make the same sequence of calls.
+     mla_fp4_cp_exchange_bytes: size of a block for partials of up to max_rows rows (rows = batch*q_len*heads).
+     mla_fp4_cp_alloc:  allocates (cudaMalloc) and zeroes this rank's block and returns its IPC handle
+                        (MLA_FP4_CP_HANDLE_BYTES bytes) for the caller to send to the peers.  Allocates and
+                        synchronises; call it once, at set-up.
+     mla_fp4_cp_open / _close: map / unmap a peer's block from its handle.   mla_fp4_cp_free: free the own block.
+     mla_fp4_cp_exchange_merge: blocks[world] are the blocks as mapped here (own block at [rank]); partial is this
+                        rank's packed partial, f32 [rows][512] followed by f32 [rows] LSEs (base 2), 16-byte
+                        aligned, as mla_fp4_decode writes them with out_dtype F32 and lse pointing behind the rows;
+                        out [rows][512] (out_dtype), optional lse [rows]; status as in MlaFp4DecodeArgs (word 0 set
+                        to MLA_FP4_ERR_DEVICE_TIMEOUT when a peer's flag does not arrive within wait_polls polls,
+                        0 = default); asynchronous on `stream`, CUDA-graph capturable (the step counter lives in
+                        the block). */
+#define MLA_FP4_CP_MAX_RANKS 8
+#define MLA_FP4_CP_HANDLE_BYTES 64
+int mla_fp4_cp_exchange_bytes(int32_t world, int64_t max_rows, size_t* bytes_out);
+int mla_fp4_cp_alloc(size_t bytes, void** block_out, unsigned char* handle_out);
+int mla_fp4_cp_open(const unsigned char* handle, void** block_out);
+int mla_fp4_cp_close(void* peer_block);
+int mla_fp4_cp_free(void* own_block);
+int mla_fp4_cp_exchange_merge(void* const* blocks, int32_t world, int32_t rank, const float* partial, int64_t rows,
+                              void* out, int32_t out_dtype, float* lse, int32_t* status, int32_t wait_polls,
+                              void* stream);
+
 /* Bit-exact E2M1 nibble -> E4M3 byte dequantisation of `n_bytes` packed bytes on the device
    (out holds 2*n_bytes E4M3 bytes, low nibble first).  Pins the table of
    tests/test_cute_dsl_mla_fp4.py:80-84.  (The decode kernel itself hands the packed codes to the

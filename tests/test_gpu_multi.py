@@ -1,5 +1,6 @@
-"""Two-rank GPU tests (NCCL): context-parallel decode equals the unsharded decode and the oracle;
-data-parallel attention needs no collective.  Run as child processes, one per GPU."""
+"""Two-rank GPU tests: context-parallel decode equals the oracle, with the one-kernel peer exchange (plain stores
+into the peers' memory over NVLink, flags, bounded waits) and with the NCCL all-gather + merge kernel; a peer that
+does not show up makes the bounded wait run out and is reported.  Run as child processes, one per GPU."""
 import os
 import socket
 import sys
@@ -37,18 +38,40 @@ def _cp_worker(rank: int, world: int, port: int, tmp: str) -> None:
         # a ragged batch with shards that are empty on one rank, and the shape of the context-parallel
         # benchmark configuration (B=8, H=64) at 4096 tokens per rank
         w = BatchMLADecodeCuteDSLFP4Wrapper(torch.empty(64 << 20, dtype=torch.int8, device=dev))
-        cp = ContextParallelDecoder(w, dist.group.WORLD)
-        for name, lens, seed in (("cp_ragged", [5000, 130, 64, 1, 9000, 777], 31), ("cp_b8", [4096 * world] * 8, 32)):
-            case = synth.build_case(name, lens, 64, 64, seed=seed, device=dev)
-            bt, sl = shard_context(case.block_tables, case.seq_lens, case.page_size, rank, world)
-            w.plan(num_heads=case.num_heads, page_size=case.page_size)
-            out, lse = cp.run(case.q, case.kv_cache, bt, sl, case.max_seq_len, case.softmax_scale,
-                              kv_cache_sf=case.kv_cache_sf, return_lse=True)
-            torch.cuda.synchronize()
-            ref, ref_lse = O.mla_decode(case.q, case.kv_cache, case.kv_cache_sf, case.block_tables, case.seq_lens,
-                                        case.softmax_scale)
-            O.assert_parity(out, ref, f"{name} rank {rank}")
-            torch.testing.assert_close(lse.cpu(), ref_lse, atol=2e-3, rtol=1e-4)
+        w.plan(num_heads=64, page_size=64)
+        outs = {}
+        for exchange in ("peer", "nccl"):
+            cp = ContextParallelDecoder(w, dist.group.WORLD, exchange=exchange)
+            for name, lens, seed in (("cp_ragged", [5000, 130, 64, 1, 9000, 777], 31), ("cp_b8", [4096 * world] * 8, 32)):
+                case = synth.build_case(name, lens, 64, 64, seed=seed, device=dev)
+                bt, sl = shard_context(case.block_tables, case.seq_lens, case.page_size, rank, world)
+                for rep in range(3):  # the peer exchange alternates between two buffers: go round more than once
+                    out, lse = cp.run(case.q, case.kv_cache, bt, sl, case.max_seq_len, case.softmax_scale,
+                                      kv_cache_sf=case.kv_cache_sf, return_lse=True)
+                torch.cuda.synchronize()
+                cp.check_device_status()
+                ref, ref_lse = O.mla_decode(case.q, case.kv_cache, case.kv_cache_sf, case.block_tables, case.seq_lens,
+                                            case.softmax_scale)
+                O.assert_parity(out, ref, f"{name} rank {rank} {exchange}")
+                torch.testing.assert_close(lse.cpu(), ref_lse, atol=2e-3, rtol=1e-4)
+                outs[(exchange, name)] = out.clone()
+            if exchange == "peer":
+                # Failure made on the host: rank 1 skips a step, so its flag never reaches rank 0, whose bounded wait
+                # runs out (a small poll budget here); the kernel returns and the status says so.  Nothing faults.
+                dist.barrier()
+                if rank == 0:
+                    cp._wait_polls = 2000
+                    cp.run(case.q, case.kv_cache, bt, sl, case.max_seq_len, case.softmax_scale, kv_cache_sf=case.kv_cache_sf)
+                    torch.cuda.synchronize()
+                    try:
+                        cp.check_device_status()
+                        raise AssertionError("the missing peer went unnoticed")
+                    except RuntimeError as e:
+                        assert "device error 5" in str(e)
+                dist.barrier()
+                cp.close()
+        for name in ("cp_ragged", "cp_b8"):  # same merge arithmetic either way
+            torch.testing.assert_close(outs[("peer", name)].float(), outs[("nccl", name)].float(), atol=1e-2, rtol=0)
         Path(tmp, f"ok{rank}").write_text("ok")
     finally:
         dist.destroy_process_group()
