@@ -353,6 +353,40 @@ def run_reference_gpu_arm(args, rank: int, world: int):
     except Exception as e:  # noqa: BLE001
         res["flashinfer_fp8_unavailable"] = f"unavailable on this box: {type(e).__name__}: {e}"[:600]
         res["flashinfer_fp8_trace"] = traceback.format_exc()[-800:]
+        # The installed release splits the KV only with 128 heads.  The nearest shape it accepts: the same requests with
+        # H = 128; the native kernel is timed on that very case beside it, so the pair is a same-box, same-shape comparison.
+        try:
+            from flashinfer.cute_dsl.attention.wrappers.batch_mla import BatchMLADecodeCuteDSLWrapper
+            from flashinfer_mla_fp4_b200 import BatchMLADecodeCuteDSLFP4Wrapper, synth
+
+            c128 = synth.build_case(case.name + "_h128", case.seq_lens_host, 128, case.page_size, 1, 1400, device)
+            lat, _ = O.dequantize_cache(c128.kv_cache.cpu(), c128.kv_cache_sf.cpu())
+            f8 = torch.cat((lat.to(torch.float8_e4m3fn).view(torch.uint8), c128.kv_cache.cpu()[..., 256:]), dim=-1).to(device)
+            n = min(16, max(2, -(-int(1.5 * L2_BYTES) // max(f8.numel(), 1))))
+            f8s = [f8.view(torch.float8_e4m3fn)] + [f8.clone().view(torch.float8_e4m3fn) for _ in range(n - 1)]
+            o128 = torch.empty(c128.batch, 1, 128, 512, dtype=torch.bfloat16, device=device)
+            w8 = BatchMLADecodeCuteDSLWrapper(ws)
+            w8.plan(**{**common, "num_heads": 128})
+
+            def step8h(i):
+                w8.run(q=c128.q, kv_cache=f8s[i % n], block_tables=c128.block_tables, seq_lens=c128.seq_lens,
+                       max_seq_len=c128.max_seq_len, softmax_scale=c128.softmax_scale, out=o128)
+
+            res["flashinfer_fp8_h128_us"] = timed(step8h, n)
+            del f8s
+            cs = cache_copies(c128)
+            wn = BatchMLADecodeCuteDSLFP4Wrapper(torch.empty(64 << 20, dtype=torch.int8, device=device))
+            wn.plan(num_heads=128, page_size=c128.page_size)
+
+            def stepn(i):
+                wn.run(c128.q, cs[i % len(cs)][0], c128.block_tables, c128.seq_lens, c128.max_seq_len, c128.softmax_scale,
+                       out=o128, kv_cache_sf=cs[i % len(cs)][1])
+
+            res["native_h128_us"] = timed(stepn, len(cs))
+            res["h128_label"] = (f"same requests with 128 heads: flashinfer {res['flashinfer_version']} FP8 kernel on the E4M3 cache "
+                                 "vs this library's FP4 kernel on the FP4 cache, same harness, same box")
+        except Exception as e2:  # noqa: BLE001
+            res["flashinfer_fp8_h128_unavailable"] = f"unavailable on this box: {type(e2).__name__}: {e2}"[:600]
     # (b) the reference's own FP4 kernel, unmodified sources from baseline/_ref, under a shim for its version gate
     try:
         ref_dir = ROOT / "baseline" / "_ref"
@@ -448,6 +482,10 @@ def main() -> None:
     from flashinfer_mla_fp4_b200.distributed import ContextParallelDecoder
 
     def barrier():
+        # The device is drained before the ranks meet: an NCCL barrier kernel launched beside a still running graph
+        # would share the GPU with kernels that need every SM (the decode kernel is a cooperative launch) or, in the
+        # "nccl" exchange, with another collective of the same communicator.
+        torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
@@ -536,18 +574,18 @@ def main() -> None:
         for j in range(copies):  # one captured step per cache copy, so the rotation (cold L2) stays
             step(j, q_d, bt_d, sl_d)
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
+            with torch.cuda.graph(g, stream=stream):  # H2D of the step's inputs, the step, D2H of its output: one graph launch per step
+                q_d.copy_(q_h, non_blocking=True)
+                bt_d.copy_(bt_h, non_blocking=True)
+                sl_d.copy_(sl_h, non_blocking=True)
                 step(j, q_d, bt_d, sl_d)
+                out_h.copy_(out, non_blocking=True)
             e2e_graphs.append(g)
     torch.cuda.synchronize()
 
     def e2e_step(i: int):
         with torch.cuda.stream(stream):
-            q_d.copy_(q_h, non_blocking=True)
-            bt_d.copy_(bt_h, non_blocking=True)
-            sl_d.copy_(sl_h, non_blocking=True)
             e2e_graphs[i % copies].replay()
-            out_h.copy_(out, non_blocking=True)
         stream.synchronize()  # the caller consumes the result of every step
 
     for i in range(warmup):
@@ -626,7 +664,7 @@ def main() -> None:
                          "roofline_us": max(t_hbm, t_fp8), "step_frac_of_roofline": max(t_hbm, t_fp8) / us,
                          "fp8_peak_tflops_assumed": fp8_peak},
             "e2e": {"value": e2e_us, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "how": "pinned host -> persistent device buffers, replay of the captured step, output -> pinned host, stream synchronize"},
+                    "how": "one captured graph per step: pinned host -> device copies of q, block tables, seq_lens; the decode step; output -> pinned host; then stream synchronize"},
             "gpu_launches": launches_per_step * K,
             "clocks": main_run["clocks"],
             "extra": extra,
@@ -637,8 +675,13 @@ def main() -> None:
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1:
+        # Leave without tearing the process group down: the captured graphs still hold NCCL work, and destroying the
+        # communicator under them has hung at exit.  Everything is measured and printed by now.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -119,8 +119,8 @@ def _load() -> C.CDLL:
     lib.mla_fp4_cp_close.restype = C.c_int
     lib.mla_fp4_cp_free.argtypes = [C.c_void_p]
     lib.mla_fp4_cp_free.restype = C.c_int
-    lib.mla_fp4_cp_exchange_merge.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_void_p, C.c_int64, C.c_void_p,
-                                              C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]
+    lib.mla_fp4_cp_exchange_merge.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p,
+                                              C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
     lib.mla_fp4_cp_exchange_merge.restype = C.c_int
     lib.mla_fp4_merge_partials.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
                                            C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]

@@ -136,6 +136,13 @@ class FP4MLADecodeBackend:
         (bf16, f16 or f32) are the new tokens' compressed KV and RoPE key, in request order; ``batch`` may
         be anything up to ``max_batch`` (rows the last ``prepare`` did not fill are padding).  Returns
         ``out`` [batch, q_len, H, 512].
+
+        With ``q_len`` > 1 all ``q_len`` new tokens are appended first and EVERY query position then attends to
+        all ``seq_len`` tokens, the later draft tokens included: there is no causal mask among the query
+        positions (the reference itself accepts only ``q_len`` = 1, wrappers/batch_mla_fp4.py:297-298).  That is
+        the attention of a batched multi-token step whose positions may see one another; a verification step of
+        speculative decoding that needs position i blind to positions > i must issue its positions as separate
+        requests (``q_len`` = 1, ``seq_len`` reduced accordingly).
         """
         batch = q.shape[0]
         if batch > self.max_batch or q.shape[1] != self.q_len:

@@ -273,8 +273,7 @@ int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, i
 
 int mla_fp4_cp_exchange_bytes(int32_t world, int64_t max_rows, size_t* bytes_out) {
   if (!bytes_out || world < 1 || world > MLA_FP4_CP_MAX_RANKS || max_rows < 0) return fail(MLA_FP4_ERR_BAD_ARG, "world/max_rows out of range");
-  const int64_t n = max_rows * mla::kLatent + ((max_rows + 3) / 4) * 4;
-  *bytes_out = mla::kCpHeaderBytes + size_t(2) * size_t(world) * size_t(n) * sizeof(float);
+  *bytes_out = mla::kCpHeaderBytes + size_t(2) * size_t(world) * mla::cp_partial_bytes(max_rows);
   return MLA_FP4_OK;
 }
 
@@ -320,10 +319,11 @@ int mla_fp4_cp_free(void* own_block) {
   return MLA_FP4_OK;
 }
 
-int mla_fp4_cp_exchange_merge(void* const* blocks, int32_t world, int32_t rank, const float* partial, int64_t rows,
-                              void* out, int32_t out_dtype, float* lse, int32_t* status, int32_t wait_polls, void* stream) {
+int mla_fp4_cp_exchange_merge(void* const* blocks, int32_t world, int32_t rank, const float* partial, int64_t rows, int64_t max_rows,
+                              void* out, int32_t out_dtype, float* lse, int32_t* status, int32_t wait_polls, int32_t enable_pdl,
+                              void* stream) {
   if (!blocks || world < 1 || world > MLA_FP4_CP_MAX_RANKS || rank < 0 || rank >= world) return fail(MLA_FP4_ERR_BAD_ARG, "blocks/world/rank out of range");
-  if (rows < 0 || wait_polls < 0) return fail(MLA_FP4_ERR_BAD_ARG, "rows/wait_polls out of range");
+  if (rows < 0 || wait_polls < 0 || rows > max_rows) return fail(MLA_FP4_ERR_BAD_ARG, "rows/max_rows/wait_polls out of range");
   if (rows == 0) return MLA_FP4_OK;
   if (!partial || !out) return fail(MLA_FP4_ERR_BAD_ARG, "null pointer");
   if (out_dtype != MLA_FP4_OUT_BF16 && out_dtype != MLA_FP4_OUT_F32 && out_dtype != MLA_FP4_OUT_E4M3)
@@ -333,11 +333,13 @@ int mla_fp4_cp_exchange_merge(void* const* blocks, int32_t world, int32_t rank, 
   for (int s = 0; s < 8; ++s) p.block[s] = s < world ? blocks[s] : nullptr;
   for (int s = 0; s < world; ++s)
     if (!p.block[s] || reinterpret_cast<uintptr_t>(p.block[s]) % 16) return fail(MLA_FP4_ERR_BAD_ARG, "an exchange block is null or misaligned");
-  p.part = partial; p.rows = rows; p.n = rows * mla::kLatent + ((rows + 3) / 4) * 4;
+  p.part = partial; p.rows = rows; p.max_rows = max_rows;
   p.out = out; p.lse = lse; p.status = status; p.world = world; p.rank = rank; p.out_dtype = out_dtype;
+  p.pdl = enable_pdl ? 1 : 0;
   p.wait_polls = wait_polls > 0 ? uint32_t(wait_polls) : (1u << 22);
-  // every CTA of the grid must be resident at once (CTAs that wait for peers hold their place): rows, capped well below that
-  const int ctas = int(rows < 296 ? rows : 296);
+  // every CTA of the grid must be resident at once (CTAs that wait for peers hold their place): one per row, capped at what
+  // half the SMs of the smallest supported part hold (128 threads and a few bytes of shared memory each)
+  const int ctas = int(rows < 1024 ? rows : 1024);
   cudaError_t e = mla::launch_cp_exchange_merge(p, ctas, reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("exchange launch: ") + cudaGetErrorString(e));
   return MLA_FP4_OK;

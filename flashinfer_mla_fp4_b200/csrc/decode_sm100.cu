@@ -1458,50 +1458,82 @@ bool encode_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims
   return r == CUDA_SUCCESS;
 }
 
+// The four tensor maps of a launch depend only on the query's address and strides, the cache's address and the
+// shapes.  A serving loop calls with the same ones step after step, and encoding four maps cost more host time than
+// the rest of the call: the last set is kept per thread and reused when its key matches.
+struct MapKey {
+  const void* q;
+  const void* kv;
+  int64_t sb, sq, sh, num_pages;
+  int32_t batch, q_len, num_heads, page_size;
+  bool operator==(const MapKey& o) const {
+    return q == o.q && kv == o.kv && sb == o.sb && sq == o.sq && sh == o.sh && num_pages == o.num_pages && batch == o.batch &&
+           q_len == o.q_len && num_heads == o.num_heads && page_size == o.page_size;
+  }
+};
+struct MapSet {
+  MapKey key;
+  bool valid = false;
+  CUtensorMap q_lat, q_rope, rope, lat;
+};
+
 }  // namespace
 
 cudaError_t launch_decode_sm100(const DecodeParams& p, int num_ctas, cudaStream_t stream, const char** err) {
   *err = nullptr;
-  CUtensorMap map_q_lat, map_q_rope, map_rope;
-  {
-    // q viewed as [576, H, q_len, B] bytes
-    uint64_t sq = p.q_len > 1 ? uint64_t(p.q_stride_qpos) : uint64_t(p.q_stride_head) * uint64_t(p.num_heads);
-    uint64_t sb = p.batch > 1 ? uint64_t(p.q_stride_batch) : sq * uint64_t(p.q_len);
-    uint64_t dims[4] = {uint64_t(kQDim), uint64_t(p.num_heads), uint64_t(p.q_len), uint64_t(p.batch)};
-    uint64_t strides[3] = {uint64_t(p.q_stride_head), sq, sb};
-    uint32_t box_lat[4] = {128, uint32_t(kGroupHeads), 1, 1};
-    uint32_t box_rope[4] = {64, uint32_t(kGroupHeads), 1, 1};
-    if (!encode_map(&map_q_lat, p.q, 4, dims, strides, box_lat, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !encode_map(&map_q_rope, p.q, 4, dims, strides, box_rope, CU_TENSOR_MAP_SWIZZLE_64B)) {
-      *err = "cuTensorMapEncodeTiled failed for q (check alignment and strides)";
-      return cudaErrorInvalidValue;
+  static thread_local MapSet cache;
+  const MapKey key{p.q, p.kv_cache, p.q_stride_batch, p.q_stride_qpos, p.q_stride_head, p.num_pages, p.batch, p.q_len, p.num_heads, p.page_size};
+  if (!(cache.valid && cache.key == key)) {
+    cache.valid = false;
+    CUtensorMap& map_q_lat = cache.q_lat;
+    CUtensorMap& map_q_rope = cache.q_rope;
+    CUtensorMap& map_rope = cache.rope;
+    CUtensorMap& map_lat = cache.lat;
+    {
+      // q viewed as [576, H, q_len, B] bytes
+      uint64_t sq = p.q_len > 1 ? uint64_t(p.q_stride_qpos) : uint64_t(p.q_stride_head) * uint64_t(p.num_heads);
+      uint64_t sb = p.batch > 1 ? uint64_t(p.q_stride_batch) : sq * uint64_t(p.q_len);
+      uint64_t dims[4] = {uint64_t(kQDim), uint64_t(p.num_heads), uint64_t(p.q_len), uint64_t(p.batch)};
+      uint64_t strides[3] = {uint64_t(p.q_stride_head), sq, sb};
+      uint32_t box_lat[4] = {128, uint32_t(kGroupHeads), 1, 1};
+      uint32_t box_rope[4] = {64, uint32_t(kGroupHeads), 1, 1};
+      if (!encode_map(&map_q_lat, p.q, 4, dims, strides, box_lat, CU_TENSOR_MAP_SWIZZLE_128B) ||
+          !encode_map(&map_q_rope, p.q, 4, dims, strides, box_rope, CU_TENSOR_MAP_SWIZZLE_64B)) {
+        *err = "cuTensorMapEncodeTiled failed for q (check alignment and strides)";
+        return cudaErrorInvalidValue;
+      }
     }
-  }
-  {
-    uint64_t dims[3] = {uint64_t(kRowBytes), uint64_t(p.page_size), uint64_t(p.num_pages)};
-    uint64_t strides[2] = {uint64_t(kRowBytes), uint64_t(kRowBytes) * uint64_t(p.page_size)};
-    uint32_t box[3] = {64, uint32_t(p.page_size), 1};
-    if (!encode_map(&map_rope, p.kv_cache, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B)) {
-      *err = "cuTensorMapEncodeTiled failed for kv_cache (check alignment)";
-      return cudaErrorInvalidValue;
+    {
+      uint64_t dims[3] = {uint64_t(kRowBytes), uint64_t(p.page_size), uint64_t(p.num_pages)};
+      uint64_t strides[2] = {uint64_t(kRowBytes), uint64_t(kRowBytes) * uint64_t(p.page_size)};
+      uint32_t box[3] = {64, uint32_t(p.page_size), 1};
+      if (!encode_map(&map_rope, p.kv_cache, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B)) {
+        *err = "cuTensorMapEncodeTiled failed for kv_cache (check alignment)";
+        return cudaErrorInvalidValue;
+      }
     }
-  }
-  CUtensorMap map_lat;
-  {
-    // the cache as 4-bit elements: 640 per row (the 512 latent codes, then the RoPE bytes seen as nibbles and
-    // never fetched through this map), page_size rows per page; a box is one 128-dim block of one page
-    EncodeTiledFn fn = get_encode_fn();
-    cuuint64_t gd[3] = {cuuint64_t(2 * kRowBytes), cuuint64_t(p.page_size), cuuint64_t(p.num_pages)};
-    cuuint64_t gs[2] = {cuuint64_t(kRowBytes), cuuint64_t(kRowBytes) * cuuint64_t(p.page_size)};
-    cuuint32_t bx[3] = {128, cuuint32_t(p.page_size), 1};
-    cuuint32_t es[3] = {1, 1, 1};
-    if (!fn || fn(&map_lat, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, const_cast<void*>(p.kv_cache), gd, gs, bx, es,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-      *err = "cuTensorMapEncodeTiled failed for the packed latent (kv_cache must be 32-byte aligned)";
-      return cudaErrorInvalidValue;
+    {
+      // the cache as 4-bit elements: 640 per row (the 512 latent codes, then the RoPE bytes seen as nibbles and
+      // never fetched through this map), page_size rows per page; a box is one 128-dim block of one page
+      EncodeTiledFn fn = get_encode_fn();
+      cuuint64_t gd[3] = {cuuint64_t(2 * kRowBytes), cuuint64_t(p.page_size), cuuint64_t(p.num_pages)};
+      cuuint64_t gs[2] = {cuuint64_t(kRowBytes), cuuint64_t(kRowBytes) * cuuint64_t(p.page_size)};
+      cuuint32_t bx[3] = {128, cuuint32_t(p.page_size), 1};
+      cuuint32_t es[3] = {1, 1, 1};
+      if (!fn || fn(&map_lat, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, const_cast<void*>(p.kv_cache), gd, gs, bx, es,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+        *err = "cuTensorMapEncodeTiled failed for the packed latent (kv_cache must be 32-byte aligned)";
+        return cudaErrorInvalidValue;
+      }
     }
+    cache.key = key;
+    cache.valid = true;
   }
+  const CUtensorMap& map_q_lat = cache.q_lat;
+  const CUtensorMap& map_q_rope = cache.q_rope;
+  const CUtensorMap& map_rope = cache.rope;
+  const CUtensorMap& map_lat = cache.lat;
   {
     static std::atomic<bool> attr_done[64];  // zero-initialised; setting the attribute twice is harmless
     int dev = 0;

@@ -37,20 +37,22 @@ struct CombineParams {
 };
 
 // Exchange block of the context-parallel exchange (cp_exchange.cu): words of its 256-byte header, and where the
-// partial of rank `src` lies in the gather area that follows (two parities, `n` floats per partial).
+// partial of rank `src` lies in the gather area that follows (two parities; per partial max_rows fp16 rows of 512, then
+// max_rows pairs of f32: LSE and row scale).
 constexpr int kCpPushedWord = 8, kCpFinishedWord = 9, kCpStepWord = 10;
 constexpr size_t kCpHeaderBytes = 256;
-__host__ __device__ inline float* cp_gather(void* block, int parity, int world, int src, int64_t n) {
-  return reinterpret_cast<float*>(static_cast<char*>(block) + kCpHeaderBytes) + (int64_t(parity) * world + src) * n;
+__host__ __device__ inline size_t cp_partial_bytes(int64_t max_rows) { return size_t(max_rows) * (512 * 2 + 8); }
+__host__ __device__ inline char* cp_gather(void* block, int parity, int world, int src, int64_t max_rows) {
+  return static_cast<char*>(block) + kCpHeaderBytes + (size_t(parity) * world + src) * cp_partial_bytes(max_rows);
 }
 struct CpExchangeParams {
   void* block[8];     // exchange block of every rank as mapped into this process (own block at [rank])
-  const float* part;  // this rank's packed partial: [rows][512] f32, then [rows] f32 LSEs (n floats in all, n % 4 == 0)
-  int64_t rows, n;
+  const float* part;  // this rank's packed partial: [rows][512] f32, then [rows] f32 LSEs
+  int64_t rows, max_rows;
   void* out;
   float* lse;
   int32_t* status;
-  int32_t world, rank, out_dtype;
+  int32_t world, rank, out_dtype, pdl;
   uint32_t wait_polls;
 };
 cudaError_t launch_cp_exchange_merge(const CpExchangeParams& p, int num_ctas, cudaStream_t stream);

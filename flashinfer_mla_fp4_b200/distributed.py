@@ -165,7 +165,8 @@ class ContextParallelDecoder:
         part_o = self._buf[: rows * LATENT_DIM].view(B, ql, H, LATENT_DIM)
         part_lse = self._buf[rows * LATENT_DIM: rows * LATENT_DIM + rows].view(B, ql, H)
         # 1. local shard -> normalised FP32 partial + base-2 LSE, written straight into the packed buffer [rows*512 | rows]
-        self._local.run(q, kv_cache, block_tables, seq_lens, max(1, max_seq_len), softmax_scale,
+        local_max = max(1, min(int(max_seq_len), block_tables.shape[1] * self._local._page_size))  # the shard's own bound
+        self._local.run(q, kv_cache, block_tables, seq_lens, local_max, softmax_scale,
                         output_scale=output_scale, out=part_o, kv_cache_sf=kv_cache_sf, return_lse=True, lse_out=part_lse)
         if out is None:
             out = torch.empty(B, ql, H, LATENT_DIM, dtype=self._final_dtype, device=q.device)
@@ -180,8 +181,9 @@ class ContextParallelDecoder:
             if self._exchange == "peer":
                 # 2+3. one kernel: push to the peers, flag, wait for their flags, merge
                 _cabi.check(_cabi.lib.mla_fp4_cp_exchange_merge(
-                    self._blocks, self._world, self._rank, C.c_void_p(self._buf.data_ptr()), rows, C.c_void_p(out.data_ptr()), odt,
-                    lse_ptr, C.c_void_p(self._local._status.data_ptr()), self._wait_polls, stream))
+                    self._blocks, self._world, self._rank, C.c_void_p(self._buf.data_ptr()), rows, self._max_rows,
+                    C.c_void_p(out.data_ptr()), odt, lse_ptr, C.c_void_p(self._local._status.data_ptr()), self._wait_polls,
+                    1 if self._local._enable_pdl else 0, stream))
             else:
                 # 2. one all-gather into local memory  3. merge kernel over the gathered partials
                 dist.all_gather_into_tensor(self._gathered, self._buf, group=self._group)

@@ -175,6 +175,9 @@ int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, i
      mla_fp4_cp_exchange_merge: blocks[world] are the blocks as mapped here (own block at [rank]); partial is this
                         rank's packed partial, f32 [rows][512] followed by f32 [rows] LSEs (base 2), 16-byte
                         aligned, as mla_fp4_decode writes them with out_dtype F32 and lse pointing behind the rows;
+                        max_rows is the value the blocks were sized with (the same on every rank); enable_pdl launches
+                        the kernel as a programmatic dependent launch (it starts while the kernel before it on the
+                        stream drains and waits for that kernel's end before it reads anything);
                         out [rows][512] (out_dtype), optional lse [rows]; status as in MlaFp4DecodeArgs (word 0 set
                         to MLA_FP4_ERR_DEVICE_TIMEOUT when a peer's flag does not arrive within wait_polls polls,
                         0 = default); asynchronous on `stream`, CUDA-graph capturable (the step counter lives in
@@ -187,8 +190,8 @@ int mla_fp4_cp_open(const unsigned char* handle, void** block_out);
 int mla_fp4_cp_close(void* peer_block);
 int mla_fp4_cp_free(void* own_block);
 int mla_fp4_cp_exchange_merge(void* const* blocks, int32_t world, int32_t rank, const float* partial, int64_t rows,
-                              void* out, int32_t out_dtype, float* lse, int32_t* status, int32_t wait_polls,
-                              void* stream);
+                              int64_t max_rows, void* out, int32_t out_dtype, float* lse, int32_t* status,
+                              int32_t wait_polls, int32_t enable_pdl, void* stream);
 
 /* Bit-exact E2M1 nibble -> E4M3 byte dequantisation of `n_bytes` packed bytes on the device
    (out holds 2*n_bytes E4M3 bytes, low nibble first).  Pins the table of

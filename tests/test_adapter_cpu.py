@@ -66,6 +66,33 @@ def test_api_log_levels(tmp_path):
     assert "tag = 'stats'" in text and "-> Tensor(shape=(3,)" in text and "max=6" in text
 
 
+def test_api_log_level_10_dumps_tensors(tmp_path):
+    """Level 10: every tensor argument and the result are written to a directory per call, with a description;
+    a tensor above the size limit is described but not written."""
+    import json
+
+    @api_log.api_logged
+    def step(x, pair, scale=1.0):
+        return x * scale, pair[0] + 1
+
+    x = torch.arange(6, dtype=torch.float32).view(2, 3)
+    big = torch.zeros(1 << 20)
+    try:
+        api_log.configure(level=10, dest=str(tmp_path / "log.txt"), dump_dir=str(tmp_path / "dumps"), dump_max_mb=1.0)
+        step(x, (big, 3), scale=0.5)
+    finally:
+        api_log.configure(level=0, dest="stdout", dump_dir="mla_fp4_dumps", dump_max_mb=256)
+    dirs = sorted((tmp_path / "dumps").iterdir())
+    assert len(dirs) == 1 and dirs[0].name.endswith("step")
+    ins = torch.load(dirs[0] / "inputs.pt")
+    outs = torch.load(dirs[0] / "outputs.pt")
+    meta = json.loads((dirs[0] / "meta.json").read_text())
+    assert torch.equal(ins["x"], x) and "pair.0" not in ins            # 4 MiB > the 1 MiB limit
+    assert meta["inputs"]["pair.0"]["skipped"] and meta["inputs"]["x"]["shape"] == [2, 3]
+    assert torch.equal(outs["result.0"], x * 0.5) and meta["scalars"]["scale"] == "0.5"
+    assert "inputs dumped to" in (tmp_path / "log.txt").read_text()
+
+
 def test_public_entry_points_are_logged():
     from flashinfer_mla_fp4_b200 import BatchMLADecodeCuteDSLFP4Wrapper, FP4MLADecodeBackend
     from flashinfer_mla_fp4_b200.kvcache import write_tokens
