@@ -435,6 +435,8 @@ def main() -> None:
     ap.add_argument("--workload", default="northstar", choices=["small", "uniform", "northstar", "varlen", "spec", "dp512", "cache_write"])
     ap.add_argument("--mode", default="auto", choices=["auto", "dp", "cp"], help="N > 1: context parallel (auto, cp) or data parallel")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="context parallel: how the partials travel")
+    ap.add_argument("--algo", default="auto", choices=["auto", "all_gather", "reduce_scatter"],
+                    help="context parallel, peer exchange: every rank merges every row, or every row has an owner rank (auto: from 4 ranks on)")
     ap.add_argument("--impl", default="native", choices=["native", "reference", "reference_gpu"])
     ap.add_argument("--copies", type=int, default=0, help="cache copies rotated for cold L2 (0 = enough to exceed L2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -503,7 +505,7 @@ def main() -> None:
         wrapper.plan(num_heads=case.num_heads, page_size=case.page_size, out_dtype=torch.bfloat16, is_var_seq=True)
         wrapper._kernel = _cabi.KERNEL_TCGEN05 if args.kernel == "fused" else _cabi.KERNEL_TCGEN05_2PASS
         out = torch.empty(case.batch, case.q_len, case.num_heads, 512, dtype=torch.bfloat16, device=device)
-        cp = ContextParallelDecoder(wrapper, dist.group.WORLD, exchange=args.exchange) if (m == "cp" and world > 1) else None
+        cp = ContextParallelDecoder(wrapper, dist.group.WORLD, exchange=args.exchange, algo=args.algo) if (m == "cp" and world > 1) else None
         runner = cp if cp is not None else wrapper
 
         def step(i: int, q=None, bt=None, sl=None):

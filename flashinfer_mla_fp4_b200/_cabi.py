@@ -84,6 +84,7 @@ EXPORTS = (
 )
 CP_MAX_RANKS = 8
 CP_HANDLE_BYTES = 64
+CP_AUTO, CP_ALL_GATHER, CP_REDUCE_SCATTER = 0, 1, 2
 
 
 def _load() -> C.CDLL:
@@ -120,7 +121,7 @@ def _load() -> C.CDLL:
     lib.mla_fp4_cp_free.argtypes = [C.c_void_p]
     lib.mla_fp4_cp_free.restype = C.c_int
     lib.mla_fp4_cp_exchange_merge.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p,
-                                              C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
+                                              C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
     lib.mla_fp4_cp_exchange_merge.restype = C.c_int
     lib.mla_fp4_merge_partials.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
                                            C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]

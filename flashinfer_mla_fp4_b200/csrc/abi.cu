@@ -273,7 +273,7 @@ int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, i
 
 int mla_fp4_cp_exchange_bytes(int32_t world, int64_t max_rows, size_t* bytes_out) {
   if (!bytes_out || world < 1 || world > MLA_FP4_CP_MAX_RANKS || max_rows < 0) return fail(MLA_FP4_ERR_BAD_ARG, "world/max_rows out of range");
-  *bytes_out = mla::kCpHeaderBytes + size_t(2) * size_t(world) * mla::cp_partial_bytes(max_rows);
+  *bytes_out = mla::cp_block_bytes(world, max_rows);
   return MLA_FP4_OK;
 }
 
@@ -321,7 +321,7 @@ int mla_fp4_cp_free(void* own_block) {
 
 int mla_fp4_cp_exchange_merge(void* const* blocks, int32_t world, int32_t rank, const float* partial, int64_t rows, int64_t max_rows,
                               void* out, int32_t out_dtype, float* lse, int32_t* status, int32_t wait_polls, int32_t enable_pdl,
-                              void* stream) {
+                              int32_t algo, void* stream) {
   if (!blocks || world < 1 || world > MLA_FP4_CP_MAX_RANKS || rank < 0 || rank >= world) return fail(MLA_FP4_ERR_BAD_ARG, "blocks/world/rank out of range");
   if (rows < 0 || wait_polls < 0 || rows > max_rows) return fail(MLA_FP4_ERR_BAD_ARG, "rows/max_rows/wait_polls out of range");
   if (rows == 0) return MLA_FP4_OK;
@@ -336,10 +336,13 @@ int mla_fp4_cp_exchange_merge(void* const* blocks, int32_t world, int32_t rank, 
   p.part = partial; p.rows = rows; p.max_rows = max_rows;
   p.out = out; p.lse = lse; p.status = status; p.world = world; p.rank = rank; p.out_dtype = out_dtype;
   p.pdl = enable_pdl ? 1 : 0;
+  if (algo != MLA_FP4_CP_AUTO && algo != MLA_FP4_CP_ALL_GATHER && algo != MLA_FP4_CP_REDUCE_SCATTER)
+    return fail(MLA_FP4_ERR_BAD_ARG, "algo must be MLA_FP4_CP_AUTO, _ALL_GATHER or _REDUCE_SCATTER");
+  p.algo = algo != MLA_FP4_CP_AUTO ? algo : (world >= 4 ? MLA_FP4_CP_REDUCE_SCATTER : MLA_FP4_CP_ALL_GATHER);
   p.wait_polls = wait_polls > 0 ? uint32_t(wait_polls) : (1u << 22);
   // every CTA of the grid must be resident at once (CTAs that wait for peers hold their place): one per row, capped at what
   // half the SMs of the smallest supported part hold (128 threads and a few bytes of shared memory each)
-  const int ctas = int(rows < 1024 ? rows : 1024);
+  const int ctas = int(rows < mla::kCpMaxCtas ? rows : mla::kCpMaxCtas);
   cudaError_t e = mla::launch_cp_exchange_merge(p, ctas, reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("exchange launch: ") + cudaGetErrorString(e));
   return MLA_FP4_OK;

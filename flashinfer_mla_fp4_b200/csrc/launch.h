@@ -36,14 +36,24 @@ struct CombineParams {
   int32_t seq_cap;  // as in DecodeParams
 };
 
-// Exchange block of the context-parallel exchange (cp_exchange.cu): words of its 256-byte header, and where the
-// partial of rank `src` lies in the gather area that follows (two parities; per partial max_rows fp16 rows of 512, then
-// max_rows pairs of f32: LSE and row scale).
-constexpr int kCpPushedWord = 8, kCpFinishedWord = 9, kCpStepWord = 10;
-constexpr size_t kCpHeaderBytes = 256;
-__host__ __device__ inline size_t cp_partial_bytes(int64_t max_rows) { return size_t(max_rows) * (512 * 2 + 8); }
+// Exchange block of the context-parallel exchange (cp_exchange.cu): a step word per CTA, then the gather area: two
+// parities x `world` sources x max_rows rows of 129 tagged 16-byte words (8 bytes of data and two 4-byte tags each),
+// then the result area of the reduce-scatter form: two parities x max_rows rows of 257 tagged words.
+constexpr int kCpMaxCtas = 1024;  // all CTAs of an exchange launch are resident at once
+constexpr size_t kCpHeaderBytes = size_t(kCpMaxCtas) * 4;
+constexpr size_t kCpRowBytes = 129 * 16;
+constexpr size_t kCpResultRowBytes = 257 * 16;
+__host__ __device__ inline int32_t* cp_step_word(void* block, int cta) { return static_cast<int32_t*>(block) + cta; }
+__host__ __device__ inline size_t cp_partial_bytes(int64_t max_rows) { return size_t(max_rows) * kCpRowBytes; }
 __host__ __device__ inline char* cp_gather(void* block, int parity, int world, int src, int64_t max_rows) {
   return static_cast<char*>(block) + kCpHeaderBytes + (size_t(parity) * world + src) * cp_partial_bytes(max_rows);
+}
+__host__ __device__ inline char* cp_result(void* block, int parity, int world, int64_t max_rows) {
+  return static_cast<char*>(block) + kCpHeaderBytes + size_t(2) * world * cp_partial_bytes(max_rows) +
+         size_t(parity) * size_t(max_rows) * kCpResultRowBytes;
+}
+__host__ __device__ inline size_t cp_block_bytes(int world, int64_t max_rows) {
+  return kCpHeaderBytes + size_t(2) * world * cp_partial_bytes(max_rows) + size_t(2) * size_t(max_rows) * kCpResultRowBytes;
 }
 struct CpExchangeParams {
   void* block[8];     // exchange block of every rank as mapped into this process (own block at [rank])
@@ -52,7 +62,7 @@ struct CpExchangeParams {
   void* out;
   float* lse;
   int32_t* status;
-  int32_t world, rank, out_dtype, pdl;
+  int32_t world, rank, out_dtype, pdl, algo;
   uint32_t wait_polls;
 };
 cudaError_t launch_cp_exchange_merge(const CpExchangeParams& p, int num_ctas, cudaStream_t stream);

@@ -82,7 +82,7 @@ class ContextParallelDecoder:
     once, and mapped into every peer through CUDA IPC.  ``exchange="nccl"`` has no such limits.
     """
 
-    def __init__(self, wrapper, group=None, exchange: str = "peer", max_rows: int = 1024) -> None:
+    def __init__(self, wrapper, group=None, exchange: str = "peer", max_rows: int = 1024, algo: str = "auto") -> None:
         from .wrapper import BatchMLADecodeCuteDSLFP4Wrapper
 
         if exchange not in ("peer", "nccl"):
@@ -103,6 +103,9 @@ class ContextParallelDecoder:
         self._blocks = None
         self._own_block = None
         self._wait_polls = 0
+        # form of the peer exchange: "all_gather" (one hop, world-1 partials per rank), "reduce_scatter" (every row merged by
+        # one owner rank, two hops, under two partials per rank) or "auto" (all-gather below four ranks)
+        self._algo = {"auto": _cabi.CP_AUTO, "all_gather": _cabi.CP_ALL_GATHER, "reduce_scatter": _cabi.CP_REDUCE_SCATTER}[algo]
         if exchange == "peer":
             self._setup_peer_blocks()
 
@@ -183,7 +186,7 @@ class ContextParallelDecoder:
                 _cabi.check(_cabi.lib.mla_fp4_cp_exchange_merge(
                     self._blocks, self._world, self._rank, C.c_void_p(self._buf.data_ptr()), rows, self._max_rows,
                     C.c_void_p(out.data_ptr()), odt, lse_ptr, C.c_void_p(self._local._status.data_ptr()), self._wait_polls,
-                    1 if self._local._enable_pdl else 0, stream))
+                    1 if self._local._enable_pdl else 0, self._algo, stream))
             else:
                 # 2. one all-gather into local memory  3. merge kernel over the gathered partials
                 dist.all_gather_into_tensor(self._gathered, self._buf, group=self._group)

@@ -184,6 +184,12 @@ int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, i
                         the block). */
 #define MLA_FP4_CP_MAX_RANKS 8
 #define MLA_FP4_CP_HANDLE_BYTES 64
+/* form of the exchange: every rank receives every peer's rows and merges them all (one NVLink hop, (world-1) partials
+   per rank), or every row is merged by one owner rank which sends the final row to the others (two hops, under two
+   partials per rank whatever the number of ranks).  AUTO: all-gather below four ranks.  All ranks pass the same value. */
+#define MLA_FP4_CP_AUTO 0
+#define MLA_FP4_CP_ALL_GATHER 1
+#define MLA_FP4_CP_REDUCE_SCATTER 2
 int mla_fp4_cp_exchange_bytes(int32_t world, int64_t max_rows, size_t* bytes_out);
 int mla_fp4_cp_alloc(size_t bytes, void** block_out, unsigned char* handle_out);
 int mla_fp4_cp_open(const unsigned char* handle, void** block_out);
@@ -191,7 +197,7 @@ int mla_fp4_cp_close(void* peer_block);
 int mla_fp4_cp_free(void* own_block);
 int mla_fp4_cp_exchange_merge(void* const* blocks, int32_t world, int32_t rank, const float* partial, int64_t rows,
                               int64_t max_rows, void* out, int32_t out_dtype, float* lse, int32_t* status,
-                              int32_t wait_polls, int32_t enable_pdl, void* stream);
+                              int32_t wait_polls, int32_t enable_pdl, int32_t algo, void* stream);
 
 /* Bit-exact E2M1 nibble -> E4M3 byte dequantisation of `n_bytes` packed bytes on the device
    (out holds 2*n_bytes E4M3 bytes, low nibble first).  Pins the table of

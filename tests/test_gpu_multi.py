@@ -40,8 +40,8 @@ def _cp_worker(rank: int, world: int, port: int, tmp: str) -> None:
         w = BatchMLADecodeCuteDSLFP4Wrapper(torch.empty(64 << 20, dtype=torch.int8, device=dev))
         w.plan(num_heads=64, page_size=64)
         outs = {}
-        for exchange in ("peer", "nccl"):
-            cp = ContextParallelDecoder(w, dist.group.WORLD, exchange=exchange)
+        for exchange, algo in (("peer", "all_gather"), ("peer", "reduce_scatter"), ("nccl", "auto")):
+            cp = ContextParallelDecoder(w, dist.group.WORLD, exchange=exchange, algo=algo)
             for name, lens, seed in (("cp_ragged", [5000, 130, 64, 1, 9000, 777], 31), ("cp_b8", [4096 * world] * 8, 32)):
                 case = synth.build_case(name, lens, 64, 64, seed=seed, device=dev)
                 bt, sl = shard_context(case.block_tables, case.seq_lens, case.page_size, rank, world)
@@ -52,10 +52,18 @@ def _cp_worker(rank: int, world: int, port: int, tmp: str) -> None:
                 cp.check_device_status()
                 ref, ref_lse = O.mla_decode(case.q, case.kv_cache, case.kv_cache_sf, case.block_tables, case.seq_lens,
                                             case.softmax_scale)
-                O.assert_parity(out, ref, f"{name} rank {rank} {exchange}")
+                O.assert_parity(out, ref, f"{name} rank {rank} {exchange} {algo}")
                 torch.testing.assert_close(lse.cpu(), ref_lse, atol=2e-3, rtol=1e-4)
-                outs[(exchange, name)] = out.clone()
-            if exchange == "peer":
+                outs[(exchange, algo, name)] = out.clone()
+                if exchange == "peer":  # the other output types travel as one or two words per thread in the reduce-scatter form
+                    for dt in (torch.float32, torch.float8_e4m3fn):
+                        o2 = torch.empty(out.shape, dtype=dt, device=dev)
+                        cp.run(case.q, case.kv_cache, bt, sl, case.max_seq_len, case.softmax_scale, kv_cache_sf=case.kv_cache_sf, out=o2)
+                        torch.cuda.synchronize()
+                        cp.check_device_status()
+                        tol = 2e-2 if dt == torch.float32 else 0.3
+                        assert (o2.float() - out.float()).abs().max().item() <= tol * max(1.0, out.float().abs().max().item()), (name, algo, dt)
+            if exchange == "peer" and algo == "all_gather":
                 # Failure made on the host: rank 1 skips a step, so its flag never reaches rank 0, whose bounded wait
                 # runs out (a small poll budget here); the kernel returns and the status says so.  Nothing faults.
                 dist.barrier()
@@ -69,9 +77,10 @@ def _cp_worker(rank: int, world: int, port: int, tmp: str) -> None:
                     except RuntimeError as e:
                         assert "device error 5" in str(e)
                 dist.barrier()
-                cp.close()
-        for name in ("cp_ragged", "cp_b8"):  # same merge arithmetic either way
-            torch.testing.assert_close(outs[("peer", name)].float(), outs[("nccl", name)].float(), atol=1e-2, rtol=0)
+            cp.close()
+        for name in ("cp_ragged", "cp_b8"):  # same merge arithmetic every way
+            torch.testing.assert_close(outs[("peer", "all_gather", name)].float(), outs[("nccl", "auto", name)].float(), atol=1e-2, rtol=0)
+            assert torch.equal(outs[("peer", "all_gather", name)], outs[("peer", "reduce_scatter", name)]), name
         Path(tmp, f"ok{rank}").write_text("ok")
     finally:
         dist.destroy_process_group()
