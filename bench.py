@@ -299,6 +299,39 @@ def bench_cache_write(device, tokens: int = 1 << 20, reps: int = 10):
                          "peak_kind": kind, "algorithmic_bytes_per_token": bytes_per_token, "kernel": "cache_write_kernel"}}
 
 
+def bench_merge_partials(device, parts: int = 8, rows: int = 512, reps: int = 10):
+    """The merge kernel of the NCCL form of context parallel on `parts` gathered partials of `rows` rows (the north-star
+    shape at 8 ranks), L2 flushed before every launch: microseconds and roofline fraction."""
+    import ctypes as C
+
+    from flashinfer_mla_fp4_b200 import _cabi
+
+    g = torch.Generator(device=device).manual_seed(77)
+    n = rows * 512 + rows
+    gathered = torch.randn(parts * n, generator=g, device=device, dtype=torch.float32)
+    out = torch.empty(rows, 512, dtype=torch.bfloat16, device=device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    times = []
+    for i in range(3 + reps):
+        flush.fill_(i & 0xFF)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        _cabi.check(_cabi.lib.mla_fp4_merge_partials(C.c_void_p(gathered.data_ptr()), C.c_void_p(gathered.data_ptr() + 4 * rows * 512), parts, rows,
+                                                    n, n, C.c_void_p(out.data_ptr()), _cabi.OUT_BF16, None, stream))
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(e0.elapsed_time(e1) * 1e-3)
+    t = statistics.median(times)
+    nbytes = parts * n * 4 + rows * 512 * 2
+    peak, _, kind = peaks()
+    return {"metric": "cp_merge_partials_us", "value": t * 1e6, "unit": "us", "higher_is_better": False, "data": "synthetic", "n_gpus": 1,
+            "dtype": "f32", "config": {"workload": "merge_partials", "parts": parts, "rows": rows, "l2": "flushed before every launch (256 MiB written)"},
+            "roofline": {"bound": "hbm", "achieved": nbytes / t / 1e9, "peak": peak, "unit": "GB/s", "frac": nbytes / t / 1e9 / peak,
+                         "peak_kind": kind, "algorithmic_bytes": nbytes, "kernel": "merge_partials_kernel"}}
+
+
 # ----------------------------------------------------------------------------------------------------------------
 # the reference's kernels on this GPU (not the default arm)
 # ----------------------------------------------------------------------------------------------------------------
@@ -432,7 +465,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="northstar", choices=["small", "uniform", "northstar", "varlen", "spec", "dp512", "cache_write"])
+    ap.add_argument("--workload", default="northstar", choices=["small", "uniform", "northstar", "varlen", "spec", "dp512", "cache_write", "merge_partials"])
     ap.add_argument("--mode", default="auto", choices=["auto", "dp", "cp"], help="N > 1: context parallel (auto, cp) or data parallel")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="context parallel: how the partials travel")
     ap.add_argument("--algo", default="auto", choices=["auto", "all_gather", "reduce_scatter"],
@@ -466,9 +499,13 @@ def main() -> None:
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    if args.workload == "cache_write":
+    if args.workload in ("cache_write", "merge_partials"):  # the two side kernels; --profile-steps N: a short run for an ncu capture
         if rank == 0:
-            print(json.dumps(bench_cache_write(device)), flush=True)
+            if args.workload == "cache_write":
+                res = bench_cache_write(device, 262144, args.profile_steps) if args.profile_steps else bench_cache_write(device)
+            else:
+                res = bench_merge_partials(device, reps=args.profile_steps or 10)
+            print(json.dumps(res), flush=True)
         return
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
