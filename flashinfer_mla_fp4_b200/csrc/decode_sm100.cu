@@ -1302,24 +1302,12 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   c.misc = reinterpret_cast<Misc*>(c.smem_ptr + kOffMisc);
   c.status = p.status;
   c.polls = p.wait_polls;
-  // The generation of this step: one more than that of the last completed step.  No CTA of this step
-  // can have advanced it yet (that takes every CTA of the grid to have finished).
-  c.gen = p.fused_merge ? ld_acquire(ws_generation(p.workspace)) + 1 : 0;
-#ifdef MLA_FP4_TRACE
-  c.trace_cta = (p.status && p.status[7] >= 0 && p.status[7] < int(gridDim.x) && p.status[7] != 0) ? p.status[7] : int(gridDim.x) - 1;
-#endif
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
 
+  // What needs nothing an earlier kernel wrote comes first: with a programmatic dependent launch this part runs
+  // while the kernel before this one on the stream is still draining.
   if (warp == 0) {
-    Walker w = make_walker(p.seq_lens, p.batch, p.seq_cap, p.groups, blockIdx.x, gridDim.x);
-    if (tid == 0) {
-      c.misc->walker = w;
-      c.misc->abort = 0;
-      c.misc->n_merge = 0;
-      stage_segments(c);
-    }
-    __syncwarp();
     ptx::tmem_alloc(c.smem + kOffMisc + offsetof(Misc, tmem_base), 512);
     ptx::tmem_relinquish();
   } else if (warp == kWarpTMA && (tid & 31) == 0) {
@@ -1346,6 +1334,23 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
     ptx::prefetch_tensormap(&map_q_rope);
     ptx::prefetch_tensormap(&map_rope);
     ptx::prefetch_tensormap(&map_lat);
+  }
+  // From here on the kernel reads what earlier kernels wrote (sequence lengths, q, the cache, the workspace).
+  if (p.pdl_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
+  // The generation of this step: one more than that of the last completed step.  No CTA of this step
+  // can have advanced it yet (that takes every CTA of the grid to have finished).
+  c.gen = p.fused_merge ? ld_acquire(ws_generation(p.workspace)) + 1 : 0;
+#ifdef MLA_FP4_TRACE
+  c.trace_cta = (p.status && p.status[7] >= 0 && p.status[7] < int(gridDim.x) && p.status[7] != 0) ? p.status[7] : int(gridDim.x) - 1;
+#endif
+  if (warp == 0) {
+    Walker w = make_walker(p.seq_lens, p.batch, p.seq_cap, p.groups, blockIdx.x, gridDim.x);
+    if (tid == 0) {
+      c.misc->walker = w;
+      c.misc->abort = 0;
+      c.misc->n_merge = 0;
+      stage_segments(c);
+    }
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -1550,12 +1555,48 @@ cudaError_t launch_decode_sm100(const DecodeParams& p, int num_ctas, cudaStream_
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = kSmemAlloc;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeCooperative;  // the CTAs wait for one another in the tail merge
-  attr[0].val.cooperative = 1;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (p.fused_merge) {
+    attr[n_attr].id = cudaLaunchAttributeCooperative;  // the CTAs wait for one another in the tail merge
+    attr[n_attr].val.cooperative = 1;
+    ++n_attr;
+  }
+  // Programmatic dependent launch of this kernel itself: its CTAs are placed and run their prologue while the kernel
+  // before it on the stream drains, then wait for that kernel's completion.  Whether the driver takes the attribute
+  // together with the cooperative one is found out once per process, on a launch outside stream capture (a launch that
+  // fails inside a capture would invalidate it); until then, and if it does not, the kernel is launched without it.
+  static std::atomic<int> chain_state{0};  // 0 unknown, 1 accepted, 2 refused
+  DecodeParams pp = p;
+  pp.pdl_wait = 0;
+#ifndef MLA_FP4_NO_PDL_CHAIN
+  if (p.pdl) {
+    int state = chain_state.load(std::memory_order_acquire);
+    if (state == 0) {
+      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+      if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) state = 2;  // not now
+    }
+    if (state != 2) {
+      attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = n_attr + 1;
+      pp.pdl_wait = 1;
+      cudaError_t e = cudaLaunchKernelEx(&cfg, mla_fp4_decode_sm100_kernel, pp, map_q_lat, map_q_rope, map_rope, map_lat);
+      if (e == cudaSuccess) {
+        chain_state.store(1, std::memory_order_release);
+        return e;
+      }
+      if (state == 1) return e;
+      (void)cudaGetLastError();  // refused: remember, and launch without the attribute
+      chain_state.store(2, std::memory_order_release);
+      pp.pdl_wait = 0;
+    }
+  }
+#endif
   cfg.attrs = attr;
-  cfg.numAttrs = p.fused_merge ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, mla_fp4_decode_sm100_kernel, p, map_q_lat, map_q_rope, map_rope, map_lat);
+  cfg.numAttrs = n_attr;
+  return cudaLaunchKernelEx(&cfg, mla_fp4_decode_sm100_kernel, pp, map_q_lat, map_q_rope, map_rope, map_lat);
 }
 
 }  // namespace mla

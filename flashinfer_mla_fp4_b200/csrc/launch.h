@@ -21,7 +21,8 @@ struct DecodeParams {
   int64_t num_pages;
   float softmax_scale, output_scale;
   int32_t out_dtype;
-  int32_t pdl;
+  int32_t pdl;          // let a dependent kernel start early (griddepcontrol.launch_dependents)
+  int32_t pdl_wait;     // set by the launcher: this kernel itself is a dependent launch and waits for the one before it
   int32_t fused_merge;  // the decode kernel merges the split-KV partials itself (cooperative launch)
   int32_t seq_cap;      // most tokens a request may have: block-table width * page_size (INT_MAX when not given)
   uint32_t wait_polls;  // poll budget of every bounded wait
