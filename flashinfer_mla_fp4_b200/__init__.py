@@ -15,6 +15,9 @@ _EXPORTS = {
     "FP4MLADecodeBackend": ".adapter",
     "FP4MLAPagedCache": ".adapter",
     "decode_slot_mapping": ".adapter",
+    "StandardAttention": ".variants",
+    "AttentionWithSink": ".variants",
+    "SoftCappingAttention": ".variants",
 }
 
 __all__ = list(_EXPORTS)

@@ -11,7 +11,7 @@ from pathlib import Path
 
 # MLA_FP4_B200_LIB overrides the library location (for instance a debug build)
 LIB_PATH = Path(os.environ.get("MLA_FP4_B200_LIB") or (Path(__file__).resolve().parent / "libmla_fp4_b200.so"))
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 OK = 0
 ERR_BAD_ARG = 1
@@ -60,6 +60,7 @@ class DecodeArgs(C.Structure):
         ("stream", C.c_void_p),
         ("max_pages_per_request", C.c_int32),
         ("wait_polls", C.c_int32),
+        ("logits_soft_cap", C.c_float), ("sink", C.c_void_p),
     ]
 
 

@@ -156,6 +156,9 @@ int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
     p.seq_cap = cap < INT_MAX ? int32_t(cap) : INT_MAX;
   }
   p.wait_polls = a->wait_polls > 0 ? uint32_t(a->wait_polls) : (1u << 22);
+  if (!(a->logits_soft_cap >= 0.f)) return fail(MLA_FP4_ERR_BAD_ARG, "logits_soft_cap must be >= 0 (0 = off)");
+  p.soft_cap = a->logits_soft_cap;
+  p.sink = a->sink;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(a->stream);
 
   cudaError_t e = cudaSuccess;

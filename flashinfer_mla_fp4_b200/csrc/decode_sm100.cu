@@ -615,6 +615,7 @@ struct SoftmaxTile {
   uint32_t psw;            // swizzle term of the row
   uint32_t half;           // which 32 heads this warp owns
   uint64_t sc2, cs2;       // (scale_t, scale_t), (c, c)
+  uint64_t cap2, rcap2;    // soft-cap variant: (cap, cap), (1/cap, 1/cap)
   bool valid;
 };
 // A thread's P' of one tile: 32 heads x (hi, lo) as bytes, kept in registers until the P buffer is free.
@@ -647,7 +648,13 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
-template <bool kSecond>
+__device__ __forceinline__ float tanh_approx(float x) {
+  float r;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+// kSoftCap: the raw score x = q.k passes through cap * tanh(x / cap) first (compiled only into the soft-cap kernel).
+template <bool kSecond, bool kSoftCap>
 __device__ __forceinline__ float softmax_pass(const SoftmaxTile& t, uint64_t (&l2)[kHalfHeads / 2], PRegs& pr) {
   float mx = -INFINITY;
 #pragma unroll
@@ -669,7 +676,12 @@ __device__ __forceinline__ float softmax_pass(const SoftmaxTile& t, uint64_t (&l
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int i = 4 * q + 2 * h;
-        const uint64_t x2 = fma2(pack2u(a[i], a[i + 1]), t.sc2, pack2u(b[i], b[i + 1]));
+        uint64_t x2 = fma2(pack2u(a[i], a[i + 1]), t.sc2, pack2u(b[i], b[i + 1]));
+        if (kSoftCap) {
+          float x0, x1;
+          unpack2(mul2(x2, t.rcap2), x0, x1);
+          x2 = mul2(pack2(tanh_approx(x0), tanh_approx(x1)), t.cap2);
+        }
         const uint64_t arg2 = fma2(x2, t.cs2, h ? nm1 : nm0);
         float a0, a1;
         unpack2(arg2, a0, a1);
@@ -714,7 +726,8 @@ __device__ __forceinline__ void store_p(const SoftmaxTile& t, const PRegs& pr) {
 // Refresh the per-head reference: column max of y = x*c + log2(scale_t) over the tile's tokens,
 // m = max(m_old, colmax - shift); f = 2^(m_old - m) (0 when there was no reference yet).
 __device__ __noinline__ void refresh_reference(const Ctx& c, uint32_t t_lat, uint32_t t_rope, float sc, bool valid,
-                                               float cscale, float lg, bool have_m, int tid) {
+                                               float cscale, float lg, bool have_m, int tid, float cap) {
+  const float rcap = cap > 0.f ? 1.f / cap : 0.f;
   const int warp = tid >> 5, lane = tid & 31;
   const int quarter = warp & 3, half = warp >> 2;  // t_lat / t_rope already point at this warp's 32 columns
   const uint32_t wred = c.smem + kOffWmax;
@@ -727,7 +740,9 @@ __device__ __noinline__ void refresh_reference(const Ctx& c, uint32_t t_lat, uin
     float mine = -INFINITY;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const float y = fmaf(fmaf(__uint_as_float(a[i]), sc, __uint_as_float(b[i])), cscale, lg);
+      float x = fmaf(__uint_as_float(a[i]), sc, __uint_as_float(b[i]));
+      if (cap > 0.f) x = cap * tanh_approx(x * rcap);
+      const float y = fmaf(x, cscale, lg);
       const float r = ptx::redux_max_f32(valid ? y : -INFINITY);
       if ((lane & 15) == i) mine = r;
     }
@@ -827,6 +842,7 @@ __device__ __noinline__ void write_output(const DecodeParams& p, const Ctx& c, u
   }
 }
 
+template <bool kSoftCap>
 __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c, uint32_t tmem, int tid, RoleState& st) {
   const int nseg = c.misc->nseg;
   const Segment* sg = segs(c);
@@ -839,6 +855,9 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
   SoftmaxTile t;
   t.negm = c.smem + kOffM + 4 * kHalfHeads * half;
   t.cs2 = pack2(cscale, cscale);
+  const float cap = kSoftCap ? p.soft_cap : 0.f;
+  t.cap2 = pack2(cap, cap);
+  t.rcap2 = pack2(kSoftCap ? 1.f / cap : 0.f, kSoftCap ? 1.f / cap : 0.f);
   t.psw = (uint32_t(row) >> 1) & 3u;
   t.half = uint32_t(half);
   int pending0 = 0, pending1 = 0, n_pending = 0;  // slots of the partials written in this call, published together at its end
@@ -874,19 +893,19 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       ptx::tc_fence_after();
 
       // first tile of a segment: set the reference before anything is exponentiated
-      if (first) refresh_reference(c, t.t_lat, t.t_rope, sc, t.valid, cscale, lg, false, tid);
+      if (first) refresh_reference(c, t.t_lat, t.t_rope, sc, t.valid, cscale, lg, false, tid, cap);
       if (tid == 0) MLA_TRACE(0, it, 2);
 
       // Speculative pass with the current reference.  It stands unless some score beat the
       // reference by more than the lazy threshold (P' would leave the E4M3 range).
       PRegs pr;
-      const float mx = softmax_pass<false>(t, l2, pr);
+      const float mx = softmax_pass<false, kSoftCap>(t, l2, pr);
       const bool need = t.valid && (mx + lg > kPShift + kLazyThreshold);
       const bool refresh = ptx::bar_or(1, kSoftmaxThreads, need);
       if (refresh) {
         // Refresh the reference.  (l + e_old) * f equals l * f + e_new, so the row sums only need
         // the factor; O^T is rescaled in TMEM; P' is recomputed with the new reference.
-        refresh_reference(c, t.t_lat, t.t_rope, sc, t.valid, cscale, lg, true, tid);
+        refresh_reference(c, t.t_lat, t.t_rope, sc, t.valid, cscale, lg, true, tid, cap);
 #pragma unroll
         for (int q = 0; q < kHalfHeads / 4; ++q) {
           uint64_t f0, f1;
@@ -894,7 +913,7 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
           l2[2 * q] = mul2(l2[2 * q], f0);
           l2[2 * q + 1] = mul2(l2[2 * q + 1], f1);
         }
-        (void)softmax_pass<true>(t, l2, pr);
+        (void)softmax_pass<true, kSoftCap>(t, l2, pr);
       }
       if (tid == 0) MLA_TRACE(0, it, 3);
       ptx::tc_fence_before();  // orders the S reads before the arrive
@@ -925,8 +944,21 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       if (tid < kGroupHeads) {
         const float L = (lds_f32(wred + 4 * tid) + lds_f32(wred + 4 * (kGroupHeads + tid))) +
                         (lds_f32(wred + 4 * (2 * kGroupHeads + tid)) + lds_f32(wred + 4 * (3 * kGroupHeads + tid)));
-        sts_f32(c.smem + kOffLinv + 4 * tid, p.output_scale / L);
-        sts_f32(c.smem + kOffLse + 4 * tid, __log2f(L) - lds_f32(c.smem + kOffM + 4 * tid));
+        float m = -lds_f32(c.smem + kOffM + 4 * tid);
+        float Ls = L, fo = 1.f;
+        if (p.sink && g.tile_begin == 0) {  // the sink: a virtual token with a zero value row, counted with the first tile of a request
+          int qpos, head0;
+          group_coords(g.g, p.num_heads, qpos, head0);
+          if (head0 + tid < p.num_heads) {
+            const float sk = __ldg(p.sink + head0 + tid) * kLog2e;
+            const float mm = fmaxf(m, sk);
+            fo = ptx::ex2(m - mm);  // the reference may lie far below the sink: fold it into the output factor, not into L
+            Ls = L * fo + ptx::ex2(sk - mm);
+            m = mm;
+          }
+        }
+        sts_f32(c.smem + kOffLinv + 4 * tid, p.output_scale * fo / Ls);
+        sts_f32(c.smem + kOffLse + 4 * tid, __log2f(Ls) + m);
       }
       ptx::bar_sync(1, kSoftmaxThreads);
       // wait for the PV of the last tile
@@ -1287,6 +1319,7 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
 // ------------------------------------------------------------------------------------------
 // kernel
 // ------------------------------------------------------------------------------------------
+template <bool kSoftCap>
 __global__ void __launch_bounds__(kThreads, 1)
 mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map_q_lat,
                             const __grid_constant__ CUtensorMap map_q_rope, const __grid_constant__ CUtensorMap map_rope,
@@ -1380,7 +1413,7 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   // Rounds: almost always exactly one; more only when a CTA's range spans more than kMaxSeg requests.
   for (;;) {
     if (warp >= kWarpSoftmax0) {
-      softmax_role(p, c, tmem, tid - 32 * kWarpSoftmax0, st);
+      softmax_role<kSoftCap>(p, c, tmem, tid - 32 * kWarpSoftmax0, st);
     } else if (warp == kWarpQK) {
       qk_role(c, tmem, st);
     } else if (warp == kWarpPV || warp == kWarpPV2) {
@@ -1545,11 +1578,15 @@ cudaError_t launch_decode_sm100(const DecodeParams& p, int num_ctas, cudaStream_
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64 || !attr_done[dev].load(std::memory_order_acquire)) {
-      e = cudaFuncSetAttribute(mla_fp4_decode_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemAlloc));
+      e = cudaFuncSetAttribute(mla_fp4_decode_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemAlloc));
+      if (e != cudaSuccess) return e;
+      e = cudaFuncSetAttribute(mla_fp4_decode_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemAlloc));
       if (e != cudaSuccess) return e;
       if (dev >= 0 && dev < 64) attr_done[dev].store(true, std::memory_order_release);
     }
   }
+  // the attention variant with a score transform is a kernel of its own: the standard one carries none of its instructions
+  auto* kernel = p.soft_cap > 0.f ? mla_fp4_decode_sm100_kernel<true> : mla_fp4_decode_sm100_kernel<false>;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(num_ctas);
   cfg.blockDim = dim3(kThreads);
@@ -1582,7 +1619,7 @@ cudaError_t launch_decode_sm100(const DecodeParams& p, int num_ctas, cudaStream_
       cfg.attrs = attr;
       cfg.numAttrs = n_attr + 1;
       pp.pdl_wait = 1;
-      cudaError_t e = cudaLaunchKernelEx(&cfg, mla_fp4_decode_sm100_kernel, pp, map_q_lat, map_q_rope, map_rope, map_lat);
+      cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, pp, map_q_lat, map_q_rope, map_rope, map_lat);
       if (e == cudaSuccess) {
         chain_state.store(1, std::memory_order_release);
         return e;
@@ -1596,7 +1633,7 @@ cudaError_t launch_decode_sm100(const DecodeParams& p, int num_ctas, cudaStream_
 #endif
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
-  return cudaLaunchKernelEx(&cfg, mla_fp4_decode_sm100_kernel, pp, map_q_lat, map_q_rope, map_rope, map_lat);
+  return cudaLaunchKernelEx(&cfg, kernel, pp, map_q_lat, map_q_rope, map_rope, map_lat);
 }
 
 }  // namespace mla

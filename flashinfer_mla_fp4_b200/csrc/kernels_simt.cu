@@ -156,7 +156,8 @@ __global__ void __launch_bounds__(256) fp32_check_kernel(DecodeParams p) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           int t = (tid & 3) + 4 * j;
-          p_s[h * kChkTok + t] = (t < nt) ? acc[j] * c : -INFINITY;
+          const float raw = p.soft_cap > 0.f ? p.soft_cap * tanhf(acc[j] / p.soft_cap) : acc[j];
+          p_s[h * kChkTok + t] = (t < nt) ? raw * c : -INFINITY;
         }
       }
       __syncthreads();
@@ -188,6 +189,23 @@ __global__ void __launch_bounds__(256) fp32_check_kernel(DecodeParams p) {
       }
     }
     __syncthreads();
+    if (p.sink && s.tile_begin == 0) {  // the sink: a virtual token with a zero value row, counted with the first tile of the request
+      if (tid < kGroupHeads) {
+        float f = 1.f;
+        if (tid < heads_here) {
+          const float sk = p.sink[head0 + tid] * kLog2e;
+          const float m = fmaxf(m_s[tid], sk);
+          f = (m_s[tid] == -INFINITY) ? 0.f : exp2f(m_s[tid] - m);
+          l_s[tid] = l_s[tid] * f + exp2f(sk - m);
+          m_s[tid] = m;
+        }
+        f_s[tid] = f;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int h = 0; h < kGroupHeads; ++h) { o0[h] *= f_s[h]; o1[h] *= f_s[h]; }
+      __syncthreads();
+    }
     // epilogue
     const size_t row0 = (size_t(s.b) * p.q_len + qpos) * p.num_heads + head0;
     if (s.slot < 0) {

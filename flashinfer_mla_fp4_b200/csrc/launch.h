@@ -26,6 +26,8 @@ struct DecodeParams {
   int32_t fused_merge;  // the decode kernel merges the split-KV partials itself (cooperative launch)
   int32_t seq_cap;      // most tokens a request may have: block-table width * page_size (INT_MAX when not given)
   uint32_t wait_polls;  // poll budget of every bounded wait
+  float soft_cap;       // > 0: raw scores pass through cap * tanh(s / cap)
+  const float* sink;    // per-head sink logits or null
 };
 
 struct CombineParams {

@@ -96,6 +96,10 @@ class ContextParallelDecoder:
         self._local = BatchMLADecodeCuteDSLFP4Wrapper(wrapper._workspace_buffer)
         self._local.plan(num_heads=wrapper._num_heads, page_size=wrapper._page_size, out_dtype=torch.float32,
                          is_var_seq=wrapper._is_var_seq, enable_pdl=wrapper._enable_pdl)
+        # the attention variant of the caller's plan; a sink joins the denominator once per request: on rank 0 only
+        self._local._soft_cap = wrapper._soft_cap
+        self._local._sink = wrapper._sink if self._rank == 0 else None
+        self._local._num_ctas = wrapper._num_ctas
         self._buf: Optional[torch.Tensor] = None
         self._gathered: Optional[torch.Tensor] = None
         self._exchange = exchange

@@ -23,6 +23,7 @@ import torch
 from . import _cabi
 from .api_log import api_logged
 from .kvcache import LATENT_DIM, ROPE_DIM, ROW_BYTES
+from .variants import resolve as resolve_variant
 
 _OUT_DTYPES = {torch.bfloat16: _cabi.OUT_BF16, torch.float32: _cabi.OUT_F32, torch.float8_e4m3fn: _cabi.OUT_E4M3}
 
@@ -68,8 +69,15 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         enable_pdl: Optional[bool] = None,
         variant=None,
         kv_dtype: torch.dtype = torch.uint8,
+        max_ctas: Optional[int] = None,
     ) -> None:
-        """Validate the configuration and bind it (nothing is compiled: the kernels are built ahead of time)."""
+        """Validate the configuration and bind it (nothing is compiled: the kernels are built ahead of time).
+
+        ``variant``: None / ``StandardAttention``, ``AttentionWithSink`` or ``SoftCappingAttention`` (``variants.py``).
+        ``max_ctas`` (not in the reference, whose per-request split counts ``block_split_kvs`` are plumbed but switched
+        off, wrappers/batch_mla_fp4.py:231, :453): caps the persistent grid, and with it into how many partials the
+        requests are split (the tiles of all requests are dealt to the CTAs in order); None = one CTA per SM.
+        """
         if kv_lora_rank != 512:
             raise ValueError(f"Per-token-scaled FP4 MLA requires kv_lora_rank=512, got {kv_lora_rank}")
         if qk_rope_head_dim != 64:
@@ -78,18 +86,14 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
             raise ValueError("Per-token-scaled FP4 MLA requires an E4M3 query")
         if kv_dtype != torch.uint8:
             raise ValueError("Per-token-scaled FP4 MLA requires a byte-packed uint8 KV cache")
-        if variant is not None and type(variant).__name__ != "StandardAttention":
-            raise ValueError(
-                "only the standard attention variant is supported (score_mod / update_statistics / "
-                "transform_output hooks are JIT-traced callbacks in the reference and have no ahead-of-time form)"
-            )
+        if not (1 <= num_heads <= 128):
+            raise ValueError(f"Unsupported num_heads={num_heads}: must be in [1, 128]")
+        soft_cap, sink = resolve_variant(variant, num_heads, self._device)
         o_dtype = torch.bfloat16 if out_dtype is None else out_dtype
         # the reference accepts page sizes that divide 128 except 1, at most 128 heads, bf16/e4m3 output
         # (flashinfer cute_dsl/attention/mla_config.py:186-229); this build: pages of 8..128 tokens, bf16/f32 output
         if page_size not in (8, 16, 32, 64, 128):
             raise ValueError(f"Unsupported page_size={page_size}: must be one of 8, 16, 32, 64, 128")
-        if not (1 <= num_heads <= 128):
-            raise ValueError(f"Unsupported num_heads={num_heads}: must be in [1, 128]")
         if o_dtype not in _OUT_DTYPES:
             raise ValueError(f"Unsupported out_dtype={o_dtype}: must be torch.bfloat16, torch.float8_e4m3fn or torch.float32")
         _require_sm100(self._device)
@@ -103,6 +107,12 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         self._is_var_seq = is_var_seq
         self._enable_pdl = True if enable_pdl is None else bool(enable_pdl)
         self._num_ctas = torch.cuda.get_device_properties(self._device).multi_processor_count
+        if max_ctas is not None:
+            if max_ctas < 1:
+                raise ValueError(f"max_ctas must be at least 1, got {max_ctas}")
+            self._num_ctas = min(self._num_ctas, int(max_ctas))
+        self._soft_cap = soft_cap
+        self._sink = sink
         if self._status is None:
             self._status = torch.zeros(8, dtype=torch.int32, device=self._device)
         self._init_workspace()
@@ -243,6 +253,8 @@ class BatchMLADecodeCuteDSLFP4Wrapper:
         a.enable_pdl = 1 if self._enable_pdl else 0
         a.phase_mask = self._phase_mask
         a.max_pages_per_request = block_tables.shape[1]
+        a.logits_soft_cap = self._soft_cap
+        a.sink = self._sink.data_ptr() if self._sink is not None else None
         a.wait_polls = self._wait_polls
         with torch.cuda.device(q.device):
             a.stream = torch.cuda.current_stream(q.device).cuda_stream

@@ -20,7 +20,7 @@
 extern "C" {
 #endif
 
-#define MLA_FP4_ABI_VERSION 4
+#define MLA_FP4_ABI_VERSION 5
 
 /* status codes */
 #define MLA_FP4_OK 0
@@ -112,6 +112,15 @@ typedef struct MlaFp4DecodeArgs {
   /* Poll budget of every bounded device-side wait (0 = the default, 2^22).  When a wait runs
      out the kernel records MLA_FP4_ERR_DEVICE_TIMEOUT in the status words and returns. */
   int32_t wait_polls;
+  /* Attention variants, compiled into the kernels (the reference passes an AttentionVariant object whose hooks are
+     traced into its kernel, wrappers/batch_mla_fp4.py:237-253; the two hooks in use there are restated as data):
+     logits_soft_cap > 0: every raw score s = q.k becomes cap * tanh(s / cap) before softmax_scale is applied (the
+       score_mod hook of a soft-capping variant); 0 = off.
+     sink: f32 [num_heads] on the device or NULL: one virtual token per head with logit sink[h] (natural-log units,
+       compared with the scaled scores) and a zero value row: it only adds exp(sink[h]) to the softmax denominator
+       (the update_statistics hook of the sink variant, applied with the first tile of a request). */
+  float logits_soft_cap;
+  const float* sink;
 } MlaFp4DecodeArgs;
 
 /* ABI version of the loaded library (== MLA_FP4_ABI_VERSION of the header it was built from). */

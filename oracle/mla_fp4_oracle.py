@@ -179,8 +179,17 @@ def mla_decode(
     seq_lens: torch.Tensor,
     softmax_scale: float,
     output_scale: float = 1.0,
+    logits_soft_cap: float = 0.0,
+    sink: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Dense FP32 MLA decode over the dequantised cache.
+
+    Attention variants (the hooks of flashinfer's ``cute_dsl/attention/fusion/variant.py`` that the reference
+    wrapper forwards, wrappers/batch_mla_fp4.py:237-253, restated as plain arithmetic):
+    ``logits_soft_cap`` > 0 turns every raw score s = q.k into cap * tanh(s / cap) before ``softmax_scale``
+    (the soft-capping ``score_mod``); ``sink`` f32 [H] adds one virtual token per head with logit sink[h]
+    (compared with the scaled scores) and a zero value row, i.e. exp(sink[h]) in the denominator only
+    (``AttentionWithSink.update_statistics``).
 
     q: E4M3 (or float) [B, q_len, H, 576]; kv_cache uint8 [P, ps, 320] (or 4-D with a
     singleton dim 1); kv_cache_sf f32 [P, ps, 1]; block_tables int [B, max_pages];
@@ -214,10 +223,17 @@ def mla_decode(
         rope = rope.reshape(-1, ROPE_DIM)[:n]
         qb = qf[b].reshape(q_len * H, D)
         score = qb[:, :LATENT_DIM] @ lat.T + qb[:, LATENT_DIM:] @ rope.T
+        if logits_soft_cap > 0:
+            score = float(logits_soft_cap) * torch.tanh(score / float(logits_soft_cap))
         x = score * float(softmax_scale)
         m = x.max(dim=-1, keepdim=True).values
+        if sink is not None:
+            sk = sink.detach().cpu().float().reshape(1, H).expand(q_len, H).reshape(q_len * H, 1)
+            m = torch.maximum(m, sk)
         p = torch.exp(x - m)
         l = p.sum(dim=-1, keepdim=True)
+        if sink is not None:
+            l = l + torch.exp(sk - m)
         o = (p @ lat) / l * float(output_scale)
         out[b] = o.reshape(q_len, H, LATENT_DIM)
         lse2[b] = ((m + torch.log(l)) * LOG2_E).reshape(q_len, H)

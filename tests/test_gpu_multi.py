@@ -81,6 +81,22 @@ def _cp_worker(rank: int, world: int, port: int, tmp: str) -> None:
         for name in ("cp_ragged", "cp_b8"):  # same merge arithmetic every way
             torch.testing.assert_close(outs[("peer", "all_gather", name)].float(), outs[("nccl", "auto", name)].float(), atol=1e-2, rtol=0)
             assert torch.equal(outs[("peer", "all_gather", name)], outs[("peer", "reduce_scatter", name)]), name
+        # an attention sink joins the denominator once per request, whichever rank holds the request's first tokens
+        from flashinfer_mla_fp4_b200 import AttentionWithSink
+
+        sink = torch.linspace(-3.0, 8.0, 64, device=dev)
+        w2 = BatchMLADecodeCuteDSLFP4Wrapper(torch.empty(64 << 20, dtype=torch.int8, device=dev))
+        w2.plan(num_heads=64, page_size=64, variant=AttentionWithSink(sink))
+        cp = ContextParallelDecoder(w2, dist.group.WORLD, exchange="peer")
+        case = synth.build_case("cp_sink", [5000, 130, 64, 1, 9000, 777], 64, 64, seed=33, device=dev)
+        bt, sl = shard_context(case.block_tables, case.seq_lens, case.page_size, rank, world)
+        out, lse = cp.run(case.q, case.kv_cache, bt, sl, case.max_seq_len, case.softmax_scale, kv_cache_sf=case.kv_cache_sf, return_lse=True)
+        torch.cuda.synchronize()
+        cp.check_device_status()
+        ref, ref_lse = O.mla_decode(case.q, case.kv_cache, case.kv_cache_sf, case.block_tables, case.seq_lens, case.softmax_scale, sink=sink)
+        O.assert_parity(out, ref, f"cp_sink rank {rank}")
+        torch.testing.assert_close(lse.cpu(), ref_lse, atol=2e-3, rtol=1e-4)
+        cp.close()
         Path(tmp, f"ok{rank}").write_text("ok")
     finally:
         dist.destroy_process_group()

@@ -24,12 +24,13 @@ def _dev():
 
 
 def run_case(case, kernel="tcgen05", out_dtype=torch.bfloat16, return_lse=True, output_scale=1.0, workspace=None,
-             four_d=False, out=None):
+             four_d=False, out=None, variant=None, max_ctas=None):
     from flashinfer_mla_fp4_b200 import BatchMLADecodeCuteDSLFP4Wrapper
 
     ws = workspace if workspace is not None else torch.empty(64 << 20, dtype=torch.int8, device=case.q.device)
     w = BatchMLADecodeCuteDSLFP4Wrapper(ws)
-    w.plan(num_heads=case.num_heads, page_size=case.page_size, out_dtype=out_dtype, is_var_seq=True)
+    w.plan(num_heads=case.num_heads, page_size=case.page_size, out_dtype=out_dtype, is_var_seq=True, variant=variant,
+           max_ctas=max_ctas)
     w._kernel = KERNELS[kernel]
     cache, sf = (case.kv_cache.unsqueeze(1), case.kv_cache_sf.unsqueeze(1)) if four_d else (case.kv_cache, case.kv_cache_sf)
     res = w.run(case.q, cache, case.block_tables, case.seq_lens, case.max_seq_len, case.softmax_scale,
@@ -41,8 +42,11 @@ def run_case(case, kernel="tcgen05", out_dtype=torch.bfloat16, return_lse=True, 
 
 def check_case(case, kernel, **kw):
     out, lse = run_case(case, kernel, **kw)
+    variant = kw.get("variant")
     ref, ref_lse = O.mla_decode(case.q, case.kv_cache, case.kv_cache_sf, case.block_tables, case.seq_lens,
-                                case.softmax_scale, kw.get("output_scale", 1.0))
+                                case.softmax_scale, kw.get("output_scale", 1.0),
+                                logits_soft_cap=getattr(variant, "cap", 0.0),
+                                sink=getattr(variant, "extra_params", None))
     m = O.assert_parity(out, ref, f"{case.name}/{kernel}")
     live = torch.isfinite(ref_lse)
     torch.testing.assert_close(lse.cpu()[live], ref_lse[live], atol=2e-3, rtol=1e-4)
@@ -137,6 +141,45 @@ def test_q_len_two_and_output_scale_and_f32_out(kernel):
 
     case = synth.build_case("spec", [3000, 1500], 128, 64, q_len=2, seed=12, device=_dev())
     check_case(case, kernel, output_scale=0.37, out_dtype=torch.float32)
+
+
+@pytest.mark.parametrize("kernel", ["fp32_check", "tcgen05", "tcgen05_2pass"])
+@pytest.mark.parametrize("which", ["sink", "soft_cap", "soft_cap_and_sink"])
+def test_attention_variants(which, kernel):
+    """The sink (counted once per request, however many CTAs share it) and the soft cap, against the oracle's restatement."""
+    from flashinfer_mla_fp4_b200 import AttentionWithSink, SoftCappingAttention, synth
+
+    dev = _dev()
+    for heads, q_len, lens, seed in ((64, 1, [9000, 130, 1, 4100], 21), (16, 2, [700, 64], 22), (128, 1, [20000], 23)):
+        case = synth.build_case(f"variant_{which}", lens, heads, 64, q_len=q_len, seed=seed, device=dev)
+        g = torch.Generator().manual_seed(seed)
+        # sinks from well below to well above the typical score, so that some heads are dominated by it
+        sink = (torch.rand(heads, generator=g) * 12.0 - 4.0).to(dev)
+        raw = (O.decode_e4m3(case.q.cpu()).float()[..., :512].norm(dim=-1).mean().item())
+        cap = max(1.0, 0.5 * raw)  # a cap the scores actually reach
+        variant = {"sink": AttentionWithSink(sink), "soft_cap": SoftCappingAttention(cap),
+                   "soft_cap_and_sink": SoftCappingAttention(cap, sink=sink)}[which]
+        check_case(case, kernel, variant=variant)
+
+
+def test_unknown_variants_are_rejected():
+    from flashinfer_mla_fp4_b200 import BatchMLADecodeCuteDSLFP4Wrapper, SoftCappingAttention
+
+    class WithTransform:
+        has_logits_transform = True
+
+    w = BatchMLADecodeCuteDSLFP4Wrapper(torch.empty(1 << 20, dtype=torch.int8, device=_dev()))
+    for v in (WithTransform(), object(), SoftCappingAttention(cap=0.0)):
+        with pytest.raises(ValueError):
+            w.plan(num_heads=64, page_size=64, variant=v)
+
+
+@pytest.mark.parametrize("max_ctas", [1, 7, 40])
+def test_grid_cap_limits_the_split(max_ctas):
+    from flashinfer_mla_fp4_b200 import synth
+
+    case = synth.build_case("capped", [6000, 300, 2500], 64, 64, seed=24, device=_dev())
+    check_case(case, "tcgen05", max_ctas=max_ctas)
 
 
 @pytest.mark.parametrize("kernel", ["tcgen05"])

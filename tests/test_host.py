@@ -22,7 +22,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in the header but not exported"
     assert set(_cabi.EXPORTS) == declared
-    assert lib.mla_fp4_abi_version() == _cabi.ABI_VERSION == 4
+    assert lib.mla_fp4_abi_version() == _cabi.ABI_VERSION == 5
 
 
 def test_abi_rejects_bad_arguments_without_a_gpu():

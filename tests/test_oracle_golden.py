@@ -90,3 +90,26 @@ def test_empty_request_gives_zero_and_minus_inf():
     out, lse = O.mla_decode(c.q, c.kv_cache, c.kv_cache_sf, c.block_tables, sl, c.softmax_scale)
     assert (out[1] == 0).all() and torch.isinf(lse[1]).all() and (lse[1] < 0).all()
     assert torch.isfinite(out[0]).all()
+
+
+def test_sink_equals_merging_a_zero_partial_and_huge_cap_changes_nothing():
+    """The two attention variants, pinned by identities: a sink is one more partial with a zero value row and
+    LSE = sink * log2(e); a soft cap far above every score is the identity, one far below gives uniform weights."""
+    from flashinfer_mla_fp4_b200 import synth
+
+    c = synth.build_case("t", [300, 77], 8, page_size=16, seed=7)
+    args = (c.q, c.kv_cache, c.kv_cache_sf, c.block_tables, c.seq_lens, c.softmax_scale)
+    plain, lse = O.mla_decode(*args)
+    sink = torch.linspace(-3.0, 6.0, 8)
+    with_sink, lse_sink = O.mla_decode(*args, sink=sink)
+    zero = torch.zeros_like(plain)
+    sink_lse = (sink * O.LOG2_E).view(1, 1, 8).expand_as(lse).contiguous()
+    merged, mlse = O.merge_partials([plain, zero], [lse, sink_lse])
+    torch.testing.assert_close(with_sink, merged, atol=1e-6, rtol=1e-5)
+    torch.testing.assert_close(lse_sink, mlse, atol=1e-4, rtol=1e-5)
+    same, _ = O.mla_decode(*args, logits_soft_cap=1e6)
+    torch.testing.assert_close(same, plain, atol=1e-5, rtol=1e-4)
+    flat, _ = O.mla_decode(*args, logits_soft_cap=1e-4)
+    lat, _ = O.dequantize_cache(c.kv_cache, c.kv_cache_sf)
+    mean0 = lat[c.block_tables[0, : (300 + 15) // 16].long()].reshape(-1, 512)[:300].mean(dim=0)
+    torch.testing.assert_close(flat[0, 0, 0], mean0, atol=1e-4, rtol=1e-3)
