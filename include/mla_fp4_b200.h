@@ -48,11 +48,13 @@ extern "C" {
 #define MLA_FP4_KERNEL_TCGEN05_2PASS 2   /* the tcgen05 kernel followed by a separate combine
                                             kernel (the reference's two-kernel structure)      */
 
-/* The workspace starts with a header of this many bytes: the generation of the last decode step
-   that ran on it and one flag per split-KV partial slot (the generation that last published the
-   slot).  It must be zero before the first decode step on that workspace
-   (mla_fp4_workspace_init); steps keep it consistent by themselves afterwards, also a step that
-   reported MLA_FP4_ERR_DEVICE_TIMEOUT, as long as its kernel returned.  The partial slots follow. */
+/* The workspace starts with a header of this many bytes (the generation of the last decode step
+   that completed on it and a count of the CTAs that have finished the running one), followed by
+   296 slot tails of 272 bytes (64 LSEs, the slot scale, and a flag: the generation that last
+   published the slot) and then the partial slots of 65536 bytes.  Header and tails must be zero
+   before the first decode step on that workspace (mla_fp4_workspace_init); completed steps keep
+   them consistent by themselves.  After a step that reported MLA_FP4_ERR_DEVICE_TIMEOUT call
+   mla_fp4_workspace_init again. */
 #define MLA_FP4_WORKSPACE_HEADER_BYTES 2048
 
 /* input element types of mla_fp4_cache_write */
