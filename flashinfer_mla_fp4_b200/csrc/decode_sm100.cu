@@ -43,6 +43,8 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "launch.h"
 #include "ptx_sm100.cuh"
@@ -90,7 +92,8 @@ constexpr int kBarRopeFull = 2 * kRing + 6, kBarRopeEmpty = 2 * kRing + 7, kBarP
               kBarTail = 2 * kRing + 14;
 constexpr int kNumBars = 2 * kRing + 15;
 constexpr uint32_t kOffTail = kOffBars + kNumBars * 8;                    // merge plan: [148] slot ids, then [64] f32 1/sum of weights
-constexpr uint32_t kOffTailInv = kOffTail + kMaxCombineSlots * 4;
+constexpr uint32_t kOffTailInv = (kOffTail + kMaxCombineSlots * 4 + 15u) & ~15u;
+static_assert(kOffTailInv % 16 == 0, "read with 16-byte shared loads");
 constexpr uint32_t kOffSegs = kOffTailInv + kGroupHeads * 4;              // Segment[kMaxSeg]
 constexpr uint32_t kOffMisc = kOffSegs + kMaxSeg * 24;                    // tmem base, abort flag, walker
 constexpr uint32_t kSmemBytes = kOffMisc + 256;
@@ -126,6 +129,7 @@ struct Misc {
   MergeReq merge[2];
   // the merge plan (plan_merge)
   int n_slots, n_part, rank, merge_k;
+  int unit0, unit1;  // this CTA's share of every slot of the merged request: units [unit0, unit1) of 32 bytes
 };
 static_assert(sizeof(Misc) <= 256, "misc area");
 
@@ -566,6 +570,11 @@ __device__ __forceinline__ float2 lds_f32x2(uint32_t addr) {
   asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
   return v;
 }
+__device__ __forceinline__ uint4 lds_u32x4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ float4 lds_f32x4(uint32_t addr) {
   float4 v;
   asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
@@ -780,15 +789,15 @@ __device__ __noinline__ void rescale_output(const Ctx& c, uint32_t tmem_lane, ui
 
 // Normalise O^T and write it: to the output tensor (slot < 0) or to a split-KV partial slot.
 // Runs once per segment, so its instructions are fetched cold: rolled loops over (block, 16 heads), a small body.
-__device__ __noinline__ void write_output(const DecodeParams& p, const Ctx& c, uint32_t tmem_lane, int row, int half,
-                                          int tid, int b, int g, int slot, float slot_scale_v) {
+// Normalise O^T and write it to the output tensor (a segment that covers its request).  Runs once per segment, so
+// its instructions are fetched cold, and a workload of many short requests runs it between every few tiles: rolled
+// loops over (block, 16 heads), a small body (unrolled four times it slowed the variable-length workload by 10 %).
+__device__ __noinline__ void write_final(const DecodeParams& p, const Ctx& c, uint32_t tmem_lane, int row, int half,
+                                         int tid, int b, int g) {
   int qpos, head0;
   group_coords(g, p.num_heads, qpos, head0);
   const int heads_here = min(kGroupHeads, p.num_heads - head0);
   const size_t row0 = (size_t(b) * p.q_len + qpos) * p.num_heads + head0;
-  const bool direct = slot < 0;
-  __half* so = reinterpret_cast<__half*>(slot_o(p.workspace, direct ? 0 : slot));
-  const float post = direct ? 1.f : 1.f / slot_scale_v;  // a partial is stored divided by its slot scale
   const uint32_t esz = uint32_t(out_elem_bytes(p.out_dtype));
 #pragma unroll 1
   for (int jb = 0; jb < kBlocks; ++jb) {  // a block of 128 dims: this thread's 32 heads as two TMEM loads in flight together
@@ -800,44 +809,70 @@ __device__ __noinline__ void write_output(const DecodeParams& p, const Ctx& c, u
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
       const int h0 = 32 * half + 16 * hh;
-      float v[16];
+      char* dst = static_cast<char*>(p.out) + ((row0 + h0) * kLatent + dim) * esz;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {  // output_scale / l of four heads per shared load
         const float4 f = lds_f32x4(c.smem + kOffLinv + 4 * (h0 + 4 * q));
-        v[4 * q] = __uint_as_float(o[hh][4 * q]) * (f.x * post);
-        v[4 * q + 1] = __uint_as_float(o[hh][4 * q + 1]) * (f.y * post);
-        v[4 * q + 2] = __uint_as_float(o[hh][4 * q + 2]) * (f.z * post);
-        v[4 * q + 3] = __uint_as_float(o[hh][4 * q + 3]) * (f.w * post);
-      }
-      if (!direct) {
-        uint32_t pk[8];
+        const float fs[4] = {f.x, f.y, f.z, f.w};
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          __half2 h2 = __floats2half2_rn(v[2 * q], v[2 * q + 1]);
-          pk[q] = *reinterpret_cast<uint32_t*>(&h2);
-        }
-        // the warp's 32 dims x 8 heads are 512 contiguous bytes of the slot
-        *reinterpret_cast<uint4*>(so + slot_o_index(dim, h0)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-        *reinterpret_cast<uint4*>(so + slot_o_index(dim, h0 + 8)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-      } else {
-        char* dst = static_cast<char*>(p.out) + ((row0 + h0) * kLatent + dim) * esz;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
+        for (int e = 0; e < 4; ++e) {
+          const int i = 4 * q + e;
           if (h0 + i < heads_here) {
+            const float v = __uint_as_float(o[hh][i]) * fs[e];
             char* d = dst + size_t(i) * kLatent * esz;
-            if (p.out_dtype == MLA_FP4_OUT_BF16) *reinterpret_cast<__nv_bfloat16*>(d) = __float2bfloat16_rn(v[i]);
-            else if (p.out_dtype == MLA_FP4_OUT_F32) *reinterpret_cast<float*>(d) = v[i];
-            else *reinterpret_cast<uint8_t*>(d) = __nv_cvt_float_to_fp8(v[i], __NV_SATFINITE, __NV_E4M3);
+            if (p.out_dtype == MLA_FP4_OUT_BF16) *reinterpret_cast<__nv_bfloat16*>(d) = __float2bfloat16_rn(v);
+            else if (p.out_dtype == MLA_FP4_OUT_F32) *reinterpret_cast<float*>(d) = v;
+            else *reinterpret_cast<uint8_t*>(d) = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
           }
         }
       }
     }
   }
-  const float lse = lds_f32(c.smem + kOffLse + 4 * (tid & 63));
-  if (direct) {
-    if (p.lse && tid < heads_here) p.lse[row0 + tid] = lse;
-  } else if (tid < kGroupHeads) {
-    slot_lse(p.workspace, slot)[tid] = lse;
+  if (p.lse && tid < heads_here) p.lse[row0 + tid] = lds_f32(c.smem + kOffLse + 4 * tid);
+}
+
+// Normalise O^T and write it to a split-KV partial slot, as fp16 divided by the slot scale.  A block of 128 dims per
+// round: this thread's 32 heads as two TMEM loads.  The loads of the next block are in flight while this one is
+// scaled, converted and stored (a round is bound by the latencies of load -> convert -> store, not by their amounts:
+// 64 registers of buffer buy the overlap).
+__device__ __noinline__ void write_partial(const DecodeParams& p, const Ctx& c, uint32_t tmem_lane, int row, int half,
+                                           int tid, int slot, float slot_scale_v) {
+  __half* so = reinterpret_cast<__half*>(slot_o(p.workspace, slot));
+  const float post = 1.f / slot_scale_v;  // a partial is stored divided by its slot scale
+  uint32_t o[2][2][16];
+  ptx::tmem_ld16(tmem_lane + kColO + uint32_t(32 * half), o[0][0]);
+  ptx::tmem_ld16(tmem_lane + kColO + uint32_t(32 * half + 16), o[0][1]);
+#pragma unroll
+  for (int jb = 0; jb < kBlocks; ++jb) {
+    if (tid == 0) MLA_TRACE(10, uint32_t(jb), 0);
+    const int cur = jb & 1;
+    const int dim = 128 * jb + row;
+    ptx::tmem_wait_ld();
+    if (jb + 1 < kBlocks) {
+      ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(jb + 1) + uint32_t(32 * half), o[cur ^ 1][0]);
+      ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(jb + 1) + uint32_t(32 * half + 16), o[cur ^ 1][1]);
+    }
+    if (tid == 0) MLA_TRACE(10, uint32_t(jb), 1);
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int h0 = 32 * half + 16 * hh;
+      uint32_t pk[8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {  // output_scale / l of four heads per shared load
+        const float4 f = lds_f32x4(c.smem + kOffLinv + 4 * (h0 + 4 * q));
+        __half2 a = __floats2half2_rn(__uint_as_float(o[cur][hh][4 * q]) * (f.x * post), __uint_as_float(o[cur][hh][4 * q + 1]) * (f.y * post));
+        __half2 b2 = __floats2half2_rn(__uint_as_float(o[cur][hh][4 * q + 2]) * (f.z * post), __uint_as_float(o[cur][hh][4 * q + 3]) * (f.w * post));
+        pk[2 * q] = *reinterpret_cast<uint32_t*>(&a);
+        pk[2 * q + 1] = *reinterpret_cast<uint32_t*>(&b2);
+      }
+      // the warp's 32 dims x 8 heads are 512 contiguous bytes of the slot
+      *reinterpret_cast<uint4*>(so + slot_o_index(dim, h0)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      *reinterpret_cast<uint4*>(so + slot_o_index(dim, h0 + 8)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+    }
+  }
+  if (tid == 0) MLA_TRACE(10, 4u, 0);
+  if (tid < kGroupHeads) {
+    slot_lse(p.workspace, slot)[tid] = lds_f32(c.smem + kOffLse + 4 * tid);
     if (tid == 0) slot_scale(p.workspace, slot)[0] = slot_scale_v;
   }
 }
@@ -969,7 +1004,10 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       for (int w8 = 0; w8 < kSoftmaxThreads / 32; ++w8) sc_all = fmaxf(sc_all, lds_f32(c.smem + kOffScMax + 4 * w8));
       const float slot_scale_v = slot_scale_for(6.f * sc_all * fabsf(p.output_scale));
       if (tid == 0) MLA_TRACE(0, lit, 7);
-      if (!c.misc->abort) write_output(p, c, tmem_lane, row, half, tid, g.b, g.g, g.slot, slot_scale_v);
+      if (!c.misc->abort) {
+        if (g.slot < 0) write_final(p, c, tmem_lane, row, half, tid, g.b, g.g);
+        else write_partial(p, c, tmem_lane, row, half, tid, g.slot, slot_scale_v);
+      }
       if (tid == 0) MLA_TRACE(0, lit, 4);
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar_addr(c, kBarOFree));
@@ -988,7 +1026,11 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
   // all of them, after the last segment: a fence in the middle would hold up the next segment's first tile,
   // and nobody can use a partial before this CTA, itself a writer of the later request, is done anyway.
   if (n_pending > 0) {
+#ifdef MLA_FP4_FENCE_ALL
     __threadfence();
+#endif
+    // One release for the whole CTA: the barrier orders every thread's stores before thread 0's release, and a release is
+    // cumulative (a fence by each of the 256 threads before the barrier measured no better).
     ptx::bar_sync(1, kSoftmaxThreads);
     if (tid == 0) {
       st_release(slot_flag(p.workspace, pending0), c.gen);
@@ -1137,10 +1179,18 @@ __device__ __noinline__ void plan_merge(const Ctx& c, int lane) {
     if (bw == 0 && cnt > 0) break;  // past the request
   }
   if (lane == 0) {
-    misc->n_slots = min(cnt, kMaxCombineSlots);
+    const int ns = min(cnt, kMaxCombineSlots);
+    misc->n_slots = ns;
     misc->n_part = part;
     misc->rank = rank;
     misc->merge_k = k;
+    // what the tail would otherwise compute on its critical path: the share, and the barrier its copies complete on
+    misc->unit0 = part > 0 ? (2048 * rank) / part : 0;
+    misc->unit1 = part > 0 ? (2048 * (rank + 1)) / part : 0;
+    if (ns > 0) {
+      ptx::mbar_init(bar_addr(c, kBarTail), uint32_t(ns));  // one arrival per slot
+      ptx::fence_barrier_init();
+    }
   }
 }
 
@@ -1160,67 +1210,59 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
   const size_t row0 = (size_t(m.b) * p.q_len + qpos) * p.num_heads + head0;
   // This CTA's share of every slot: units [2048*rank/np, 2048*(rank+1)/np) of 32 bytes (a pair of dims of one head
   // group, in the slot's own order), so a share is one contiguous range of the slot: one bulk copy.
-  const int U0 = (2048 * rank) / np, U1 = (2048 * (rank + 1)) / np;
+  const int U0 = misc->unit0, U1 = misc->unit1;
   const uint32_t share_bytes = uint32_t(U1 - U0) * 32u;
-  const int s0 = int(lds_u32(list));
   const uint32_t rows = c.smem + kTailStage;
-  const uint32_t tails = rows + uint32_t(ns) * share_bytes;  // the tails of slots s0 .. last, as they lie in the workspace
-  const int warps = (ns + 31) >> 5;
-  const bool fits = uint32_t(ns) * share_bytes + uint32_t(2 * ns + 2) * kTailLseBytes <= kTailStageBytes;
+  const uint32_t tails = rows + uint32_t(ns) * share_bytes;  // the tails of the listed slots, in list order
+  const bool fits = uint32_t(ns) * (share_bytes + kTailLseBytes) <= kTailStageBytes;
   if (tid == 0) {
-    ptx::mbar_init(bar_addr(c, kBarTail), uint32_t(ns + warps));  // one arrival per slot and one per warp's range of tails
-    ptx::fence_barrier_init();
     if (!fits) flag_timeout(c, 200, uint32_t(ns));  // cannot happen: mergers >= writers - 1
     MLA_TRACE(3, 1u, 1);
   }
-  __syncthreads();
-  // Thread i: wait for slot i, then fetch this CTA's share of it.  The warps poll in step (a ballot ends the loop)
-  // and the lanes whose flags came up in the same round issue their copies together.  A bulk copy costs about
-  // fifty clocks to issue whatever its size: one per slot, and one per warp for the tails of its 32 slots.
-  if (tid < 32 * warps && !misc->abort) {
-    const bool mine = tid < ns;
-    const int slot = mine ? int(lds_u32(list + 4u * uint32_t(tid))) : 0;
-    const int32_t* flag = slot_flag(ws, slot);
-    const uint32_t bar = bar_addr(c, kBarTail);
-    bool done = !mine;
+  // Slot i belongs to lane i / kWarps of warp i % kWarps: wait for its flag, then fetch this CTA's share of it and its
+  // tail (LSEs, scale).  A bulk copy costs about fifty clocks to issue whatever its size and the lanes of a warp issue
+  // theirs one after the other, so the slots are dealt round the warps (32 slots on one warp spent 1.6 k clocks
+  // issuing).  The lanes of a warp poll in step (a ballot ends the loop).
+  {
+    constexpr int kWarps = kThreads / 32;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int i = lane * kWarps + warp;           // slot index in the list
+    const bool mine = i < ns;
+    const bool busy = __any_sync(0xffffffffu, mine);
+    if (busy && !misc->abort) {
+      const int slot = mine ? int(lds_u32(list + 4u * uint32_t(i))) : 0;
+      const int32_t* flag = slot_flag(ws, slot);
+      const uint32_t bar = bar_addr(c, kBarTail);
+      bool done = !mine;
 #pragma unroll 1
-    for (uint32_t i = 0; i < c.polls; ++i) {
-      const bool now = !done && ld_acquire(flag) == c.gen;  // acquire: the slot's bytes, written before the flag, are read after it
-      if (now) {
-        done = true;
+      for (uint32_t it = 0; it < c.polls; ++it) {
+        const bool now = !done && ld_acquire(flag) == c.gen;  // acquire: the slot's bytes, written before the flag, are read after it
+        if (now) {
+          done = true;
 #ifdef MLA_FP4_TRACE
-        if (int(blockIdx.x) == c.trace_cta && c.status && tid < 128) {
-          unsigned long long t;
-          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-          long long* tr = reinterpret_cast<long long*>(c.status + 8) + ((4 + (tid >> 4)) * 16 + (tid & 15)) * 8;
-          tr[0] = (long long)t;
-          tr[1] = slot;
-        }
+          if (int(blockIdx.x) == c.trace_cta && c.status && i < 96) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            long long* tr = reinterpret_cast<long long*>(c.status + 8) + ((4 + (i >> 4)) * 16 + (i & 15)) * 8;
+            tr[0] = (long long)t;
+            tr[1] = slot;
+          }
 #endif
-        if (fits) {
-          // The copy reads the slot from L2, where its writer's fence put it before the flag: no proxy fence is
-          // needed for that, and a full fence.proxy.async here cost microseconds.
-          ptx::mbar_arrive_expect_tx(bar, share_bytes);
-          ptx::bulk_load(rows + uint32_t(tid) * share_bytes, reinterpret_cast<const char*>(slot_o(ws, slot)) + size_t(U0) * 32, share_bytes, bar);
-        } else {
-          ptx::mbar_arrive(bar);
+          if (fits) {
+            // The copy reads the slot from L2, where its writer's fence put it before the flag: no proxy fence is
+            // needed for that, and a full fence.proxy.async here cost microseconds.
+            ptx::mbar_arrive_expect_tx(bar, share_bytes + kTailLseBytes);
+            ptx::bulk_load(rows + uint32_t(i) * share_bytes, reinterpret_cast<const char*>(slot_o(ws, slot)) + size_t(U0) * 32, share_bytes, bar);
+            ptx::bulk_load(tails + uint32_t(i) * kTailLseBytes, slot_lse(ws, slot), kTailLseBytes, bar);  // its LSEs and scale
+          } else {
+            ptx::mbar_arrive(bar);
+          }
         }
+        if (__all_sync(0xffffffffu, done) || misc->abort) break;
+        __nanosleep(64);
       }
-      if (__all_sync(0xffffffffu, done) || misc->abort) break;
-      __nanosleep(64);
-    }
-    const bool all = __all_sync(0xffffffffu, done);
-    if (!done) {  // the budget ran out (or the CTA is giving up): the barrier still gets this slot's arrival
-      if (!misc->abort) flag_timeout(c, 100, uint32_t(slot));
-      ptx::mbar_arrive(bar);
-    }
-    if ((tid & 31) == 0) {  // the tails of this warp's slots: one contiguous range of the workspace
-      const int first = slot, last = int(lds_u32(list + 4u * uint32_t(min(tid + 31, ns - 1))));
-      if (all && fits) {
-        const uint32_t bytes = uint32_t(last - first + 1) * kTailLseBytes;
-        ptx::mbar_arrive_expect_tx(bar, bytes);
-        ptx::bulk_load(tails + uint32_t(first - s0) * kTailLseBytes, slot_lse(ws, first), bytes, bar);
-      } else {
+      if (!done) {  // the budget ran out (or the CTA is giving up): the barrier still gets this slot's arrivals
+        if (!misc->abort) flag_timeout(c, 100, uint32_t(slot));
         ptx::mbar_arrive(bar);
       }
     }
@@ -1241,7 +1283,7 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int i = min(i0 + 4 * q, ns - 1);
-          l[q] = lds_f32(col + uint32_t(int(lds_u32(list + 4u * uint32_t(i))) - s0) * kTailLseBytes);
+          l[q] = lds_f32(col + uint32_t(i) * kTailLseBytes);
         }
         mx = fmaxf(fmaxf(mx, fmaxf(l[0], l[1])), fmaxf(l[2], l[3]));
       }
@@ -1255,7 +1297,7 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int i = min(i0 + 4 * q, ns - 1);
-          at[q] = uint32_t(int(lds_u32(list + 4u * uint32_t(i))) - s0) * kTailLseBytes;
+          at[q] = uint32_t(i) * kTailLseBytes;
           l[q] = lds_f32(col + at[q]);
           sc[q] = lds_f32(tails + at[q] + 4u * kGroupHeads);
         }
@@ -1276,40 +1318,76 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
     __syncthreads();
     if (tid == 0) MLA_TRACE(3, 1u, 4);
     // An item is (unit of this CTA's share, pair of heads of the unit's group): 4 bytes per dim and slot.
+    // (Measured alternative: one unit per thread read with 16-byte loads, a quarter of the shared-memory wavefronts
+    // but a quarter of the threads busy: slower, 22.4 against 21.1 us on the short workload.)
     const int items = (U1 - U0) * 4;
-#pragma unroll 1
-    for (int item = tid; item < items; item += kThreads) {
-      const int u = U0 + (item >> 2), hq = item & 3;
-      const int head = 8 * (u >> 8) + 2 * hq, dim = 2 * (u & 255);
-      const uint32_t src = rows + uint32_t(item >> 2) * 32u + 4u * uint32_t(hq);
-      const uint32_t wcol = tails + 4u * uint32_t(head);
-      float a00 = 0.f, a01 = 0.f, a10 = 0.f, a11 = 0.f;  // [dim][head]
+    auto round = [&](int base, auto two_tag) {
+      constexpr int E = decltype(two_tag)::value;  // items per thread in this round
+      int item[E];
+      uint32_t src[E], wcol[E];
+      float acc[E][4];  // [item][dim * 2 + head]
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        item[e] = min(base + e * kThreads + tid, items - 1);  // a thread without an item repeats the last one and stores nothing
+        const int u = U0 + (item[e] >> 2), hq = item[e] & 3;
+        src[e] = rows + uint32_t(item[e] >> 2) * 32u + 4u * uint32_t(hq);
+        wcol[e] = tails + 4u * uint32_t(8 * (u >> 8) + 2 * hq);
+        acc[e][0] = acc[e][1] = acc[e][2] = acc[e][3] = 0.f;
+      }
 #pragma unroll 1
       for (int i0 = 0; i0 < ns; i0 += 4) {  // four slots at a time: their loads first; the sums still in slot order
-        uint32_t u0[4], u1[4];
-        float2 wv[4];
+        uint32_t u0[E][4], u1[E][4];
+        float2 wv[E][4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const int i = min(i0 + q, ns - 1);
-          u0[q] = lds_u32(src + uint32_t(i) * share_bytes);
-          u1[q] = lds_u32(src + uint32_t(i) * share_bytes + 16u);
-          wv[q] = lds_f32x2(wcol + uint32_t(int(lds_u32(list + 4u * uint32_t(i))) - s0) * kTailLseBytes);
+          const uint32_t i = uint32_t(min(i0 + q, ns - 1));
+#pragma unroll
+          for (int e = 0; e < E; ++e) {
+            u0[e][q] = lds_u32(src[e] + i * share_bytes);
+            u1[e][q] = lds_u32(src[e] + i * share_bytes + 16u);
+            wv[e][q] = lds_f32x2(wcol[e] + i * kTailLseBytes);
+          }
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           if (i0 + q < ns) {  // in slot order: bit-reproducible whatever the order of arrival
-            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u0[q])), f1 = __half22float2(*reinterpret_cast<const __half2*>(&u1[q]));
-            a00 += wv[q].x * f0.x;
-            a01 += wv[q].y * f0.y;
-            a10 += wv[q].x * f1.x;
-            a11 += wv[q].y * f1.y;
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+              const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u0[e][q])), f1 = __half22float2(*reinterpret_cast<const __half2*>(&u1[e][q]));
+              acc[e][0] += wv[e][q].x * f0.x;
+              acc[e][1] += wv[e][q].y * f0.y;
+              acc[e][2] += wv[e][q].x * f1.x;
+              acc[e][3] += wv[e][q].y * f1.y;
+            }
           }
         }
       }
-      const float2 inv = lds_f32x2(c.smem + kOffTailInv + 4u * uint32_t(head));
-      const size_t idx = (row0 + head) * kLatent + dim;
-      if (head < heads_here) store_out_pair(p.out, p.out_dtype, idx, a00 * inv.x, a10 * inv.x);
-      if (head + 1 < heads_here) store_out_pair(p.out, p.out_dtype, idx + kLatent, a01 * inv.y, a11 * inv.y);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        if (base + e * kThreads + tid < items) {
+          const int u = U0 + (item[e] >> 2), hq = item[e] & 3;
+          const int head = 8 * (u >> 8) + 2 * hq, dim = 2 * (u & 255);
+          const float2 inv = lds_f32x2(c.smem + kOffTailInv + 4u * uint32_t(head));
+          const size_t idx = (row0 + head) * kLatent + dim;
+          if (head < heads_here) store_out_pair(p.out, p.out_dtype, idx, acc[e][0] * inv.x, acc[e][2] * inv.x);
+          if (head + 1 < heads_here) store_out_pair(p.out, p.out_dtype, idx + kLatent, acc[e][1] * inv.y, acc[e][3] * inv.y);
+        }
+      }
+    };
+    // A thread takes two items per round when there are that many (tid and tid + kThreads) and walks the slots once for
+    // both: a round is bound by the chain of shared-memory latencies along the slots, so the second item rides along
+    // (455 items on 384 threads were two rounds, the second of them nearly empty).
+#pragma unroll 1
+    for (int base = 0; base < items;) {
+      if (tid == 0) MLA_TRACE(10, 5u + uint32_t(base / kThreads), 0);
+      if (items - base > kThreads) {
+        round(base, std::integral_constant<int, 2>{});
+        base += 2 * kThreads;
+      } else {
+        round(base, std::integral_constant<int, 1>{});
+        base += kThreads;
+      }
+      if (tid == 0) MLA_TRACE(10, 5u + uint32_t(base / kThreads), 1);
     }
     if (tid == 0) MLA_TRACE(3, 1u, 5);
   }
