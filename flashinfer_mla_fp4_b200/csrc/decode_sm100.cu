@@ -43,8 +43,6 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
-#include <type_traits>
-
 #include "common.cuh"
 #include "launch.h"
 #include "ptx_sm100.cuh"
@@ -792,13 +790,14 @@ __device__ __noinline__ void rescale_output(const Ctx& c, uint32_t tmem_lane, ui
 // Normalise O^T and write it to the output tensor (a segment that covers its request).  Runs once per segment, so
 // its instructions are fetched cold, and a workload of many short requests runs it between every few tiles: rolled
 // loops over (block, 16 heads), a small body (unrolled four times it slowed the variable-length workload by 10 %).
+template <int kOutDtype>  // one instantiation per output type: a call fetches the instructions of its own type only
 __device__ __noinline__ void write_final(const DecodeParams& p, const Ctx& c, uint32_t tmem_lane, int row, int half,
                                          int tid, int b, int g) {
   int qpos, head0;
   group_coords(g, p.num_heads, qpos, head0);
   const int heads_here = min(kGroupHeads, p.num_heads - head0);
   const size_t row0 = (size_t(b) * p.q_len + qpos) * p.num_heads + head0;
-  const uint32_t esz = uint32_t(out_elem_bytes(p.out_dtype));
+  constexpr uint32_t esz = kOutDtype == MLA_FP4_OUT_F32 ? 4u : (kOutDtype == MLA_FP4_OUT_BF16 ? 2u : 1u);
 #pragma unroll 1
   for (int jb = 0; jb < kBlocks; ++jb) {  // a block of 128 dims: this thread's 32 heads as two TMEM loads in flight together
     uint32_t o[2][16];
@@ -820,8 +819,8 @@ __device__ __noinline__ void write_final(const DecodeParams& p, const Ctx& c, ui
           if (h0 + i < heads_here) {
             const float v = __uint_as_float(o[hh][i]) * fs[e];
             char* d = dst + size_t(i) * kLatent * esz;
-            if (p.out_dtype == MLA_FP4_OUT_BF16) *reinterpret_cast<__nv_bfloat16*>(d) = __float2bfloat16_rn(v);
-            else if (p.out_dtype == MLA_FP4_OUT_F32) *reinterpret_cast<float*>(d) = v;
+            if (kOutDtype == MLA_FP4_OUT_BF16) *reinterpret_cast<__nv_bfloat16*>(d) = __float2bfloat16_rn(v);
+            else if (kOutDtype == MLA_FP4_OUT_F32) *reinterpret_cast<float*>(d) = v;
             else *reinterpret_cast<uint8_t*>(d) = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
           }
         }
@@ -839,20 +838,13 @@ __device__ __noinline__ void write_partial(const DecodeParams& p, const Ctx& c, 
                                            int tid, int slot, float slot_scale_v) {
   __half* so = reinterpret_cast<__half*>(slot_o(p.workspace, slot));
   const float post = 1.f / slot_scale_v;  // a partial is stored divided by its slot scale
+  // Two blocks per round of a rolled loop (this runs once per partial: unrolled four times its instructions took
+  // longer to fetch than the overlap saved).
   uint32_t o[2][2][16];
   ptx::tmem_ld16(tmem_lane + kColO + uint32_t(32 * half), o[0][0]);
   ptx::tmem_ld16(tmem_lane + kColO + uint32_t(32 * half + 16), o[0][1]);
-#pragma unroll
-  for (int jb = 0; jb < kBlocks; ++jb) {
-    if (tid == 0) MLA_TRACE(10, uint32_t(jb), 0);
-    const int cur = jb & 1;
+  auto convert_store = [&](const uint32_t (&ob)[2][16], int jb) {
     const int dim = 128 * jb + row;
-    ptx::tmem_wait_ld();
-    if (jb + 1 < kBlocks) {
-      ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(jb + 1) + uint32_t(32 * half), o[cur ^ 1][0]);
-      ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(jb + 1) + uint32_t(32 * half + 16), o[cur ^ 1][1]);
-    }
-    if (tid == 0) MLA_TRACE(10, uint32_t(jb), 1);
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
       const int h0 = 32 * half + 16 * hh;
@@ -860,8 +852,8 @@ __device__ __noinline__ void write_partial(const DecodeParams& p, const Ctx& c, 
 #pragma unroll
       for (int q = 0; q < 4; ++q) {  // output_scale / l of four heads per shared load
         const float4 f = lds_f32x4(c.smem + kOffLinv + 4 * (h0 + 4 * q));
-        __half2 a = __floats2half2_rn(__uint_as_float(o[cur][hh][4 * q]) * (f.x * post), __uint_as_float(o[cur][hh][4 * q + 1]) * (f.y * post));
-        __half2 b2 = __floats2half2_rn(__uint_as_float(o[cur][hh][4 * q + 2]) * (f.z * post), __uint_as_float(o[cur][hh][4 * q + 3]) * (f.w * post));
+        __half2 a = __floats2half2_rn(__uint_as_float(ob[hh][4 * q]) * (f.x * post), __uint_as_float(ob[hh][4 * q + 1]) * (f.y * post));
+        __half2 b2 = __floats2half2_rn(__uint_as_float(ob[hh][4 * q + 2]) * (f.z * post), __uint_as_float(ob[hh][4 * q + 3]) * (f.w * post));
         pk[2 * q] = *reinterpret_cast<uint32_t*>(&a);
         pk[2 * q + 1] = *reinterpret_cast<uint32_t*>(&b2);
       }
@@ -869,6 +861,20 @@ __device__ __noinline__ void write_partial(const DecodeParams& p, const Ctx& c, 
       *reinterpret_cast<uint4*>(so + slot_o_index(dim, h0)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       *reinterpret_cast<uint4*>(so + slot_o_index(dim, h0 + 8)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
     }
+  };
+#pragma unroll 1
+  for (int jp = 0; jp < kBlocks / 2; ++jp) {
+    if (tid == 0) MLA_TRACE(10, uint32_t(2 * jp), 0);
+    ptx::tmem_wait_ld();
+    ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(2 * jp + 1) + uint32_t(32 * half), o[1][0]);
+    ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(2 * jp + 1) + uint32_t(32 * half + 16), o[1][1]);
+    convert_store(o[0], 2 * jp);
+    ptx::tmem_wait_ld();
+    if (jp + 1 < kBlocks / 2) {
+      ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(2 * jp + 2) + uint32_t(32 * half), o[0][0]);
+      ptx::tmem_ld16(tmem_lane + kColO + 64u * uint32_t(2 * jp + 2) + uint32_t(32 * half + 16), o[0][1]);
+    }
+    convert_store(o[1], 2 * jp + 1);
   }
   if (tid == 0) MLA_TRACE(10, 4u, 0);
   if (tid < kGroupHeads) {
@@ -1005,8 +1011,10 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       const float slot_scale_v = slot_scale_for(6.f * sc_all * fabsf(p.output_scale));
       if (tid == 0) MLA_TRACE(0, lit, 7);
       if (!c.misc->abort) {
-        if (g.slot < 0) write_final(p, c, tmem_lane, row, half, tid, g.b, g.g);
-        else write_partial(p, c, tmem_lane, row, half, tid, g.slot, slot_scale_v);
+        if (g.slot >= 0) write_partial(p, c, tmem_lane, row, half, tid, g.slot, slot_scale_v);
+        else if (p.out_dtype == MLA_FP4_OUT_BF16) write_final<MLA_FP4_OUT_BF16>(p, c, tmem_lane, row, half, tid, g.b, g.g);
+        else if (p.out_dtype == MLA_FP4_OUT_F32) write_final<MLA_FP4_OUT_F32>(p, c, tmem_lane, row, half, tid, g.b, g.g);
+        else write_final<MLA_FP4_OUT_E4M3>(p, c, tmem_lane, row, half, tid, g.b, g.g);
       }
       if (tid == 0) MLA_TRACE(0, lit, 4);
       ptx::tc_fence_before();
@@ -1271,6 +1279,9 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
   const bool landed = wait(c, kBarTail, 0);
   if (tid == 0) MLA_TRACE(3, 1u, 3);
   if (landed && !misc->abort) {
+    // The tail runs once: what it costs is mostly the fetching of its instructions (8 KB of straight-line code added
+    // here cost the north-star step 3 us, 0.4 us per KB), so the loops below are rolled and small rather than
+    // unrolled for throughput.
     // weights: four lanes per head split the slots; butterflies give all four the results.  w_i = 2^(lse_i - max) *
     // slot scale, left in place of the LSE; the division by their sum is one multiply per output at the end.
     if (tid < 4 * kGroupHeads) {
@@ -1278,116 +1289,75 @@ __device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int
       const uint32_t col = tails + 4u * uint32_t(h);
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int i0 = j; i0 < ns; i0 += 16) {
-        float l[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int i = min(i0 + 4 * q, ns - 1);
-          l[q] = lds_f32(col + uint32_t(i) * kTailLseBytes);
-        }
-        mx = fmaxf(fmaxf(mx, fmaxf(l[0], l[1])), fmaxf(l[2], l[3]));
-      }
-#pragma unroll
-      for (int off = 2; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      for (int i = j; i < ns; i += 4) mx = fmaxf(mx, lds_f32(col + uint32_t(i) * kTailLseBytes));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
       float dsum = 0.f;
 #pragma unroll 1
-      for (int i0 = j; i0 < ns; i0 += 16) {
-        float l[4], sc[4];
-        uint32_t at[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int i = min(i0 + 4 * q, ns - 1);
-          at[q] = uint32_t(i) * kTailLseBytes;
-          l[q] = lds_f32(col + at[q]);
-          sc[q] = lds_f32(tails + at[q] + 4u * kGroupHeads);
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          if (i0 + 4 * q < ns) {
-            const float e = (l[q] == -INFINITY) ? 0.f : ptx::ex2(l[q] - mx);
-            sts_f32(col + at[q], e * sc[q]);
-            dsum += e;
-          }
-        }
+      for (int i = j; i < ns; i += 4) {
+        const uint32_t at = uint32_t(i) * kTailLseBytes;
+        const float l = lds_f32(col + at);
+        const float e = (l == -INFINITY) ? 0.f : ptx::ex2(l - mx);
+        sts_f32(col + at, e * lds_f32(tails + at + 4u * kGroupHeads));
+        dsum += e;
       }
-#pragma unroll
-      for (int off = 2; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
-      if (j == 0) sts_f32(c.smem + kOffTailInv + 4u * uint32_t(h), dsum > 0.f ? __frcp_rn(dsum) : 0.f);
-      if (j == 0 && rank == 0 && p.lse && h < heads_here) p.lse[row0 + h] = (dsum > 0.f) ? (__log2f(dsum) + mx) : -INFINITY;
+      dsum += __shfl_xor_sync(0xffffffffu, dsum, 1);
+      dsum += __shfl_xor_sync(0xffffffffu, dsum, 2);
+      if (j == 0) {
+        sts_f32(c.smem + kOffTailInv + 4u * uint32_t(h), dsum > 0.f ? __frcp_rn(dsum) : 0.f);
+        if (rank == 0 && p.lse && h < heads_here) p.lse[row0 + h] = (dsum > 0.f) ? (__log2f(dsum) + mx) : -INFINITY;
+      }
     }
     __syncthreads();
     if (tid == 0) MLA_TRACE(3, 1u, 4);
-    // An item is (unit of this CTA's share, pair of heads of the unit's group): 4 bytes per dim and slot.
-    // (Measured alternative: one unit per thread read with 16-byte loads, a quarter of the shared-memory wavefronts
-    // but a quarter of the threads busy: slower, 22.4 against 21.1 us on the short workload.)
+    // An item is (unit of this CTA's share, pair of heads of the unit's group): 4 bytes per dim and slot; the sums
+    // run in slot order (bit-reproducible whatever the order of arrival), four slots' loads in flight together.
     const int items = (U1 - U0) * 4;
-    auto round = [&](int base, auto two_tag) {
-      constexpr int E = decltype(two_tag)::value;  // items per thread in this round
-      int item[E];
-      uint32_t src[E], wcol[E];
-      float acc[E][4];  // [item][dim * 2 + head]
-#pragma unroll
-      for (int e = 0; e < E; ++e) {
-        item[e] = min(base + e * kThreads + tid, items - 1);  // a thread without an item repeats the last one and stores nothing
-        const int u = U0 + (item[e] >> 2), hq = item[e] & 3;
-        src[e] = rows + uint32_t(item[e] >> 2) * 32u + 4u * uint32_t(hq);
-        wcol[e] = tails + 4u * uint32_t(8 * (u >> 8) + 2 * hq);
-        acc[e][0] = acc[e][1] = acc[e][2] = acc[e][3] = 0.f;
-      }
 #pragma unroll 1
-      for (int i0 = 0; i0 < ns; i0 += 4) {  // four slots at a time: their loads first; the sums still in slot order
-        uint32_t u0[E][4], u1[E][4];
-        float2 wv[E][4];
+    for (int item = tid; item < items; item += kThreads) {
+      const int u = U0 + (item >> 2), hq = item & 3;
+      const int head = 8 * (u >> 8) + 2 * hq, dim = 2 * (u & 255);
+      uint32_t src = rows + uint32_t(item >> 2) * 32u + 4u * uint32_t(hq);
+      uint32_t wcol = tails + 4u * uint32_t(head);
+      float a00 = 0.f, a01 = 0.f, a10 = 0.f, a11 = 0.f;  // [dim][head]
+      int i = 0;
+#pragma unroll 1
+      for (; i + 4 <= ns; i += 4) {
+        uint32_t u0[4], u1[4];
+        float2 wv[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const uint32_t i = uint32_t(min(i0 + q, ns - 1));
-#pragma unroll
-          for (int e = 0; e < E; ++e) {
-            u0[e][q] = lds_u32(src[e] + i * share_bytes);
-            u1[e][q] = lds_u32(src[e] + i * share_bytes + 16u);
-            wv[e][q] = lds_f32x2(wcol[e] + i * kTailLseBytes);
-          }
+          u0[q] = lds_u32(src);
+          u1[q] = lds_u32(src + 16u);
+          wv[q] = lds_f32x2(wcol);
+          src += share_bytes;
+          wcol += kTailLseBytes;
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          if (i0 + q < ns) {  // in slot order: bit-reproducible whatever the order of arrival
-#pragma unroll
-            for (int e = 0; e < E; ++e) {
-              const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u0[e][q])), f1 = __half22float2(*reinterpret_cast<const __half2*>(&u1[e][q]));
-              acc[e][0] += wv[e][q].x * f0.x;
-              acc[e][1] += wv[e][q].y * f0.y;
-              acc[e][2] += wv[e][q].x * f1.x;
-              acc[e][3] += wv[e][q].y * f1.y;
-            }
-          }
+          const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u0[q])), f1 = __half22float2(*reinterpret_cast<const __half2*>(&u1[q]));
+          a00 += wv[q].x * f0.x;
+          a01 += wv[q].y * f0.y;
+          a10 += wv[q].x * f1.x;
+          a11 += wv[q].y * f1.y;
         }
       }
-#pragma unroll
-      for (int e = 0; e < E; ++e) {
-        if (base + e * kThreads + tid < items) {
-          const int u = U0 + (item[e] >> 2), hq = item[e] & 3;
-          const int head = 8 * (u >> 8) + 2 * hq, dim = 2 * (u & 255);
-          const float2 inv = lds_f32x2(c.smem + kOffTailInv + 4u * uint32_t(head));
-          const size_t idx = (row0 + head) * kLatent + dim;
-          if (head < heads_here) store_out_pair(p.out, p.out_dtype, idx, acc[e][0] * inv.x, acc[e][2] * inv.x);
-          if (head + 1 < heads_here) store_out_pair(p.out, p.out_dtype, idx + kLatent, acc[e][1] * inv.y, acc[e][3] * inv.y);
-        }
-      }
-    };
-    // A thread takes two items per round when there are that many (tid and tid + kThreads) and walks the slots once for
-    // both: a round is bound by the chain of shared-memory latencies along the slots, so the second item rides along
-    // (455 items on 384 threads were two rounds, the second of them nearly empty).
 #pragma unroll 1
-    for (int base = 0; base < items;) {
-      if (tid == 0) MLA_TRACE(10, 5u + uint32_t(base / kThreads), 0);
-      if (items - base > kThreads) {
-        round(base, std::integral_constant<int, 2>{});
-        base += 2 * kThreads;
-      } else {
-        round(base, std::integral_constant<int, 1>{});
-        base += kThreads;
+      for (; i < ns; ++i) {
+        const uint32_t u0 = lds_u32(src), u1 = lds_u32(src + 16u);
+        const float2 wv = lds_f32x2(wcol);
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u0)), f1 = __half22float2(*reinterpret_cast<const __half2*>(&u1));
+        a00 += wv.x * f0.x;
+        a01 += wv.y * f0.y;
+        a10 += wv.x * f1.x;
+        a11 += wv.y * f1.y;
+        src += share_bytes;
+        wcol += kTailLseBytes;
       }
-      if (tid == 0) MLA_TRACE(10, 5u + uint32_t(base / kThreads), 1);
+      const float2 inv = lds_f32x2(c.smem + kOffTailInv + 4u * uint32_t(head));
+      const size_t idx = (row0 + head) * kLatent + dim;
+      if (head < heads_here) store_out_pair(p.out, p.out_dtype, idx, a00 * inv.x, a10 * inv.x);
+      if (head + 1 < heads_here) store_out_pair(p.out, p.out_dtype, idx + kLatent, a01 * inv.y, a11 * inv.y);
     }
     if (tid == 0) MLA_TRACE(3, 1u, 5);
   }
