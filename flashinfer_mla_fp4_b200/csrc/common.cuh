@@ -100,10 +100,16 @@ MLA_HD int num_groups(int q_len, int num_heads) {
   return q_len * ((num_heads + kGroupHeads - 1) / kGroupHeads);
 }
 
-MLA_HD int64_t cta_lo(int64_t Tt, int n, int i) { return (Tt * int64_t(i)) / n; }
+// (32-bit division when the operands fit, which they do up to millions of tokens: a 64-bit division is a subroutine of
+// a hundred instructions, and these run in the prologue of every CTA.)
+MLA_HD int64_t cta_lo(int64_t Tt, int n, int i) {
+  if (Tt * int64_t(n) < (int64_t(1) << 32)) return int64_t((uint32_t(Tt) * uint32_t(i)) / uint32_t(n));
+  return (Tt * int64_t(i)) / n;
+}
 
 // CTA that owns flat tile f: the largest i with cta_lo(i) <= f.
 MLA_HD int cta_of_tile(int64_t Tt, int n, int64_t f) {
+  if ((Tt + 1) * int64_t(n) + Tt < (int64_t(1) << 32)) return int((uint32_t(f + 1) * uint32_t(n) + uint32_t(Tt) - 1u) / uint32_t(Tt)) - 1;
   return int(((f + 1) * n + Tt - 1) / Tt) - 1;
 }
 
@@ -234,8 +240,13 @@ __device__ __forceinline__ Walker make_walker(const int32_t* seq_lens, int batch
   w.hi = cta_lo(Tt, n, cta + 1);
   w.b = 0; w.g = groups; w.t = 0;
   if (T > 0 && w.f < w.hi) {
-    w.g = int(w.f / T);
-    warp_locate(seq_lens, batch, cap, w.f % T, w.b, w.t);
+    if (Tt < (int64_t(1) << 32)) {
+      w.g = int(uint32_t(w.f) / uint32_t(T));
+      warp_locate(seq_lens, batch, cap, int64_t(uint32_t(w.f) - uint32_t(w.g) * uint32_t(T)), w.b, w.t);
+    } else {
+      w.g = int(w.f / T);
+      warp_locate(seq_lens, batch, cap, w.f % T, w.b, w.t);
+    }
   }
   return w;
 }

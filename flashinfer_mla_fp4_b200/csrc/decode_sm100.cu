@@ -732,9 +732,10 @@ __device__ __forceinline__ void store_p(const SoftmaxTile& t, const PRegs& pr) {
 
 // Refresh the per-head reference: column max of y = x*c + log2(scale_t) over the tile's tokens,
 // m = max(m_old, colmax - shift); f = 2^(m_old - m) (0 when there was no reference yet).
+template <bool kSoftCap>
 __device__ __noinline__ void refresh_reference(const Ctx& c, uint32_t t_lat, uint32_t t_rope, float sc, bool valid,
                                                float cscale, float lg, bool have_m, int tid, float cap) {
-  const float rcap = cap > 0.f ? 1.f / cap : 0.f;
+  const float rcap = kSoftCap ? 1.f / cap : 0.f;
   const int warp = tid >> 5, lane = tid & 31;
   const int quarter = warp & 3, half = warp >> 2;  // t_lat / t_rope already point at this warp's 32 columns
   const uint32_t wred = c.smem + kOffWmax;
@@ -748,7 +749,7 @@ __device__ __noinline__ void refresh_reference(const Ctx& c, uint32_t t_lat, uin
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       float x = fmaf(__uint_as_float(a[i]), sc, __uint_as_float(b[i]));
-      if (cap > 0.f) x = cap * tanh_approx(x * rcap);
+      if (kSoftCap) x = cap * tanh_approx(x * rcap);
       const float y = fmaf(x, cscale, lg);
       const float r = ptx::redux_max_f32(valid ? y : -INFINITY);
       if ((lane & 15) == i) mine = r;
@@ -790,7 +791,9 @@ __device__ __noinline__ void rescale_output(const Ctx& c, uint32_t tmem_lane, ui
 // Normalise O^T and write it to the output tensor (a segment that covers its request).  Runs once per segment, so
 // its instructions are fetched cold, and a workload of many short requests runs it between every few tiles: rolled
 // loops over (block, 16 heads), a small body (unrolled four times it slowed the variable-length workload by 10 %).
-template <int kOutDtype>  // one instantiation per output type: a call fetches the instructions of its own type only
+// One instantiation per output type and for a full group of 64 heads (no per-head predicates: half the instructions):
+// a call fetches the instructions of its own form only.
+template <int kOutDtype, bool kAllHeads>
 __device__ __noinline__ void write_final(const DecodeParams& p, const Ctx& c, uint32_t tmem_lane, int row, int half,
                                          int tid, int b, int g) {
   int qpos, head0;
@@ -816,7 +819,7 @@ __device__ __noinline__ void write_final(const DecodeParams& p, const Ctx& c, ui
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int i = 4 * q + e;
-          if (h0 + i < heads_here) {
+          if (kAllHeads || h0 + i < heads_here) {
             const float v = __uint_as_float(o[hh][i]) * fs[e];
             char* d = dst + size_t(i) * kLatent * esz;
             if (kOutDtype == MLA_FP4_OUT_BF16) *reinterpret_cast<__nv_bfloat16*>(d) = __float2bfloat16_rn(v);
@@ -934,7 +937,7 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       ptx::tc_fence_after();
 
       // first tile of a segment: set the reference before anything is exponentiated
-      if (first) refresh_reference(c, t.t_lat, t.t_rope, sc, t.valid, cscale, lg, false, tid, cap);
+      if (first) refresh_reference<kSoftCap>(c, t.t_lat, t.t_rope, sc, t.valid, cscale, lg, false, tid, cap);
       if (tid == 0) MLA_TRACE(0, it, 2);
 
       // Speculative pass with the current reference.  It stands unless some score beat the
@@ -946,7 +949,7 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       if (refresh) {
         // Refresh the reference.  (l + e_old) * f equals l * f + e_new, so the row sums only need
         // the factor; O^T is rescaled in TMEM; P' is recomputed with the new reference.
-        refresh_reference(c, t.t_lat, t.t_rope, sc, t.valid, cscale, lg, true, tid, cap);
+        refresh_reference<kSoftCap>(c, t.t_lat, t.t_rope, sc, t.valid, cscale, lg, true, tid, cap);
 #pragma unroll
         for (int q = 0; q < kHalfHeads / 4; ++q) {
           uint64_t f0, f1;
@@ -1012,9 +1015,15 @@ __device__ __forceinline__ void softmax_role(const DecodeParams& p, const Ctx& c
       if (tid == 0) MLA_TRACE(0, lit, 7);
       if (!c.misc->abort) {
         if (g.slot >= 0) write_partial(p, c, tmem_lane, row, half, tid, g.slot, slot_scale_v);
-        else if (p.out_dtype == MLA_FP4_OUT_BF16) write_final<MLA_FP4_OUT_BF16>(p, c, tmem_lane, row, half, tid, g.b, g.g);
-        else if (p.out_dtype == MLA_FP4_OUT_F32) write_final<MLA_FP4_OUT_F32>(p, c, tmem_lane, row, half, tid, g.b, g.g);
-        else write_final<MLA_FP4_OUT_E4M3>(p, c, tmem_lane, row, half, tid, g.b, g.g);
+        else if ((p.num_heads & (kGroupHeads - 1)) == 0) {  // every group is full
+          if (p.out_dtype == MLA_FP4_OUT_BF16) write_final<MLA_FP4_OUT_BF16, true>(p, c, tmem_lane, row, half, tid, g.b, g.g);
+          else if (p.out_dtype == MLA_FP4_OUT_F32) write_final<MLA_FP4_OUT_F32, true>(p, c, tmem_lane, row, half, tid, g.b, g.g);
+          else write_final<MLA_FP4_OUT_E4M3, true>(p, c, tmem_lane, row, half, tid, g.b, g.g);
+        } else {
+          if (p.out_dtype == MLA_FP4_OUT_BF16) write_final<MLA_FP4_OUT_BF16, false>(p, c, tmem_lane, row, half, tid, g.b, g.g);
+          else if (p.out_dtype == MLA_FP4_OUT_F32) write_final<MLA_FP4_OUT_F32, false>(p, c, tmem_lane, row, half, tid, g.b, g.g);
+          else write_final<MLA_FP4_OUT_E4M3, false>(p, c, tmem_lane, row, half, tid, g.b, g.g);
+        }
       }
       if (tid == 0) MLA_TRACE(0, lit, 4);
       ptx::tc_fence_before();
