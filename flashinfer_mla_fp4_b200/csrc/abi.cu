@@ -185,6 +185,7 @@ int mla_fp4_decode(const MlaFp4DecodeArgs* a) {
   c.batch = a->batch; c.q_len = a->q_len; c.num_heads = a->num_heads; c.groups = p.groups;
   c.num_ctas = num_ctas; c.out_dtype = a->out_dtype; c.pdl = (p.pdl && do_decode) ? 1 : 0;
   c.seq_cap = p.seq_cap;
+  c.sink = p.sink;
   e = mla::launch_combine(c, stream);
   if (e != cudaSuccess) return fail(MLA_FP4_ERR_CUDA, std::string("combine launch: ") + cudaGetErrorString(e));
   return MLA_FP4_OK;

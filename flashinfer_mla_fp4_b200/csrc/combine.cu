@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
   const int d_out = (tid & 3) * 4;        // output phase: 4 consecutive dims of the chunk
   const size_t out_idx = (row0 + h_out) * kLatent + size_t(dchunk) * kCombDims + d_out;
 
-  if (tiles == 0) {  // empty request: zeros and lse = -inf
+  if (tiles == 0) {  // empty request: zeros and lse = -inf (the sink's logit when there is a sink)
     if (h_out < heads_here) {
       if (p.out_dtype == MLA_FP4_OUT_BF16) {
         *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + out_idx) = make_uint2(0u, 0u);
@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
         *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(p.out) + out_idx) = 0u;
       }
     }
-    if (dchunk == 0 && p.lse && tid < heads_here) p.lse[row0 + tid] = -INFINITY;
+    if (dchunk == 0 && p.lse && tid < heads_here) p.lse[row0 + tid] = p.sink ? __ldg(p.sink + head0 + tid) * kLog2e : -INFINITY;
     return;
   }
   const int64_t start = int64_t(g) * T + s_start;

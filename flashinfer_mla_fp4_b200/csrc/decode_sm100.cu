@@ -1141,7 +1141,8 @@ __device__ __noinline__ void zero_empty_requests(const DecodeParams& p, int tid)
     const uint32_t n16 = uint32_t(heads_here) * kLatent * esz / 16u;
 #pragma unroll 1
     for (uint32_t i = tid; i < n16; i += kThreads) dst[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (p.lse && tid < heads_here) p.lse[row0 + tid] = -INFINITY;
+    // no token at all: with a sink the softmax is over the sink alone (zero value row), whose logit is the LSE
+    if (p.lse && tid < heads_here) p.lse[row0 + tid] = p.sink ? __ldg(p.sink + head0 + tid) * kLog2e : -INFINITY;
   }
 }
 

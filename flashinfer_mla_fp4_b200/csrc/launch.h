@@ -37,6 +37,7 @@ struct CombineParams {
   float* lse;
   int32_t batch, q_len, num_heads, groups, num_ctas, out_dtype, pdl;
   int32_t seq_cap;  // as in DecodeParams
+  const float* sink;  // as in DecodeParams: gives the LSE of a request without tokens
 };
 
 // Exchange block of the context-parallel exchange (cp_exchange.cu): a step word per CTA, then the gather area: two

@@ -195,7 +195,7 @@ def mla_decode(
     singleton dim 1); kv_cache_sf f32 [P, ps, 1]; block_tables int [B, max_pages];
     seq_lens int [B].  Every query position attends to all seq_len tokens.
     Returns (out f32 [B, q_len, H, 512], lse2 f32 [B, q_len, H]); a request with
-    seq_len == 0 gives zeros and lse2 = -inf.
+    seq_len == 0 gives zeros and lse2 = -inf (with a sink: zeros and the sink's logit in base 2).
     """
     if kv_cache.dim() == 4:
         kv_cache = kv_cache.squeeze(1)
@@ -215,6 +215,8 @@ def mla_decode(
     for b in range(B):
         n = int(seq_lens[b])
         if n <= 0:
+            if sink is not None:  # the softmax is over the sink alone: zero output, LSE = the sink's logit
+                lse2[b] = (sink.detach().cpu().float().reshape(1, H) * LOG2_E).expand(q_len, H)
             continue
         n_pages = (n + page_size - 1) // page_size
         pages = block_tables[b, :n_pages].to(torch.long)

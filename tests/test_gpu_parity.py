@@ -150,8 +150,10 @@ def test_attention_variants(which, kernel):
     from flashinfer_mla_fp4_b200 import AttentionWithSink, SoftCappingAttention, synth
 
     dev = _dev()
-    for heads, q_len, lens, seed in ((64, 1, [9000, 130, 1, 4100], 21), (16, 2, [700, 64], 22), (128, 1, [20000], 23)):
-        case = synth.build_case(f"variant_{which}", lens, heads, 64, q_len=q_len, seed=seed, device=dev)
+    for heads, q_len, lens, seed in ((64, 1, [9000, 130, 0, 1, 4100], 21), (16, 2, [700, 64], 22), (128, 1, [20000], 23)):
+        case = synth.build_case(f"variant_{which}", [max(n, 1) for n in lens], heads, 64, q_len=q_len, seed=seed, device=dev)
+        case.seq_lens = torch.tensor(lens, dtype=torch.int32, device=dev)  # a request without tokens: the sink alone
+        case.seq_lens_host = lens
         g = torch.Generator().manual_seed(seed)
         # sinks from well below to well above the typical score, so that some heads are dominated by it
         sink = (torch.rand(heads, generator=g) * 12.0 - 4.0).to(dev)
