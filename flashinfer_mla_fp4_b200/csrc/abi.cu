@@ -69,6 +69,9 @@ int mla_fp4_plan_partition(const int32_t* seq_lens_host, int32_t batch, int32_t 
   int64_t T = 0;
   for (int b = 0; b < batch; ++b) T += mla::vtiles_of(seq_lens_host[b]);
   const int64_t Tt = T * groups;
+  int max_tiles = 0;
+  for (int b = 0; b < batch; ++b) max_tiles = std::max(max_tiles, mla::tiles_of(seq_lens_host[b]));
+  const bool whole = mla::whole_requests(max_tiles, int64_t(batch) * groups, num_ctas);
   int count = 0;
   for (int i = 0; i < num_ctas; ++i) {
     mla::Walker w;
@@ -76,7 +79,14 @@ int mla_fp4_plan_partition(const int32_t* seq_lens_host, int32_t batch, int32_t 
     w.f = mla::cta_lo(Tt, num_ctas, i);
     w.hi = mla::cta_lo(Tt, num_ctas, i + 1);
     w.b = 0; w.g = groups; w.t = 0;
-    if (T > 0 && w.f < w.hi) {
+    if (whole) {  // short requests: (request, head group) pair i, whole, on CTA i
+      w.f = 0; w.hi = 0;
+      if (i < batch * groups) {
+        w.g = i / batch;
+        w.b = i - w.g * batch;
+        w.hi = mla::vtiles_of(seq_lens_host[w.b]);
+      }
+    } else if (T > 0 && w.f < w.hi) {
       w.g = int(w.f / T);
       int64_t r = w.f % T, run = 0;
       for (int b = 0; b < batch; ++b) {

@@ -26,17 +26,19 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
   __shared__ int n_slots;
   __shared__ int64_t s_T;
   __shared__ int64_t s_start;
+  __shared__ int s_whole;
 
   const int v = blockIdx.y;
   const int dchunk = blockIdx.x;
   const int g = v / p.batch, b = v % p.batch;
   const int tid = threadIdx.x;
   if (tid < 32) {  // seq_lens is an input of the step, not a product of the decode kernel
-    int64_t T = warp_total_tiles(p.seq_lens, p.batch, p.seq_cap);
+    int mxt;
+    int64_t T = warp_total_tiles(p.seq_lens, p.batch, p.seq_cap, &mxt);
     int64_t run = 0;
     for (int i = tid; i < b; i += 32) run += vtiles_of(capped_len(p.seq_lens, i, p.seq_cap));
     for (int o = 16; o > 0; o >>= 1) run += __shfl_xor_sync(0xffffffffu, run, o);
-    if (tid == 0) { s_T = T; s_start = run; }
+    if (tid == 0) { s_T = T; s_start = run; s_whole = whole_requests(mxt, int64_t(p.batch) * p.groups, p.num_ctas) ? 1 : 0; }
   }
   __syncthreads();
   const int64_t T = s_T;
@@ -65,7 +67,7 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
   }
   const int64_t start = int64_t(g) * T + s_start;
   const Span sp = span_of(Tt, p.num_ctas, start + kPhantom, tiles - kPhantom);  // CTAs that hold its real tiles
-  if (!sp.split) return;  // the decode kernel wrote the final output itself
+  if (!sp.split || s_whole) return;  // the decode kernel wrote the final output itself
 
   // slots of this request, computed once (the partition arithmetic is 64-bit division heavy)
   if (tid < 32) {

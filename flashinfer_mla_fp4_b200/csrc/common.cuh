@@ -96,6 +96,13 @@ MLA_HD int capped_len(const int32_t* seq_lens, int b, int cap) {
 constexpr int kPhantom = MLA_FP4_PHANTOM_TILES;  // measured: 2 and 3 are equally good, 1 and 4 worse
 MLA_HD int vtiles_of(int seq_len) { return seq_len > 0 ? tiles_of(seq_len) + kPhantom : 0; }
 
+// Short requests are not split.  When no request has more than kWholeTiles tiles and there are no more (request, head
+// group) pairs than CTAs, pair v is decoded whole by CTA v: walking four tiles costs less than writing a partial,
+// publishing it and merging (about three to four tile times), which is all a split would buy.  Every user of the
+// partition (the decode kernels, the combine kernel, the host planner) takes the same decision from the same inputs.
+constexpr int kWholeTiles = 4;
+MLA_HD bool whole_requests(int max_real_tiles, int64_t pairs, int n) { return max_real_tiles <= kWholeTiles && pairs <= int64_t(n); }
+
 MLA_HD int num_groups(int q_len, int num_heads) {
   return q_len * ((num_heads + kGroupHeads - 1) / kGroupHeads);
 }
@@ -195,11 +202,20 @@ MLA_HD void group_coords(int g, int num_heads, int& qpos, int& head0) {
 
 #ifdef __CUDACC__
 // Warp-cooperative: total tile count of the batch. All 32 lanes must call; all get the result.
-__device__ __forceinline__ int64_t warp_total_tiles(const int32_t* seq_lens, int batch, int cap) {
+__device__ __forceinline__ int64_t warp_total_tiles(const int32_t* seq_lens, int batch, int cap, int* max_real_tiles = nullptr) {
   int lane = threadIdx.x & 31;
   int64_t acc = 0;
-  for (int i = lane; i < batch; i += 32) acc += vtiles_of(capped_len(seq_lens, i, cap));
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  int mx = 0;
+  for (int i = lane; i < batch; i += 32) {
+    const int v = vtiles_of(capped_len(seq_lens, i, cap));
+    acc += v;
+    mx = max(mx, v);
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if (max_real_tiles) *max_real_tiles = mx > 0 ? mx - kPhantom : 0;  // of any request
   return acc;
 }
 
@@ -233,9 +249,19 @@ __device__ __forceinline__ void warp_locate(const int32_t* seq_lens, int batch, 
 __device__ __forceinline__ Walker make_walker(const int32_t* seq_lens, int batch, int cap, int groups, int cta, int n) {
   Walker w;
   w.seq_lens = seq_lens; w.cap = cap; w.batch = batch; w.groups = groups; w.cta = cta; w.first = true;
-  int64_t T = warp_total_tiles(seq_lens, batch, cap);
+  int max_tiles;
+  int64_t T = warp_total_tiles(seq_lens, batch, cap, &max_tiles);
   int64_t Tt = T * groups;
   w.Tt = Tt;
+  if (whole_requests(max_tiles, int64_t(batch) * groups, n)) {  // CTA v: pair v, whole
+    w.f = 0; w.hi = 0; w.b = 0; w.g = groups; w.t = 0;
+    if (cta < batch * groups) {
+      w.g = cta / batch;
+      w.b = cta - w.g * batch;
+      w.hi = vtiles_of(capped_len(seq_lens, w.b, cap));
+    }
+    return w;
+  }
   w.f = cta_lo(Tt, n, cta);
   w.hi = cta_lo(Tt, n, cta + 1);
   w.b = 0; w.g = groups; w.t = 0;

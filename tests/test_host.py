@@ -51,6 +51,8 @@ def test_abi_rejects_bad_arguments_without_a_gpu():
         ([1, 0, 129, 128, 127, 5000, 0, 3], 1, 128, 7),
         ([0, 0], 1, 64, 4),
         ([77], 1, 64, 1),
+        ([512, 1, 0, 300, 129], 2, 128, 148),
+        ([512, 513], 1, 64, 148),
         (list(range(1, 400, 7)), 1, 64, 148),
     ],
 )
@@ -78,6 +80,12 @@ def test_partition_is_a_partition(seq_lens, q_len, heads, ctas):
 
     P = _cabi.PHANTOM_TILES
     flat = groups * sum(planner.tiles_of(n) + P for n in seq_lens if n > 0)
+    # short requests are not split: when none has more than four tiles and there are no more (request, group) pairs
+    # than CTAs, pair v is decoded whole by CTA v
+    if max((planner.tiles_of(n) for n in seq_lens), default=0) <= 4 and groups * len(seq_lens) <= ctas:
+        assert all(s.slot == -1 for s in segs)
+        assert all(s.cta == s.group * len(seq_lens) + s.request for s in segs)
+        return
     for i in range(ctas):
         ss = per_cta.get(i, [])
         real = sum(s.tile_end - s.tile_begin for s in ss)
