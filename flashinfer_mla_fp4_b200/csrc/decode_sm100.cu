@@ -128,6 +128,7 @@ struct Misc {
   // the merge plan (plan_merge)
   int n_slots, n_part, rank, merge_k;
   int unit0, unit1;  // this CTA's share of every slot of the merged request: units [unit0, unit1) of 32 bytes
+  int32_t gen;       // generation of this decode step, fetched once per CTA
 };
 static_assert(sizeof(Misc) <= 256, "misc area");
 
@@ -1383,6 +1384,9 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
                             const __grid_constant__ CUtensorMap map_q_rope, const __grid_constant__ CUtensorMap map_rope,
                             const __grid_constant__ CUtensorMap map_lat) {
   extern __shared__ uint8_t smem_raw[];
+#ifdef MLA_FP4_TRACE
+  const long long t_entry = clock64();
+#endif
   Ctx c;
   {
     uint32_t raw = ptx::smem_u32(smem_raw);
@@ -1430,25 +1434,43 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
   if (p.pdl_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
   // The generation of this step: one more than that of the last completed step.  No CTA of this step
   // can have advanced it yet (that takes every CTA of the grid to have finished).
-  c.gen = p.fused_merge ? ld_acquire(ws_generation(p.workspace)) + 1 : 0;
+  // One thread of a warp that has nothing else to do here fetches it: an acquire load holds back the loads behind it,
+  // and the warp that walks the partition (sequence lengths, a cold DRAM round trip) should not queue behind that.
 #ifdef MLA_FP4_TRACE
-  c.trace_cta = (p.status && p.status[7] >= 0 && p.status[7] < int(gridDim.x) && p.status[7] != 0) ? p.status[7] : int(gridDim.x) - 1;
+  long long t_pro[4] = {0, 0, 0, 0};
+  t_pro[0] = clock64();
 #endif
+  if (warp == kWarpPV && (tid & 31) == 0) c.misc->gen = p.fused_merge ? ld_acquire(ws_generation(p.workspace)) + 1 : 0;
   if (warp == 0) {
     Walker w = make_walker(p.seq_lens, p.batch, p.seq_cap, p.groups, blockIdx.x, gridDim.x);
+#ifdef MLA_FP4_TRACE
+    t_pro[1] = clock64();
+#endif
     if (tid == 0) {
       c.misc->walker = w;
       c.misc->abort = 0;
       c.misc->n_merge = 0;
       stage_segments(c);
     }
+#ifdef MLA_FP4_TRACE
+    t_pro[2] = clock64();
+#endif
   }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
+  c.gen = c.misc->gen;
+#ifdef MLA_FP4_TRACE
+  c.trace_cta = (p.status && p.status[7] >= 0 && p.status[7] < int(gridDim.x) && p.status[7] != 0) ? p.status[7] : int(gridDim.x) - 1;
+  if (tid == 0 && int(blockIdx.x) == c.trace_cta && c.status) {
+    long long* tr = reinterpret_cast<long long*>(c.status + 8) + (11 * 16 + 0) * 8;
+    tr[1] = t_pro[0]; tr[2] = t_pro[1]; tr[3] = t_pro[2]; tr[4] = clock64();
+  }
+#endif
   const uint32_t tmem = c.misc->tmem_base;
   if (tid == 0) MLA_TRACE(3, 0u, 0);
 #ifdef MLA_FP4_TRACE
+  if (tid == 0 && int(blockIdx.x) == c.trace_cta && c.status) reinterpret_cast<long long*>(c.status + 8)[(11 * 16 + 0) * 8 + 0] = t_entry;
   auto gtimer = [] { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
   unsigned long long* cta_times = p.status ? reinterpret_cast<unsigned long long*>(p.status + 8) + 12 * 16 * 8 + 4 * blockIdx.x : nullptr;
   if (tid == 0 && cta_times) cta_times[0] = gtimer();
