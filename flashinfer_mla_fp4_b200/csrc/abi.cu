@@ -68,7 +68,8 @@ int mla_fp4_plan_partition(const int32_t* seq_lens_host, int32_t batch, int32_t 
   const int groups = mla::num_groups(q_len, num_heads);
   int64_t T = 0;
   for (int b = 0; b < batch; ++b) T += mla::vtiles_of(seq_lens_host[b]);
-  const int64_t Tt = T * groups;
+  if (!mla::partition_fits(T * groups, num_ctas)) return fail(MLA_FP4_ERR_UNSUPPORTED, "the work partition is computed in 32 bits: too many tiles x CTAs");
+  const mla::flat_t Tt = mla::flat_t(T * groups);
   int max_tiles = 0;
   for (int b = 0; b < batch; ++b) max_tiles = std::max(max_tiles, mla::tiles_of(seq_lens_host[b]));
   const bool whole = mla::whole_requests(max_tiles, int64_t(batch) * groups, num_ctas);
@@ -88,7 +89,7 @@ int mla_fp4_plan_partition(const int32_t* seq_lens_host, int32_t batch, int32_t 
       }
     } else if (T > 0 && w.f < w.hi) {
       w.g = int(w.f / T);
-      int64_t r = w.f % T, run = 0;
+      int64_t r = w.f % T, run = 0;  // (host: plain 64-bit arithmetic, same values)
       for (int b = 0; b < batch; ++b) {
         int tb = mla::vtiles_of(seq_lens_host[b]);
         if (r < run + tb) { w.b = b; w.t = int(r - run); break; }

@@ -24,8 +24,8 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
   __shared__ float tile[kGroupHeads][kCombDims + 1];
   __shared__ int slot_list[kMaxCombineSlots];
   __shared__ int n_slots;
-  __shared__ int64_t s_T;
-  __shared__ int64_t s_start;
+  __shared__ flat_t s_T;
+  __shared__ flat_t s_start;
   __shared__ int s_whole;
 
   const int v = blockIdx.y;
@@ -34,15 +34,17 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
   const int tid = threadIdx.x;
   if (tid < 32) {  // seq_lens is an input of the step, not a product of the decode kernel
     int mxt;
-    int64_t T = warp_total_tiles(p.seq_lens, p.batch, p.seq_cap, &mxt);
-    int64_t run = 0;
+    const int64_t T64 = warp_total_tiles(p.seq_lens, p.batch, p.seq_cap, &mxt);
+    const flat_t T = partition_fits(T64 * p.groups, p.num_ctas) ? flat_t(T64) : -1;  // -1: the decode kernel refused the step
+    flat_t run = 0;
     for (int i = tid; i < b; i += 32) run += vtiles_of(capped_len(p.seq_lens, i, p.seq_cap));
     for (int o = 16; o > 0; o >>= 1) run += __shfl_xor_sync(0xffffffffu, run, o);
     if (tid == 0) { s_T = T; s_start = run; s_whole = whole_requests(mxt, int64_t(p.batch) * p.groups, p.num_ctas) ? 1 : 0; }
   }
   __syncthreads();
-  const int64_t T = s_T;
-  const int64_t Tt = T * p.groups;
+  const flat_t T = s_T;
+  if (T < 0) return;
+  const flat_t Tt = T * p.groups;
   const int tiles = vtiles_of(capped_len(p.seq_lens, b, p.seq_cap));  // of the flat space: phantom tiles included
   int qpos, head0;
   group_coords(g, p.num_heads, qpos, head0);
@@ -65,7 +67,7 @@ __global__ void __launch_bounds__(kCombThreads) combine_kernel(CombineParams p) 
     if (dchunk == 0 && p.lse && tid < heads_here) p.lse[row0 + tid] = p.sink ? __ldg(p.sink + head0 + tid) * kLog2e : -INFINITY;
     return;
   }
-  const int64_t start = int64_t(g) * T + s_start;
+  const flat_t start = flat_t(g) * T + s_start;
   const Span sp = span_of(Tt, p.num_ctas, start + kPhantom, tiles - kPhantom);  // CTAs that hold its real tiles
   if (!sp.split || s_whole) return;  // the decode kernel wrote the final output itself
 

@@ -107,24 +107,24 @@ MLA_HD int num_groups(int q_len, int num_heads) {
   return q_len * ((num_heads + kGroupHeads - 1) / kGroupHeads);
 }
 
-// (32-bit division when the operands fit, which they do up to millions of tokens: a 64-bit division is a subroutine of
-// a hundred instructions, and these run in the prologue of every CTA.)
-MLA_HD int64_t cta_lo(int64_t Tt, int n, int i) {
-  if (Tt * int64_t(n) < (int64_t(1) << 32)) return int64_t((uint32_t(Tt) * uint32_t(i)) / uint32_t(n));
-  return (Tt * int64_t(i)) / n;
-}
+// Positions in the flat tile space are 32-bit: a 64-bit division is a subroutine of a hundred instructions and these
+// run in the prologue of every CTA, where every instruction is fetched cold.  Valid while (Tt + 1) * (n + 1) < 2^32
+// (hundreds of millions of tokens); partition_fits says so and the kernels refuse a launch beyond it.
+typedef int32_t flat_t;
+MLA_HD bool partition_fits(int64_t Tt, int n) { return (Tt + 1) * int64_t(n + 1) < (int64_t(1) << 32); }
+
+MLA_HD flat_t cta_lo(flat_t Tt, int n, int i) { return flat_t((uint32_t(Tt) * uint32_t(i)) / uint32_t(n)); }
 
 // CTA that owns flat tile f: the largest i with cta_lo(i) <= f.
-MLA_HD int cta_of_tile(int64_t Tt, int n, int64_t f) {
-  if ((Tt + 1) * int64_t(n) + Tt < (int64_t(1) << 32)) return int((uint32_t(f + 1) * uint32_t(n) + uint32_t(Tt) - 1u) / uint32_t(Tt)) - 1;
-  return int(((f + 1) * n + Tt - 1) / Tt) - 1;
+MLA_HD int cta_of_tile(flat_t Tt, int n, flat_t f) {
+  return int((uint32_t(f + 1) * uint32_t(n) + uint32_t(Tt) - 1u) / uint32_t(Tt)) - 1;
 }
 
 // Does CTA i write a partial of the split request whose flat range (phantom tiles first) is
 // [start, start + vtiles)?  Its range must hold at least one of the request's real tiles.
-MLA_HD bool cta_writes(int64_t Tt, int n, int i, int64_t start, int vtiles) {
-  const int64_t lo = cta_lo(Tt, n, i), hi = cta_lo(Tt, n, i + 1);
-  const int64_t a = lo > start + kPhantom ? lo : start + kPhantom, b = hi < start + vtiles ? hi : start + vtiles;
+MLA_HD bool cta_writes(flat_t Tt, int n, int i, flat_t start, int vtiles) {
+  const flat_t lo = cta_lo(Tt, n, i), hi = cta_lo(Tt, n, i + 1);
+  const flat_t a = lo > start + kPhantom ? lo : start + kPhantom, b = hi < start + vtiles ? hi : start + vtiles;
   return a < b;
 }
 
@@ -135,7 +135,7 @@ struct Span {
   int cta_first, cta_last;  // inclusive
   bool split;               // more than one CTA
 };
-MLA_HD Span span_of(int64_t Tt, int n, int64_t start, int tiles) {
+MLA_HD Span span_of(flat_t Tt, int n, flat_t start, int tiles) {
   Span s;
   s.cta_first = cta_of_tile(Tt, n, start);
   s.cta_last = cta_of_tile(Tt, n, start + tiles - 1);
@@ -143,7 +143,7 @@ MLA_HD Span span_of(int64_t Tt, int n, int64_t start, int tiles) {
   return s;
 }
 // Slot written by CTA i for a split request whose flat start is `start`.
-MLA_HD int slot_in_span(int64_t Tt, int n, int i, int64_t start) {
+MLA_HD int slot_in_span(flat_t Tt, int n, int i, flat_t start) {
   return slot_of(i, cta_lo(Tt, n, i) >= start);
 }
 
@@ -161,11 +161,11 @@ struct Walker {
   const int32_t* seq_lens;
   int cap;         // most tokens a request may have (see capped_len)
   int batch, groups;
-  int64_t f, hi;   // current flat tile, end of the CTA's range
+  flat_t f, hi;    // current flat tile, end of the CTA's range
   int b, g, t;     // current request, group, tile inside the request
   bool first;      // next segment is the first of this CTA
   int cta;
-  int64_t Tt;      // size of the flat tile space (device walkers only)
+  flat_t Tt;       // size of the flat tile space (device walkers only)
 
   MLA_HD bool next(Segment& s) {
     while (f < hi) {
@@ -177,7 +177,7 @@ struct Walker {
         if (++b == batch) { b = 0; ++g; }
         continue;
       }
-      int64_t room = hi - f;
+      flat_t room = hi - f;
       int end = (tb - t) <= room ? tb : t + int(room);
       const bool whole = t <= kPhantom && end == tb;  // all real tiles of the request
       const int real_begin = (t > kPhantom ? t : kPhantom) - kPhantom, real_end = end - kPhantom;
@@ -220,23 +220,23 @@ __device__ __forceinline__ int64_t warp_total_tiles(const int32_t* seq_lens, int
 }
 
 // Warp-cooperative: locate flat tile r (0 <= r < T, within one group) -> request b and tile t.
-__device__ __forceinline__ void warp_locate(const int32_t* seq_lens, int batch, int cap, int64_t r, int& b_out, int& t_out) {
+__device__ __forceinline__ void warp_locate(const int32_t* seq_lens, int batch, int cap, flat_t r, int& b_out, int& t_out) {
   int lane = threadIdx.x & 31;
-  int64_t run = 0;
+  flat_t run = 0;
   b_out = batch; t_out = 0;
   for (int base = 0; base < batch; base += 32) {
     int i = base + lane;
-    int64_t v = i < batch ? vtiles_of(capped_len(seq_lens, i, cap)) : 0;
-    int64_t inc = v;
+    flat_t v = i < batch ? vtiles_of(capped_len(seq_lens, i, cap)) : 0;
+    flat_t inc = v;
     for (int o = 1; o < 32; o <<= 1) {
-      int64_t u = __shfl_up_sync(0xffffffffu, inc, o);
+      flat_t u = __shfl_up_sync(0xffffffffu, inc, o);
       if (lane >= o) inc += u;
     }
-    int64_t tot = __shfl_sync(0xffffffffu, inc, 31);
+    flat_t tot = __shfl_sync(0xffffffffu, inc, 31);
     if (r < run + tot) {
       unsigned m = __ballot_sync(0xffffffffu, run + inc > r);
       int l = __ffs(m) - 1;
-      int64_t exc = __shfl_sync(0xffffffffu, inc - v, l);
+      flat_t exc = __shfl_sync(0xffffffffu, inc - v, l);
       b_out = base + l;
       t_out = int(r - (run + exc));
       return;
@@ -250,11 +250,15 @@ __device__ __forceinline__ Walker make_walker(const int32_t* seq_lens, int batch
   Walker w;
   w.seq_lens = seq_lens; w.cap = cap; w.batch = batch; w.groups = groups; w.cta = cta; w.first = true;
   int max_tiles;
-  int64_t T = warp_total_tiles(seq_lens, batch, cap, &max_tiles);
-  int64_t Tt = T * groups;
+  const int64_t T64 = warp_total_tiles(seq_lens, batch, cap, &max_tiles);
+  w.f = 0; w.hi = 0; w.b = 0; w.g = groups; w.t = 0; w.Tt = 0;
+  if (!partition_fits(T64 * groups, n)) {  // never with real caches; the caller reports it
+    w.Tt = -1;
+    return w;
+  }
+  const flat_t T = flat_t(T64), Tt = T * groups;
   w.Tt = Tt;
   if (whole_requests(max_tiles, int64_t(batch) * groups, n)) {  // CTA v: pair v, whole
-    w.f = 0; w.hi = 0; w.b = 0; w.g = groups; w.t = 0;
     if (cta < batch * groups) {
       w.g = cta / batch;
       w.b = cta - w.g * batch;
@@ -264,15 +268,9 @@ __device__ __forceinline__ Walker make_walker(const int32_t* seq_lens, int batch
   }
   w.f = cta_lo(Tt, n, cta);
   w.hi = cta_lo(Tt, n, cta + 1);
-  w.b = 0; w.g = groups; w.t = 0;
   if (T > 0 && w.f < w.hi) {
-    if (Tt < (int64_t(1) << 32)) {
-      w.g = int(uint32_t(w.f) / uint32_t(T));
-      warp_locate(seq_lens, batch, cap, int64_t(uint32_t(w.f) - uint32_t(w.g) * uint32_t(T)), w.b, w.t);
-    } else {
-      w.g = int(w.f / T);
-      warp_locate(seq_lens, batch, cap, w.f % T, w.b, w.t);
-    }
+    w.g = int(uint32_t(w.f) / uint32_t(T));
+    warp_locate(seq_lens, batch, cap, w.f - flat_t(w.g) * T, w.b, w.t);
   }
   return w;
 }

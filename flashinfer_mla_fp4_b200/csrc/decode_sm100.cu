@@ -115,7 +115,7 @@ struct MergeReq {
   int b, g, tiles;
   int counter;    // the first CTA of the request's span
   int slot;       // the slot this CTA wrote (even: the segment was the CTA's first)
-  int64_t start;  // flat tile index of the request's first tile
+  flat_t start;   // flat tile index of the request's first tile
 };
 struct Misc {
   uint32_t tmem_base;
@@ -1080,7 +1080,7 @@ __device__ __noinline__ void stage_segments(const Ctx& c) {
       m.b = s.b;
       m.g = s.g;
       m.tiles = vtiles_of(s.seq_len);       // of the flat space: phantom tiles included
-      m.start = w.f - int64_t(w.t);         // w.f and w.t are the flat and the in-request position just past this segment
+      m.start = w.f - flat_t(w.t);          // w.f and w.t are the flat and the in-request position just past this segment
       m.counter = cta_of_tile(w.Tt, int(gridDim.x), m.start);
       m.slot = s.slot;
     }
@@ -1165,23 +1165,15 @@ __device__ __noinline__ void plan_merge(const Ctx& c, int lane) {
     return;
   }
   const MergeReq m = misc->merge[k];
-  const int64_t Tt = misc->walker.Tt;
-  const int64_t end = m.start + m.tiles;
-  const bool small = Tt * n < (int64_t(1) << 32);  // the usual case: 32-bit division
+  const flat_t Tt = misc->walker.Tt;
+  const flat_t end = m.start + m.tiles;
   int cnt = 0, part = 0, rank = 0;
 #pragma unroll 1
   for (int base = m.counter & ~31; base < n; base += 32) {
     const int i = base + lane;
     bool writer = false, merger = false;
     if (i < n && i >= m.counter) {
-      int64_t lo, nlo;
-      if (small) {
-        lo = int64_t(uint32_t(Tt) * uint32_t(i) / uint32_t(n));
-        nlo = int64_t(uint32_t(Tt) * uint32_t(i + 1) / uint32_t(n));
-      } else {
-        lo = cta_lo(Tt, n, i);
-        nlo = cta_lo(Tt, n, i + 1);
-      }
+      const flat_t lo = cta_lo(Tt, n, i), nlo = cta_lo(Tt, n, i + 1);
       writer = lo < end && nlo > lo && nlo > m.start + kPhantom;  // holds at least one real tile of the request
       merger = writer && lo >= m.start;
     }
@@ -1450,7 +1442,13 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
       c.misc->walker = w;
       c.misc->abort = 0;
       c.misc->n_merge = 0;
-      stage_segments(c);
+      if (w.Tt < 0) {  // the flat tile space does not fit 32 bits: nothing is decoded, the status says why
+        c.misc->nseg = 0;
+        c.misc->more = 0;
+        if (p.status) atomicCAS(p.status, 0, MLA_FP4_ERR_UNSUPPORTED);
+      } else {
+        stage_segments(c);
+      }
     }
 #ifdef MLA_FP4_TRACE
     t_pro[2] = clock64();
