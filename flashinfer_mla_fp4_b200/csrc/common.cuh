@@ -80,7 +80,7 @@ MLA_HD int out_elem_bytes(int out_dtype) { return out_dtype == MLA_FP4_OUT_F32 ?
 // decode kernel by the CTAs that wrote them (or, in the two-kernel mode, by the combine kernel).
 // ----------------------------------------------------------------------------------------------
 
-MLA_HD int tiles_of(int seq_len) { return seq_len > 0 ? (seq_len + kTile - 1) / kTile : 0; }
+MLA_HD int tiles_of(int seq_len) { return seq_len > 0 ? (seq_len - 1) / kTile + 1 : 0; }  // no overflow near INT_MAX
 
 // A sequence length as the kernels use it: never more than `cap` tokens (the tokens a block-table row can
 // address), so a garbage seq_lens entry cannot walk a kernel past the row.

@@ -245,3 +245,12 @@ def test_partition_charges_phantom_tiles_for_a_request_start():
     assert [s.cta for s in segs] == list(range(P, 10 + P))
     assert [(s.tile_begin, s.tile_end) for s in segs] == [(t, t + 1) for t in range(10)]
     assert segs[0].slot == 2 * P and all(s.slot == 2 * s.cta for s in segs)
+
+
+def test_partition_beyond_32_bits_is_refused():
+    """Flat tile positions are 32-bit: a tile space x CTA count that does not fit is refused, not wrapped round."""
+    from flashinfer_mla_fp4_b200 import planner
+
+    with pytest.raises(ValueError, match="32 bits"):
+        planner.plan_partition([2**31 - 1] * 64, 1, 64, 148)
+    assert planner.plan_partition([2**20] * 64, 1, 64, 148)  # 64 M tokens: fits
