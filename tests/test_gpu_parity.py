@@ -176,6 +176,38 @@ def test_unknown_variants_are_rejected():
             w.plan(num_heads=64, page_size=64, variant=v)
 
 
+@pytest.mark.parametrize("seed", list(range(48)))
+def test_random_shapes_against_the_oracle(seed):
+    """Seeded random batches: ragged lengths (empty requests, single tokens, tile and page boundaries), head counts,
+    page sizes, query lengths, grid caps, output types, kernels and variants drawn together."""
+    import random
+
+    from flashinfer_mla_fp4_b200 import AttentionWithSink, SoftCappingAttention, synth
+
+    rng = random.Random(1000 + seed)
+    dev = _dev()
+    heads = rng.choice([1, 8, 16, 40, 64, 96, 128])
+    page_size = rng.choice([8, 16, 32, 64, 128])
+    q_len = rng.choice([1, 1, 1, 2, 3])
+    batch = rng.choice([1, 2, 3, 5, 9, 17])
+    pool = [0, 1, 2, 63, 64, 65, 127, 128, 129, 255, 256, 257, 511, 513, 700, 1024, 1500, 3000, 6100, 9000]
+    lens = [rng.choice(pool) for _ in range(batch)]
+    if not any(lens):
+        lens[0] = 130
+    case = synth.build_case(f"fuzz{seed}", [max(n, 1) for n in lens], heads, page_size, q_len=q_len, seed=2000 + seed,
+                            device=dev, latent_dist=rng.choice(["normal", "normal", "student_t3"]))
+    case.seq_lens = torch.tensor(lens, dtype=torch.int32, device=dev)
+    case.seq_lens_host = lens
+    g = torch.Generator().manual_seed(seed)
+    sink = (torch.rand(heads, generator=g) * 10.0 - 4.0).to(dev)
+    variant = rng.choice([None, None, AttentionWithSink(sink), SoftCappingAttention(rng.choice([2.0, 8.0, 30.0])),
+                          SoftCappingAttention(5.0, sink=sink)])
+    kernel = rng.choice(["tcgen05", "tcgen05", "tcgen05_2pass", "fp32_check"])
+    out_dtype = rng.choice([torch.bfloat16, torch.bfloat16, torch.float32])
+    check_case(case, kernel, variant=variant, max_ctas=rng.choice([None, None, 1, 3, 20, 77]), out_dtype=out_dtype,
+               output_scale=rng.choice([1.0, 0.5]))
+
+
 @pytest.mark.parametrize("max_ctas", [1, 7, 40])
 def test_grid_cap_limits_the_split(max_ctas):
     from flashinfer_mla_fp4_b200 import synth
