@@ -174,9 +174,10 @@ int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, i
 
 /* Decode context parallel without a library collective (no counterpart in the reference, which has no
    multi-GPU path).  Every rank owns an "exchange block" of device memory that all peers map through CUDA
-   IPC; mla_fp4_cp_exchange_merge is ONE kernel per rank and step that pushes the rank's partial into every
-   peer's block with plain stores over NVLink, raises a flag there, waits (bounded) for the flags of all
-   peers in its own block and merges.  One process per GPU, all GPUs in one NVLink domain, at most
+   IPC; mla_fp4_cp_exchange_merge is ONE kernel per rank and step that pushes the rank's partial rows into the
+   peers' blocks with plain stores over NVLink (every 16-byte word carries the step number as its arrival tag:
+   no flags, no fences), waits (bounded) for the peers' rows in its own block and merges.  Nothing is read from
+   a peer's memory.  One process per GPU, all GPUs in one NVLink domain, at most
    MLA_FP4_CP_MAX_RANKS ranks; every rank must make the same sequence of calls.
      mla_fp4_cp_exchange_bytes: size of a block for partials of up to max_rows rows (rows = batch*q_len*heads).
      mla_fp4_cp_alloc:  allocates (cudaMalloc) and zeroes this rank's block and returns its IPC handle
@@ -190,9 +191,10 @@ int mla_fp4_merge_partials(const float* partial_out, const float* partial_lse, i
                         the kernel as a programmatic dependent launch (it starts while the kernel before it on the
                         stream drains and waits for that kernel's end before it reads anything);
                         out [rows][512] (out_dtype), optional lse [rows]; status as in MlaFp4DecodeArgs (word 0 set
-                        to MLA_FP4_ERR_DEVICE_TIMEOUT when a peer's flag does not arrive within wait_polls polls,
-                        0 = default); asynchronous on `stream`, CUDA-graph capturable (the step counter lives in
-                        the block). */
+                        to MLA_FP4_ERR_DEVICE_TIMEOUT when a peer's rows do not arrive within wait_polls polls,
+                        0 = default); asynchronous on `stream`, CUDA-graph capturable (the step counters live in
+                        the block).  After a reported time-out the ranks' step counters disagree: free the
+                        blocks and set up new ones. */
 #define MLA_FP4_CP_MAX_RANKS 8
 #define MLA_FP4_CP_HANDLE_BYTES 64
 /* form of the exchange: every rank receives every peer's rows and merges them all (one NVLink hop, (world-1) partials
