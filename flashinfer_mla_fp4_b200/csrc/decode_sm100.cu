@@ -62,7 +62,9 @@ constexpr int kBlocks = 4;                 // 128-dim blocks of the latent
 constexpr int kBlockBytes = kTile * 128;   // 16 KiB: [128 tokens][128 B], 128B swizzle
 constexpr int kMaxSeg = 16;                // segments staged per round
 constexpr float kPShift = 4.0f;            // P' = 2^(y - M + 4): keeps the E4M3 lo term out of the subnormals
-constexpr float kLazyThreshold = 4.0f;     // the reference is refreshed only when beaten by 2^4 (P' <= 2^8 < 448)
+constexpr float kLazyThreshold = 4.75f;    // the reference is refreshed only when beaten by 2^4.75: P' <= 2^8.75 = 430.5, just inside
+                                           // E4M3 (448).  A refresh costs a CTA a tile and a half, and the CTAs that had one set the
+                                           // kernel's end; at 2^4 the north-star data had eight of them, at 2^4.75 none.
 
 // shared memory map (bytes from a 1024-aligned base)
 constexpr uint32_t kOffKV = 0;                                            // [10][16384]
