@@ -1209,78 +1209,100 @@ __device__ __noinline__ void plan_merge(const Ctx& c, int lane) {
 
 // The tail runs once per CTA: small loop bodies, shared memory read with ld.shared in batches (a chain of
 // dependent load-then-add iterations is what made an earlier version slow, not the amount of work).
-__device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int tid) {
+// Geometry of this CTA's part in the merge (from the plan).
+struct TailGeo {
+  int ns, U0, U1;
+  uint32_t share_bytes, rows, tails, list;
+  bool fits;
+};
+__device__ __forceinline__ TailGeo tail_geo(const Ctx& c) {
+  const Misc* misc = c.misc;
+  TailGeo g;
+  g.ns = misc->n_slots;
+  // This CTA's share of every slot: units [2048*rank/np, 2048*(rank+1)/np) of 32 bytes (a pair of dims of one head
+  // group, in the slot's own order), so a share is one contiguous range of the slot: one bulk copy.
+  g.U0 = misc->unit0;
+  g.U1 = misc->unit1;
+  g.share_bytes = uint32_t(g.U1 - g.U0) * 32u;
+  g.list = c.smem + kOffTail;
+  g.rows = c.smem + kTailStage;
+  g.tails = g.rows + uint32_t(g.ns) * g.share_bytes;  // the tails of the listed slots, in list order
+  g.fits = uint32_t(g.ns) * (g.share_bytes + kTailLseBytes) <= kTailStageBytes;
+  return g;
+}
+
+// Fetching the partials: run by the four warps that issue copies and MMAs (QK, TMA, PV, PV2), which have nothing left
+// to do once the last tile's MMAs have drained, while the eight softmax warps still normalise, write and publish this
+// CTA's own partial: the staging area (the KV ring, RoPE, Q and P buffers) is free from that moment, and whatever the
+// other CTAs have published by then is on its way before this CTA's own partial is out.  Slot i (and i + 128) belongs to
+// lane i / 4 of helper warp i % 4: wait for its flag, then fetch this CTA's share of it and its tail (LSEs, scale).  A
+// bulk copy costs about fifty clocks to issue whatever its size and the lanes of a warp issue theirs one after the other,
+// so the slots are dealt round the warps.  The lanes of a warp poll in step (a ballot ends the loop).
+__device__ __noinline__ void tail_fetch(const DecodeParams& p, const Ctx& c, int hw, int lane) {
   Misc* misc = c.misc;
   void* ws = p.workspace;
-  const int ns = misc->n_slots;
+  const TailGeo g = tail_geo(c);
+  if (g.ns == 0) return;
+  if (hw == 0 && lane == 0) {
+    if (!g.fits) flag_timeout(c, 200, uint32_t(g.ns));  // cannot happen: mergers >= writers - 1
+    MLA_TRACE(3, 1u, 1);
+  }
+  const uint32_t bar = bar_addr(c, kBarTail);
+#pragma unroll 1
+  for (int i = lane * 4 + hw; i < kMaxCombineSlots + 128; i += 128) {  // the loop bound is uniform; a lane without a slot idles
+    const bool mine = i < g.ns;
+    if (!__any_sync(0xffffffffu, mine) || misc->abort) break;
+    const int slot = mine ? int(lds_u32(g.list + 4u * uint32_t(i))) : 0;
+    const int32_t* flag = slot_flag(ws, slot);
+    bool done = !mine;
+#pragma unroll 1
+    for (uint32_t it = 0; it < c.polls; ++it) {
+      const bool now = !done && ld_acquire(flag) == c.gen;  // acquire: the slot's bytes, written before the flag, are read after it
+      if (now) {
+        done = true;
+#ifdef MLA_FP4_TRACE
+        if (int(blockIdx.x) == c.trace_cta && c.status && i < 96) {
+          unsigned long long t;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+          long long* tr = reinterpret_cast<long long*>(c.status + 8) + ((4 + (i >> 4)) * 16 + (i & 15)) * 8;
+          tr[0] = (long long)t;
+          tr[1] = slot;
+        }
+#endif
+        if (g.fits) {
+          // The copy reads the slot from L2, where its writer's release put it before the flag: no proxy fence is
+          // needed for that, and a full fence.proxy.async here cost microseconds.
+          ptx::mbar_arrive_expect_tx(bar, g.share_bytes + kTailLseBytes);
+          ptx::bulk_load(g.rows + uint32_t(i) * g.share_bytes, reinterpret_cast<const char*>(slot_o(ws, slot)) + size_t(g.U0) * 32, g.share_bytes, bar);
+          ptx::bulk_load(g.tails + uint32_t(i) * kTailLseBytes, slot_lse(ws, slot), kTailLseBytes, bar);  // its LSEs and scale
+        } else {
+          ptx::mbar_arrive(bar);
+        }
+      }
+      if (__all_sync(0xffffffffu, done) || misc->abort) break;
+      __nanosleep(64);
+    }
+    if (!done) {  // the budget ran out (or the CTA is giving up): the barrier still gets this slot's arrival
+      if (!misc->abort) flag_timeout(c, 100, uint32_t(slot));
+      ptx::mbar_arrive(bar);
+    }
+  }
+  if (hw == 0 && lane == 0) MLA_TRACE(3, 1u, 2);
+}
+
+__device__ __noinline__ void tail_merge(const DecodeParams& p, const Ctx& c, int tid) {
+  Misc* misc = c.misc;
+  const TailGeo geo = tail_geo(c);
+  const int ns = geo.ns;
   if (ns == 0) return;
-  const int np = misc->n_part, rank = misc->rank;
+  const int rank = misc->rank;
   const MergeReq m = misc->merge[misc->merge_k];
-  const uint32_t list = c.smem + kOffTail;
   int qpos, head0;
   group_coords(m.g, p.num_heads, qpos, head0);
   const int heads_here = min(kGroupHeads, p.num_heads - head0);
   const size_t row0 = (size_t(m.b) * p.q_len + qpos) * p.num_heads + head0;
-  // This CTA's share of every slot: units [2048*rank/np, 2048*(rank+1)/np) of 32 bytes (a pair of dims of one head
-  // group, in the slot's own order), so a share is one contiguous range of the slot: one bulk copy.
-  const int U0 = misc->unit0, U1 = misc->unit1;
-  const uint32_t share_bytes = uint32_t(U1 - U0) * 32u;
-  const uint32_t rows = c.smem + kTailStage;
-  const uint32_t tails = rows + uint32_t(ns) * share_bytes;  // the tails of the listed slots, in list order
-  const bool fits = uint32_t(ns) * (share_bytes + kTailLseBytes) <= kTailStageBytes;
-  if (tid == 0) {
-    if (!fits) flag_timeout(c, 200, uint32_t(ns));  // cannot happen: mergers >= writers - 1
-    MLA_TRACE(3, 1u, 1);
-  }
-  // Slot i belongs to lane i / kWarps of warp i % kWarps: wait for its flag, then fetch this CTA's share of it and its
-  // tail (LSEs, scale).  A bulk copy costs about fifty clocks to issue whatever its size and the lanes of a warp issue
-  // theirs one after the other, so the slots are dealt round the warps (32 slots on one warp spent 1.6 k clocks
-  // issuing).  The lanes of a warp poll in step (a ballot ends the loop).
-  {
-    constexpr int kWarps = kThreads / 32;
-    const int warp = tid >> 5, lane = tid & 31;
-    const int i = lane * kWarps + warp;           // slot index in the list
-    const bool mine = i < ns;
-    const bool busy = __any_sync(0xffffffffu, mine);
-    if (busy && !misc->abort) {
-      const int slot = mine ? int(lds_u32(list + 4u * uint32_t(i))) : 0;
-      const int32_t* flag = slot_flag(ws, slot);
-      const uint32_t bar = bar_addr(c, kBarTail);
-      bool done = !mine;
-#pragma unroll 1
-      for (uint32_t it = 0; it < c.polls; ++it) {
-        const bool now = !done && ld_acquire(flag) == c.gen;  // acquire: the slot's bytes, written before the flag, are read after it
-        if (now) {
-          done = true;
-#ifdef MLA_FP4_TRACE
-          if (int(blockIdx.x) == c.trace_cta && c.status && i < 96) {
-            unsigned long long t;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            long long* tr = reinterpret_cast<long long*>(c.status + 8) + ((4 + (i >> 4)) * 16 + (i & 15)) * 8;
-            tr[0] = (long long)t;
-            tr[1] = slot;
-          }
-#endif
-          if (fits) {
-            // The copy reads the slot from L2, where its writer's fence put it before the flag: no proxy fence is
-            // needed for that, and a full fence.proxy.async here cost microseconds.
-            ptx::mbar_arrive_expect_tx(bar, share_bytes + kTailLseBytes);
-            ptx::bulk_load(rows + uint32_t(i) * share_bytes, reinterpret_cast<const char*>(slot_o(ws, slot)) + size_t(U0) * 32, share_bytes, bar);
-            ptx::bulk_load(tails + uint32_t(i) * kTailLseBytes, slot_lse(ws, slot), kTailLseBytes, bar);  // its LSEs and scale
-          } else {
-            ptx::mbar_arrive(bar);
-          }
-        }
-        if (__all_sync(0xffffffffu, done) || misc->abort) break;
-        __nanosleep(64);
-      }
-      if (!done) {  // the budget ran out (or the CTA is giving up): the barrier still gets this slot's arrivals
-        if (!misc->abort) flag_timeout(c, 100, uint32_t(slot));
-        ptx::mbar_arrive(bar);
-      }
-    }
-  }
-  if (tid == 0) MLA_TRACE(3, 1u, 2);
+  const int U0 = geo.U0, U1 = geo.U1;
+  const uint32_t share_bytes = geo.share_bytes, rows = geo.rows, tails = geo.tails;
   const bool landed = wait(c, kBarTail, 0);
   if (tid == 0) MLA_TRACE(3, 1u, 3);
   if (landed && !misc->abort) {
@@ -1502,19 +1524,20 @@ mla_fp4_decode_sm100_kernel(const DecodeParams p, const __grid_constant__ CUtens
       tma_role(p, c, &map_q_lat, &map_q_rope, &map_rope, &map_lat, st);
     }
     const int more = c.misc->more;
+    if (!more && warp < kWarpSoftmax0) {
+      // Last round: drain (everything issued has completed before TMEM is released and before shared memory is reused:
+      // a commit covers the MMAs of the thread that executes it), then these four warps, idle from here on, fetch the
+      // partials of the request this CTA merges while the softmax warps finish with its own.
+      if (warp != kWarpTMA && ptx::elect_one()) ptx::umma_commit(bar_addr(c, kBarDrain));
+      __syncwarp();
+      if ((tid & 31) == 0) drain_wait(c, kBarDrain, 0);
+      __syncwarp();
+      if (p.fused_merge) tail_fetch(p, c, warp, tid & 31);
+    }
     __syncthreads();  // every role is done with the staged segments
     if (!more) break;
     if (tid == 0) stage_segments(c);
     __syncthreads();
-  }
-
-  // drain: everything issued has completed before TMEM is released
-  if (warp == kWarpQK || warp == kWarpPV || warp == kWarpPV2) {  // a commit covers the MMAs of the thread that executes it
-    if (ptx::elect_one()) {
-      ptx::umma_commit(bar_addr(c, kBarDrain));
-      drain_wait(c, kBarDrain, 0);
-    }
-    __syncwarp();
   }
   ptx::tc_fence_before();
   __syncthreads();
